@@ -1,0 +1,229 @@
+"""The cache manager: pages of keys and values, block tables, and state slots.
+
+Storage
+-------
+Every schedule entry that owns a cache stores, per token, `kv_heads` keys and values
+of `head_dim`. Entries whose needs are equal (same heads, head size and window) form a
+*group*; a group has its own pool of pages and, per request, its own block table. One
+tensor per group, `[entries, pages, 2, kv_heads, page_size, head_dim]`, holds the
+group's pages: page `p` of entry `e` is `tensor[e, p]`, keys at index 0 and values at
+index 1 of the next axis. A request's logical page `i` (positions `i * page_size` to
+`(i + 1) * page_size - 1`) maps to the same physical page number in every entry of
+the group.
+
+A group with a window gives a page back as soon as every position in it is behind
+the window of all tokens still to come; its block-table entry becomes -1. All pages
+return when the request ends. Freed pages are handed out again, last freed first.
+
+Beside the pages there are *state slots*: a request holds one slot number for its
+whole life, and every entry that declares a `StateSpec` has a tensor
+`[slots, *shape]` indexed by it. Muse-Glimmer declares none; the slots exist so a
+mixer with state of its own needs no change here.
+
+The reference keeps one growing buffer per request and layer instead
+(src/mlx_omnia/engine/core/cache/kv.py:18-128) and says which rows a window makes
+unreadable through `Rows.keep` (src/mlx_omnia/engine/core/cache/layout.py:14-24);
+paging, groups and slots are this engine's own design.
+
+All bookkeeping is host-side Python and runs without a GPU (`device="meta"` or
+`allocate=False` skips the tensors).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from mlx_omnia_b200.parts.base import KVSpec, StateSpec
+from mlx_omnia_b200.parts.model import CacheNeed
+
+
+class CacheError(RuntimeError):
+    """Misuse of the cache manager: a page freed twice, an unknown request, ..."""
+
+
+class PagePool:
+    """Page numbers 0..count-1; a stack of free ones (last freed, first reused)."""
+
+    def __init__(self, count: int) -> None:
+        self.count = count
+        self._free = list(range(count - 1, -1, -1))
+        self._held = [False] * count
+
+    @property
+    def free(self) -> int:
+        return len(self._free)
+
+    def take(self) -> int:
+        if not self._free:
+            raise CacheError("no free page")
+        page = self._free.pop()
+        self._held[page] = True
+        return page
+
+    def give(self, page: int) -> None:
+        if not 0 <= page < self.count:
+            raise CacheError(f"page {page} is not in a pool of {self.count}")
+        if not self._held[page]:
+            raise CacheError(f"page {page} is freed twice")
+        self._held[page] = False
+        self._free.append(page)
+
+    def held(self) -> list[int]:
+        return [p for p, h in enumerate(self._held) if h]
+
+
+@dataclass
+class Group:
+    spec: KVSpec
+    entries: list[int]  # schedule entries stored in this group, in tensor order
+    pool: PagePool
+    pages: torch.Tensor | None  # [entries, pages, 2, kv_heads, page_size, head_dim]
+
+
+@dataclass
+class RequestCache:
+    """What one live request holds."""
+
+    request_id: str
+    tokens: int = 0  # positions written so far
+    tables: list[list[int]] = field(default_factory=list)  # per group: physical page per logical page (-1 freed)
+    slot: int = -1
+    fresh: bool = True  # no step has run for it yet
+
+
+class CacheManager:
+    def __init__(self, needs: list[CacheNeed], *, page_size: int, pages_per_group: int | dict[KVSpec, int],
+                 max_requests: int, dtype: torch.dtype = torch.bfloat16, device: torch.device | str = "cpu",
+                 allocate: bool = True) -> None:
+        if page_size < 1:
+            raise ValueError("page_size must be at least 1")
+        self.page_size = page_size
+        self.needs = needs
+        self.groups: list[Group] = []
+        self.group_of_entry: dict[int, tuple[int, int]] = {}  # entry -> (group, index in group)
+        by_spec: dict[KVSpec, int] = {}
+        for entry, need in enumerate(needs):
+            if need.kv is None:
+                continue
+            g = by_spec.get(need.kv)
+            if g is None:
+                g = by_spec[need.kv] = len(self.groups)
+                count = pages_per_group[need.kv] if isinstance(pages_per_group, dict) else pages_per_group
+                self.groups.append(Group(need.kv, [], PagePool(count), None))
+            self.group_of_entry[entry] = (g, len(self.groups[g].entries))
+            self.groups[g].entries.append(entry)
+        for entry, need in enumerate(needs):
+            if need.reads is not None:
+                if need.reads not in self.group_of_entry:
+                    raise ValueError(f"schedule entry {entry} reads entry {need.reads}, which keeps no pages")
+                self.group_of_entry[entry] = self.group_of_entry[need.reads]
+        if allocate:
+            for group in self.groups:
+                s = group.spec
+                group.pages = torch.zeros(len(group.entries), group.pool.count, 2, s.kv_heads, page_size, s.head_dim,
+                                          dtype=dtype, device=device)
+        self.slots = PagePool(max_requests)
+        self.state: dict[int, torch.Tensor] = {}
+        for entry, need in enumerate(needs):
+            if need.state is not None and allocate:
+                self.state[entry] = torch.zeros(max_requests, *need.state.shape, dtype=need.state.dtype, device=device)
+        self.requests: dict[str, RequestCache] = {}
+
+    # -- sizes -----------------------------------------------------------------------
+    def bytes_per_page(self, group: int, element_size: int) -> int:
+        g = self.groups[group]
+        return len(g.entries) * 2 * g.spec.kv_heads * self.page_size * g.spec.head_dim * element_size
+
+    def pages_needed(self, request: RequestCache, new_tokens: int) -> list[int]:
+        """Pages each group must take for `request` to grow by `new_tokens`."""
+        have = -(-request.tokens // self.page_size)
+        want = -(-(request.tokens + new_tokens) // self.page_size)
+        return [want - have for _ in self.groups]
+
+    def can_grow(self, request: RequestCache, new_tokens: int, reserve: list[int] | None = None) -> bool:
+        need = self.pages_needed(request, new_tokens)
+        return all(n <= g.pool.free - (reserve[i] if reserve else 0)
+                   for i, (n, g) in enumerate(zip(need, self.groups)))
+
+    # -- life of a request -------------------------------------------------------------
+    def open(self, request_id: str) -> RequestCache:
+        if request_id in self.requests:
+            raise CacheError(f"request {request_id!r} is already open")
+        if self.slots.free == 0:
+            raise CacheError("no free request slot")
+        request = RequestCache(request_id, tables=[[] for _ in self.groups], slot=self.slots.take())
+        self.requests[request_id] = request
+        return request
+
+    def grow(self, request: RequestCache, new_tokens: int) -> None:
+        """Take the pages for the next `new_tokens` positions in every group, or none
+        at all (CacheError) when some group has too few free pages."""
+        if new_tokens < 0:
+            raise ValueError("new_tokens must not be negative")
+        need = self.pages_needed(request, new_tokens)
+        for n, group in zip(need, self.groups):
+            if n > group.pool.free:
+                raise CacheError(f"group {group.spec} needs {n} pages, {group.pool.free} free")
+        for n, group, table in zip(need, self.groups, request.tables):
+            for _ in range(n):
+                table.append(group.pool.take())
+        request.tokens += new_tokens
+
+    def slot_of(self, request: RequestCache, group: int, position: int) -> int:
+        page = request.tables[group][position // self.page_size]
+        if page < 0:
+            raise CacheError(f"position {position} of {request.request_id!r} lies in a page already given back")
+        return page * self.page_size + position % self.page_size
+
+    def release_behind_window(self, request: RequestCache) -> int:
+        """Give back pages of windowed groups that no later token can read. With
+        `tokens` positions written, the next query sits at position >= tokens and sees
+        keys >= tokens - window + 1. Returns how many pages were freed."""
+        freed = 0
+        for group, table in zip(self.groups, request.tables):
+            window = group.spec.window
+            if window is None:
+                continue
+            dead_below = request.tokens - window + 1  # positions < this are never read again
+            for index in range(min(len(table), max(dead_below, 0) // self.page_size)):
+                if table[index] >= 0:
+                    group.pool.give(table[index])
+                    table[index] = -1
+                    freed += 1
+        return freed
+
+    def close(self, request_id: str) -> None:
+        """The request ended: everything it holds is given back."""
+        request = self.requests.pop(request_id, None)
+        if request is None:
+            raise CacheError(f"request {request_id!r} is not open")
+        for group, table in zip(self.groups, request.tables):
+            for page in table:
+                if page >= 0:
+                    group.pool.give(page)
+            table.clear()
+        self.slots.give(request.slot)
+        request.slot = -1
+
+    # -- views for a step --------------------------------------------------------------
+    def entry_pages(self, entry: int) -> torch.Tensor:
+        g, index = self.group_of_entry[entry]
+        return self.groups[g].pages[index]
+
+    def check(self) -> None:
+        """Every page is either free or in exactly one table (used by tests)."""
+        for g, group in enumerate(self.groups):
+            seen: dict[int, str] = {}
+            for request in self.requests.values():
+                for page in request.tables[g]:
+                    if page < 0:
+                        continue
+                    if page in seen:
+                        raise CacheError(f"page {page} of group {g} is held by {seen[page]!r} and {request.request_id!r}")
+                    seen[page] = request.request_id
+            if sorted(seen) != group.pool.held():
+                raise CacheError(f"group {g}: pages in tables {sorted(seen)} differ from pages taken {group.pool.held()}")
+            if len(seen) + group.pool.free != group.pool.count:
+                raise CacheError(f"group {g}: a page was lost")

@@ -1,0 +1,79 @@
+// Shared device helpers for the sm_100a kernels of this package.
+//
+// Every exported function is `extern "C"`, takes raw device pointers, sizes and
+// the CUDA stream to launch on, allocates nothing, and returns the cudaError_t of
+// its launch as an int (0 = launched). Element types are chosen by a code:
+// 0 = float32, 1 = bfloat16. Reductions, softmax, norms and rotation angles are
+// always computed in float32 whatever the element type.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define OMNIA_F32 0
+#define OMNIA_BF16 1
+
+// Bits of the device error word (see omnia_error_fetch in elementwise.cu).
+#define OMNIA_ERR_TOKEN_ID 1   // a token id outside the embedding table
+#define OMNIA_ERR_SLOT 2       // a cache slot outside the page pool
+#define OMNIA_ERR_PAGE 4       // a block-table entry outside the page pool was needed
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over the block; every thread gets the result. `scratch` holds 33 floats.
+// The order of the additions depends only on blockDim, never on the data.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // scratch may still be read from an earlier call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    const int warps = (blockDim.x + 31) >> 5;
+    float t = lane < warps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+#define OMNIA_LAUNCH_RESULT() ((int)cudaGetLastError())
+
+#define OMNIA_DISPATCH_DTYPE(code, ...)                    \
+  do {                                                     \
+    if ((code) == OMNIA_F32) {                             \
+      using T = float;                                     \
+      __VA_ARGS__;                                         \
+    } else if ((code) == OMNIA_BF16) {                     \
+      using T = __nv_bfloat16;                             \
+      __VA_ARGS__;                                         \
+    } else {                                               \
+      return (int)cudaErrorInvalidValue;                   \
+    }                                                      \
+  } while (0)

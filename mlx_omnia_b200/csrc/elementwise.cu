@@ -1,0 +1,274 @@
+// Embedding, norms, rotation + cache write, gated activation, logit cap, row gather.
+// One row (token) per block unless said otherwise; float32 arithmetic throughout.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------
+// Embedding lookup with an optional weightless RMS norm: x[t] = rms0(table[ids[t]]).
+// The residual stream x is float32 in both precisions.
+template <typename T>
+__global__ void embed_rmsnorm_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                     float* __restrict__ x, int hidden, int vocab, float eps,
+                                     int normed, int* err) {
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(err, OMNIA_ERR_TOKEN_ID);
+    id = 0;
+  }
+  const T* row = table + (size_t)id * hidden;
+  float* out = x + (size_t)t * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = to_f32(row[i]);
+    ss += v * v;
+  }
+  float scale = 1.f;
+  if (normed) scale = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_f32(row[i]) * scale;
+}
+
+extern "C" int omnia_embed_rmsnorm(const int* ids, const void* table, float* x, int tokens,
+                                   int hidden, int vocab, float eps, int normed, int dtype,
+                                   int* err, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  OMNIA_DISPATCH_DTYPE(dtype, (embed_rmsnorm_kernel<T><<<tokens, 256, 0, stream>>>(
+                                  ids, (const T*)table, x, hidden, vocab, eps, normed, err)));
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------------------------
+// h = x * rsqrt(mean(x^2) + eps) * w   (w may be null: weightless). x is float32.
+template <typename T>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                               T* __restrict__ h, int hidden, float eps) {
+  __shared__ float scratch[33];
+  const float* row = x + (size_t)blockIdx.x * hidden;
+  T* out = h + (size_t)blockIdx.x * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) ss += row[i] * row[i];
+  const float scale = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = row[i] * scale;
+    if (w) v *= w[i];
+    out[i] = from_f32<T>(v);
+  }
+}
+
+extern "C" int omnia_rmsnorm(const float* x, const float* w, void* h, int rows, int hidden,
+                             float eps, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  OMNIA_DISPATCH_DTYPE(dtype,
+                       (rmsnorm_kernel<T><<<rows, 256, 0, stream>>>(x, w, (T*)h, hidden, eps)));
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------------------------
+// The residual step of a block, in one pass over the row:
+//   a  = branch                      (optionally normed: a * rsqrt(mean a^2 + eps_b) * wb)
+//   x += a                           (float32, in place)
+//   h  = x * rsqrt(mean x^2 + eps_o) * wo   (optional; wo may be null)
+// The row is staged in shared memory as float32, so the branch is read once and x is
+// read and written once.
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ branch,
+                                   const float* __restrict__ wb, float eps_b, int norm_branch,
+                                   const float* __restrict__ wo, float eps_o, int norm_out,
+                                   T* __restrict__ h, int hidden) {
+  extern __shared__ float row[];
+  __shared__ float scratch[33];
+  float* xr = x + (size_t)blockIdx.x * hidden;
+  const T* br = branch + (size_t)blockIdx.x * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float a = to_f32(br[i]);
+    row[i] = a;
+    ss += a * a;
+  }
+  float scale_b = 1.f;
+  if (norm_branch) scale_b = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps_b);
+  ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float a = row[i];
+    if (norm_branch) {
+      a *= scale_b;
+      if (wb) a *= wb[i];
+    }
+    const float v = xr[i] + a;
+    xr[i] = v;
+    row[i] = v;
+    ss += v * v;
+  }
+  if (!norm_out) return;
+  const float scale_o = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps_o);
+  T* out = h + (size_t)blockIdx.x * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = row[i] * scale_o;
+    if (wo) v *= wo[i];
+    out[i] = from_f32<T>(v);
+  }
+}
+
+extern "C" int omnia_add_rmsnorm(float* x, const void* branch, const float* wb, float eps_b,
+                                 int norm_branch, const float* wo, float eps_o, int norm_out,
+                                 void* h, int rows, int hidden, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  const size_t smem = (size_t)hidden * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  OMNIA_DISPATCH_DTYPE(dtype, {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem);
+    add_rmsnorm_kernel<T><<<rows, 256, smem, stream>>>(x, (const T*)branch, wb, eps_b,
+                                                       norm_branch, wo, eps_o, norm_out, (T*)h,
+                                                       hidden);
+  });
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------------------------
+// Per head of a projected row [.. q heads .. | .. k heads .. | .. v heads ..] (each
+// group at its own column of `proj`): weightless RMS over the head (q and k; eps < 0
+// skips it), half-split rotation of the first `rot` dims by angle pos * inv_freq[i]
+// (inv_freq null: no rotation), then q goes to q_out and k, v go into cache pages
+// [page][k|v][kv_head][offset][d] at slot_mapping[t] (slot < 0: nothing is stored).
+// One warp per head, four heads per block; head_dim <= 256 and even.
+template <typename T>
+__global__ void qk_norm_rope_store_kernel(const T* __restrict__ proj, int row_stride, int q_col,
+                                          int k_col, int v_col, int nq, int nkv, int d,
+                                          float eps, const float* __restrict__ inv_freq, int rot,
+                                          const int* __restrict__ positions,
+                                          const long long* __restrict__ slot_mapping,
+                                          T* __restrict__ q_out, T* __restrict__ pages,
+                                          int page_size, long long num_slots, int* err) {
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hs = blockIdx.y * (blockDim.x >> 5) + warp;
+  if (hs >= nq + 2 * nkv) return;
+  const int kind = hs < nq ? 0 : (hs < nq + nkv ? 1 : 2);
+  const int head = kind == 0 ? hs : (kind == 1 ? hs - nq : hs - nq - nkv);
+  const T* src = proj + (size_t)t * row_stride + (kind == 0 ? q_col : kind == 1 ? k_col : v_col) +
+                 (size_t)head * d;
+  T* dst;
+  if (kind == 0) {
+    dst = q_out + ((size_t)t * nq + head) * d;
+  } else {
+    const long long slot = slot_mapping[t];
+    if (slot < 0) return;
+    if (slot >= num_slots) {
+      if (lane == 0) atomicOr(err, OMNIA_ERR_SLOT);
+      return;
+    }
+    const long long page = slot / page_size, off = slot % page_size;
+    dst = pages + (((page * 2 + (kind == 2)) * nkv + head) * page_size + off) * d;
+  }
+  if (kind == 2) {
+    for (int i = lane; i < d; i += 32) dst[i] = src[i];
+    return;
+  }
+  // The head is staged in shared memory as float32: norm, then rotation, then one rounding.
+  __shared__ float staged[4][256];
+  float* v = staged[warp];
+  float ss = 0.f;
+  for (int i = lane; i < d; i += 32) {
+    const float a = to_f32(src[i]);
+    v[i] = a;
+    ss += a * a;
+  }
+  float scale = 1.f;
+  if (eps >= 0.f) scale = rsqrtf(warp_sum(ss) / (float)d + eps);
+  __syncwarp();
+  const int rhalf = inv_freq != nullptr ? rot / 2 : 0;
+  const float pos = (float)positions[t];
+  for (int i = lane; i < rhalf; i += 32) {
+    float s, c;
+    sincosf(pos * inv_freq[i], &s, &c);
+    const float a = v[i] * scale, b = v[i + rhalf] * scale;
+    dst[i] = from_f32<T>(a * c - b * s);
+    dst[i + rhalf] = from_f32<T>(a * s + b * c);
+  }
+  for (int i = 2 * rhalf + lane; i < d; i += 32) dst[i] = from_f32<T>(v[i] * scale);
+}
+
+extern "C" int omnia_qk_norm_rope_store(const void* proj, int row_stride, int q_col, int k_col,
+                                        int v_col, int nq, int nkv, int d, float eps,
+                                        const float* inv_freq, int rot, const int* positions,
+                                        const long long* slot_mapping, void* q_out, void* pages,
+                                        int page_size, long long num_slots, int tokens, int dtype,
+                                        int* err, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (d > 256 || (d & 1) || rot > d || (rot & 1)) return (int)cudaErrorInvalidValue;
+  const int heads = nq + 2 * nkv;
+  dim3 grid(tokens, (heads + 3) / 4);
+  OMNIA_DISPATCH_DTYPE(dtype, (qk_norm_rope_store_kernel<T><<<grid, 128, 0, stream>>>(
+                                  (const T*)proj, row_stride, q_col, k_col, v_col, nq, nkv, d, eps,
+                                  inv_freq, rot, positions, slot_mapping, (T*)q_out, (T*)pages,
+                                  page_size, num_slots, err)));
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------------------------
+// act[t, i] = silu(gu[t, i]) * gu[t, inner + i], in float32, rounded once.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, long long total,
+                              int inner) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += stride) {
+    const long long t = idx / inner;
+    const int i = (int)(idx - t * inner);
+    const float g = to_f32(gu[t * 2 * inner + i]);
+    const float u = to_f32(gu[t * 2 * inner + inner + i]);
+    act[idx] = from_f32<T>(g / (1.f + expf(-g)) * u);
+  }
+}
+
+extern "C" int omnia_swiglu(const void* gu, void* act, int rows, int inner, int dtype,
+                            cudaStream_t stream) {
+  const long long total = (long long)rows * inner;
+  if (total == 0) return 0;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  OMNIA_DISPATCH_DTYPE(dtype, (swiglu_kernel<T><<<blocks, 256, 0, stream>>>(
+                                  (const T*)gu, (T*)act, total, inner)));
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------------------------
+// logits = cap * tanh(z * multiplier / cap)  (cap <= 0: logits = z * multiplier), float32 out.
+template <typename T>
+__global__ void softcap_kernel(const T* __restrict__ z, float* __restrict__ out, long long total,
+                               float multiplier, float cap) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += stride) {
+    const float v = to_f32(z[idx]) * multiplier;
+    out[idx] = cap > 0.f ? cap * tanhf(v / cap) : v;
+  }
+}
+
+extern "C" int omnia_softcap(const void* z, float* out, long long total, float multiplier,
+                             float cap, int dtype, cudaStream_t stream) {
+  if (total == 0) return 0;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  OMNIA_DISPATCH_DTYPE(dtype, (softcap_kernel<T><<<blocks, 256, 0, stream>>>((const T*)z, out,
+                                                                            total, multiplier, cap)));
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------------------------
+// out[r] = src[rows[r]]  (rows of `width` elements)
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restrict__ rows,
+                                   T* __restrict__ out, int width) {
+  const T* s = src + (size_t)rows[blockIdx.x] * width;
+  T* o = out + (size_t)blockIdx.x * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = s[i];
+}
+
+extern "C" int omnia_gather_rows(const void* src, const int* rows, void* out, int count, int width,
+                                 int dtype, cudaStream_t stream) {
+  if (count == 0) return 0;
+  OMNIA_DISPATCH_DTYPE(dtype, (gather_rows_kernel<T><<<count, 256, 0, stream>>>(
+                                  (const T*)src, rows, (T*)out, width)));
+  return OMNIA_LAUNCH_RESULT();
+}

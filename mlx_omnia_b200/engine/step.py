@@ -1,0 +1,132 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A step takes entries `(request, tokens, want)`: the request's next tokens, any number
+from one (a decoded token) to a whole prompt, cut anywhere, and the places among them
+whose logits are wanted. All entries run as one flattened batch; only these tokens
+are computed, everything earlier is read from the cache. It returns float32 logits
+`[wanted, vocab]` in the order of the entries and of `want`.
+
+The reference runs either one request's prompt block or a batch of single decode
+tokens per forward, never both (src/mlx_omnia/server/runtime/rounds.py:159-202,
+src/mlx_omnia/engine/batching.py:283-301,541-576); the mixed flattened batch is this
+engine's own design.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from mlx_omnia_b200.cache.manager import CacheManager, RequestCache
+from mlx_omnia_b200.parts.base import KVView, LayerContext, Runtime, StepContext
+from mlx_omnia_b200.parts.model import DecoderModel
+
+
+@dataclass
+class StepEntry:
+    request: RequestCache
+    tokens: list[int]
+    want: list[int] = field(default_factory=list)  # indices into `tokens`
+
+
+class StepRunner:
+    """Owns nothing but the glue: the model, the cache manager and the runtime."""
+
+    def __init__(self, model: DecoderModel, cache: CacheManager, runtime: Runtime) -> None:
+        self.model, self.cache, self.runtime = model, cache, runtime
+        self.steps_run = 0
+
+    # -- metadata ----------------------------------------------------------------------
+    def _device(self, array: np.ndarray) -> torch.Tensor:
+        tensor = torch.from_numpy(array)
+        if self.runtime.device.type == "cuda":
+            return tensor.pin_memory().to(self.runtime.device, non_blocking=True)
+        return tensor.to(self.runtime.device)
+
+    def build_context(self, entries: list[StepEntry]) -> StepContext:
+        """Take the pages the entries' tokens need and lay the batch out."""
+        cache, page = self.cache, self.cache.page_size
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        for entry in entries:
+            if not entry.tokens:
+                raise ValueError(f"request {entry.request.request_id!r} brings no tokens to this step")
+            if any(not 0 <= w < len(entry.tokens) for w in entry.want):
+                raise ValueError(f"request {entry.request.request_id!r}: a wanted place lies outside its tokens")
+        starts = [entry.request.tokens for entry in entries]
+        grown: list[tuple[RequestCache, int]] = []
+        try:
+            for entry in entries:
+                cache.grow(entry.request, len(entry.tokens))
+                grown.append((entry.request, len(entry.tokens)))
+        except Exception:
+            for request, count in grown:  # give back what this step took
+                self._shrink(request, count)
+            raise
+        q_lens = [len(e.tokens) for e in entries]
+        total = sum(q_lens)
+        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        positions = np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(starts, q_lens)])
+        cu = np.zeros(len(entries) + 1, dtype=np.int32)
+        cu[1:] = np.cumsum(q_lens)
+        seq_lens = np.asarray([e.request.tokens for e in entries], dtype=np.int32)
+        rows = [int(cu[i]) + w for i, e in enumerate(entries) for w in e.want]
+        groups = {}
+        for g in range(len(cache.groups)):
+            width = max(len(e.request.tables[g]) for e in entries)
+            table = np.full((len(entries), max(width, 1)), -1, dtype=np.int32)
+            slots = np.empty(total, dtype=np.int64)
+            for i, e in enumerate(entries):
+                t = np.asarray(e.request.tables[g], dtype=np.int64)
+                table[i, : len(t)] = t
+                pos = positions[cu[i]: cu[i + 1]].astype(np.int64)
+                slots[cu[i]: cu[i + 1]] = t[pos // page] * page + pos % page
+            groups[g] = (self._device(table), self._device(slots))
+        return StepContext(
+            num_tokens=total, num_seqs=len(entries),
+            token_ids=self._device(token_ids), positions=self._device(positions), cu_seqlens=self._device(cu),
+            seq_lens=self._device(seq_lens),
+            state_slots=self._device(np.asarray([e.request.slot for e in entries], dtype=np.int32)),
+            fresh=self._device(np.asarray([int(e.request.fresh) for e in entries], dtype=np.int32)),
+            logit_rows=self._device(np.asarray(rows, dtype=np.int32)),
+            q_lens=q_lens, seq_lens_host=[int(s) for s in seq_lens], max_q_len=max(q_lens),
+            max_seq_len=int(seq_lens.max()), decode_only=all(n == 1 for n in q_lens), groups=groups)
+
+    def _shrink(self, request: RequestCache, count: int) -> None:
+        """Undo a `grow` of `count` tokens that no kernel has used."""
+        page = self.cache.page_size
+        request.tokens -= count
+        keep = -(-request.tokens // page)
+        for group, table in zip(self.cache.groups, request.tables):
+            while len(table) > keep:
+                group.pool.give(table.pop())
+
+    def layer_contexts(self, step: StepContext) -> list[LayerContext]:
+        cache = self.cache
+        contexts = []
+        for entry, need in enumerate(cache.needs):
+            kv = None
+            if entry in cache.group_of_entry:
+                g, _ = cache.group_of_entry[entry]
+                table, slots = step.groups[g]
+                kv = KVView(cache.entry_pages(entry), table, slots, cache.page_size, cache.groups[g].spec.window,
+                            writes=need.reads is None)
+            contexts.append(LayerContext(step, kv, cache.state.get(entry), entry))
+        return contexts
+
+    # -- the step ----------------------------------------------------------------------
+    def run(self, entries: list[StepEntry]) -> torch.Tensor:
+        step = self.build_context(entries)
+        fresh_slots = [e.request.slot for e in entries if e.request.fresh]
+        if fresh_slots and self.cache.state:
+            index = torch.as_tensor(fresh_slots, device=self.runtime.device)
+            for state in self.cache.state.values():
+                state.index_fill_(0, index, 0)
+        logits = self.model.forward(step, self.layer_contexts(step))
+        for entry in entries:
+            entry.request.fresh = False
+            self.cache.release_behind_window(entry.request)
+        self.steps_run += 1
+        return logits

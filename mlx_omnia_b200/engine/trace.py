@@ -1,0 +1,77 @@
+"""Trace replay: feed given token ids through the model step by step, write logits.
+
+It samples nothing and owns no forward pass, cache or loader: it drives the same
+`Engine` (model, step function, cache manager, kernels) that generation uses.
+
+Input, one JSON object per line:
+    {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
+`entries` are one batch; `want` are the places among an entry's tokens whose logits
+are written; `end` lists requests that finish after the step. For a step that wants
+something, `<out>/<step>.f32` holds the logits as little-endian float32
+[wanted, vocab] in the order of the entries and of `want`. After each step the line
+`done <step>` is printed and flushed.
+"""
+
+from __future__ import annotations
+
+import json
+import sys
+from pathlib import Path
+from typing import IO
+
+import numpy as np
+
+from mlx_omnia_b200.engine.engine import Engine, EngineArgs
+from mlx_omnia_b200.engine.step import StepEntry
+from mlx_omnia_b200.kernels import ops
+
+MAX_LIVE_REQUESTS = 4
+TOKEN_ROUNDING = 64
+
+
+def replay(engine: Engine, lines: IO[str], out_dir: Path, done: IO[str] = sys.stdout) -> int:
+    """Run every step read from `lines`; returns how many steps ran."""
+    out_dir.mkdir(parents=True, exist_ok=True)
+    count = 0
+    for line in lines:
+        line = line.strip()
+        if not line:
+            continue
+        record = json.loads(line)
+        entries = []
+        for item in record.get("entries", []):
+            request_id = str(item["id"])
+            request = engine.cache.requests.get(request_id) or engine.cache.open(request_id)
+            entries.append(StepEntry(request, [int(t) for t in item["tokens"]], [int(w) for w in item.get("want", [])]))
+        if entries:
+            logits = engine.runner.run(entries)
+            if logits.shape[0]:
+                host = logits.to("cpu").numpy().astype("<f4", copy=False)
+                host.tofile(out_dir / f"{record['step']}.f32")
+            ops.raise_on_error(engine.runtime.device)
+        for request_id in record.get("end", []):
+            engine.cache.close(str(request_id))
+        print(f"done {record['step']}", file=done, flush=True)
+        count += 1
+    return count
+
+
+def main(argv: list[str] | None = None) -> int:
+    import argparse
+
+    parser = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
+    parser.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    parser.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+    parser.add_argument("--out", required=True, help="folder the logits are written to")
+    parser.add_argument("--max-tokens", type=int, required=True,
+                        help="most tokens live requests hold at any time, each request rounded up to 64")
+    parser.add_argument("--page-size", type=int, default=16, help="tokens per cache page (a divisor of 64)")
+    args = parser.parse_args(argv)
+    if TOKEN_ROUNDING % args.page_size:
+        parser.error("--page-size must divide 64")
+    print(f"[trace_run] loading {args.model} in {args.dtype}", file=sys.stderr, flush=True)
+    engine = Engine.from_folder(args.model, EngineArgs(dtype=args.dtype, page_size=args.page_size,
+                                                       cache_tokens=max(args.max_tokens, TOKEN_ROUNDING),
+                                                       max_requests=MAX_LIVE_REQUESTS))
+    replay(engine, sys.stdin, Path(args.out))
+    return 0

@@ -1,0 +1,218 @@
+"""The operations the parts are written in, each one a launch of this package's own
+CUDA kernels (sources under `csrc/`). There is no other implementation behind these
+functions: on a machine without a CUDA device or without nvcc they raise.
+
+Conventions: tensors are contiguous CUDA tensors; `dtype` is float32 or bfloat16 and
+names the element type of activations, matrices and cache pages; the residual stream
+`x` and all logits are float32; integer metadata is int32 except `slot_mapping`
+(int64). Functions return new tensors unless they say "in place".
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from mlx_omnia_b200.csrc.build import load_library
+from mlx_omnia_b200.parts.base import KVView, StepContext
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+ERROR_BITS = {1: "a token id outside the embedding table", 2: "a cache slot outside the page pool",
+              4: "a block-table entry outside the page pool"}
+
+
+class KernelError(RuntimeError):
+    """A kernel launch failed, or a kernel reported bad indices."""
+
+
+_functions: dict[str, ctypes._CFuncPtr] = {}
+_error_words: dict[int, torch.Tensor] = {}
+
+
+def _function(library: str, name: str, argtypes: list, defines: dict | None = None):
+    key = f"{library}:{name}:{sorted((defines or {}).items())}"
+    fn = _functions.get(key)
+    if fn is None:
+        fn = getattr(load_library(library, defines), name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+        _functions[key] = fn
+    return fn
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: CUDA error {code} at launch (bad sizes for this kernel, or an earlier fault)")
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
+
+
+def error_word(device: torch.device) -> torch.Tensor:
+    """The int32 word that kernels OR their index-check failures into."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    word = _error_words.get(index)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=device)
+        _error_words[index] = word
+    return word
+
+
+def raise_on_error(device: torch.device) -> None:
+    """Read the error word (a device sync) and raise if any kernel flagged bad indices."""
+    word = error_word(device)
+    bits = int(word.item())
+    if bits:
+        word.zero_()
+        raise KernelError("kernel index check failed: " + "; ".join(m for b, m in ERROR_BITS.items() if bits & b))
+
+
+def require_cuda() -> None:
+    if not torch.cuda.is_available():
+        raise KernelError("mlx_omnia_b200 runs on a CUDA device (sm_100a) only; none is visible")
+
+
+# ------------------------------------------------------------------------------------
+
+
+def embed_rmsnorm(ids: torch.Tensor, table: torch.Tensor, eps: float | None) -> torch.Tensor:
+    """x[t] = table[ids[t]], RMS-normalised without a weight when `eps` is given. -> float32."""
+    tokens, (vocab, hidden) = ids.shape[0], table.shape
+    x = torch.empty(tokens, hidden, dtype=torch.float32, device=table.device)
+    fn = _function("elementwise", "omnia_embed_rmsnorm",
+                   [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(ids), _ptr(table), _ptr(x), tokens, hidden, vocab, 0.0 if eps is None else eps,
+              int(eps is not None), _code(table.dtype), _ptr(error_word(table.device)), _stream()), "embed_rmsnorm")
+    return x
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor | None, eps: float, dtype: torch.dtype) -> torch.Tensor:
+    """h = x * rsqrt(mean x^2 + eps) * weight, x float32 [rows, hidden] -> `dtype`."""
+    rows, hidden = x.shape
+    h = torch.empty(rows, hidden, dtype=dtype, device=x.device)
+    fn = _function("elementwise", "omnia_rmsnorm", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p])
+    _check(fn(_ptr(x), _ptr(weight), _ptr(h), rows, hidden, eps, _code(dtype), _stream()), "rmsnorm")
+    return h
+
+
+def add_rmsnorm(x: torch.Tensor, branch: torch.Tensor, branch_weight: torch.Tensor | None,
+                branch_eps: float | None, out_weight: torch.Tensor | None, out_eps: float | None) -> torch.Tensor | None:
+    """x += norm_b(branch) in place (float32), then h = norm_o(x) in branch's dtype.
+    `branch_eps is None` adds the branch as it is; `out_eps is None` returns no h."""
+    rows, hidden = x.shape
+    h = torch.empty_like(branch) if out_eps is not None else None
+    fn = _function("elementwise", "omnia_add_rmsnorm",
+                   [c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_float, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(x), _ptr(branch), _ptr(branch_weight), branch_eps or 0.0, int(branch_eps is not None),
+              _ptr(out_weight), out_eps or 0.0, int(out_eps is not None), _ptr(h), rows, hidden,
+              _code(branch.dtype), _stream()), "add_rmsnorm")
+    return h
+
+
+def qk_norm_rope_store(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, nq: int, nkv: int, d: int,
+                       eps: float | None, inv_freq: torch.Tensor | None, positions: torch.Tensor,
+                       kv: KVView | None) -> torch.Tensor:
+    """Per head of the projected rows: weightless RMS (q, k), rotation of the first
+    2 * len(inv_freq) dims, q out as [tokens, nq, d], k and v into the cache pages.
+    With `kv` None or not writing, only q is produced."""
+    tokens, stride = proj.shape
+    q = torch.empty(tokens, nq, d, dtype=proj.dtype, device=proj.device)
+    store = kv is not None and kv.writes
+    rot = 0 if inv_freq is None else 2 * inv_freq.shape[0]
+    fn = _function("elementwise", "omnia_qk_norm_rope_store",
+                   [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p,
+                    c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(proj), stride, q_col, k_col, v_col, nq, nkv if store else 0, d, -1.0 if eps is None else eps,
+              _ptr(inv_freq), rot, _ptr(positions), _ptr(kv.slot_mapping) if store else None, _ptr(q),
+              _ptr(kv.pages) if store else None, kv.page_size if store else 1,
+              kv.pages.shape[0] * kv.page_size if store else 0, tokens, _code(proj.dtype),
+              _ptr(error_word(proj.device)), _stream()), "qk_norm_rope_store")
+    return q
+
+
+def paged_attention(q: torch.Tensor, kv: KVView, step: StepContext, scale: float,
+                    gate: torch.Tensor | None = None, gate_col: int = 0) -> torch.Tensor:
+    """Causal (windowed) attention of this step's queries over the paged cache, the
+    output multiplied by sigmoid(gate) when `gate` (the projected rows; the gate's
+    columns start at `gate_col`) is given.  -> [tokens, nq * d]"""
+    tokens, nq, d = q.shape
+    nkv = kv.pages.shape[2]
+    out = torch.empty(tokens, nq * d, dtype=q.dtype, device=q.device)
+    gate_ptr = None if gate is None else gate.data_ptr() + gate_col * gate.element_size()
+    fn = _function("attention_generic", "omnia_paged_attention_generic",
+                   [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                    c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.positions), gate_ptr,
+              0 if gate is None else gate.shape[1], _ptr(out), tokens, step.num_seqs, kv.block_table.shape[1],
+              kv.pages.shape[0], nq, nkv, d, kv.page_size, kv.window or 0, scale, _code(q.dtype),
+              _ptr(error_word(q.device)), _stream()), "paged_attention")
+    return out
+
+
+def swiglu(gu: torch.Tensor) -> torch.Tensor:
+    """act = silu(gu[:, :inner]) * gu[:, inner:]"""
+    rows, two_inner = gu.shape
+    inner = two_inner // 2
+    act = torch.empty(rows, inner, dtype=gu.dtype, device=gu.device)
+    fn = _function("elementwise", "omnia_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(gu), _ptr(act), rows, inner, _code(gu.dtype), _stream()), "swiglu")
+    return act
+
+
+def softcap(z: torch.Tensor, multiplier: float, cap: float | None) -> torch.Tensor:
+    """float32 logits = cap * tanh(z * multiplier / cap); no cap when `cap` is None."""
+    out = torch.empty(z.shape, dtype=torch.float32, device=z.device)
+    fn = _function("elementwise", "omnia_softcap", [c_void_p, c_void_p, c_longlong, c_float, c_float, c_int, c_void_p])
+    _check(fn(_ptr(z), _ptr(out), z.numel(), multiplier, cap or 0.0, _code(z.dtype), _stream()), "softcap")
+    return out
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    """out[r] = src[rows[r]]"""
+    count, width = rows.shape[0], src.shape[1]
+    out = torch.empty(count, width, dtype=src.dtype, device=src.device)
+    fn = _function("elementwise", "omnia_gather_rows", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(src), _ptr(rows), _ptr(out), count, width, _code(src.dtype), _stream()), "gather_rows")
+    return out
+
+
+def linear(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """a [rows, k] times weight [n, k] transposed -> [rows, n], float32 accumulation.
+    The matrix product itself is the vendor library's (as the reference's is MLX's);
+    on the 32-bit path it runs without any reduced-precision mode."""
+    if a.dtype == torch.float32 and (torch.backends.cuda.matmul.allow_tf32
+                                      or torch.get_float32_matmul_precision() != "highest"):
+        raise KernelError("the 32-bit path needs true float32 matrix products; TF32 is switched on")
+    return torch.mm(a, weight.t())
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           min_p: torch.Tensor, seeds: torch.Tensor, draws: torch.Tensor, penalty: torch.Tensor | None = None,
+           history: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row of float32 logits [rows, vocab] (the rows are modified when a
+    repetition penalty applies). Per-row parameters: temperature (0 = greedy), top_k
+    (0 = off), top_p (1 = off), min_p (0 = off), seed and draw index (int64). -> int32 [rows]"""
+    rows, vocab = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    fn = _function("sampling", "omnia_sample",
+                   [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                    c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(logits), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p),
+              _ptr(penalty), _ptr(history), 0 if history is None else history.shape[1], _ptr(seeds), _ptr(draws),
+              _ptr(out), _stream()), "sample")
+    return out

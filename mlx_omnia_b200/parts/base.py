@@ -1,0 +1,233 @@
+"""What a part is, what it may ask of the engine, and the registries parts live in.
+
+A model is put together from parts: a *mixer* (attention and its kin), a
+*feed-forward*, *norms*, a *position encoding*, and a *block* that arranges them
+around the residual stream. A part takes every size and constant as a constructor
+parameter, declares the tensors it wants by local name, and never learns which
+model it is in. Each kind of part has one registry from a name to a class, so a
+layer is data: ``PartSpec("gated_gqa_attention", {...})``.
+
+Interfaces
+----------
+Every part:
+    ``tensors() -> {local_name: TensorSpec}``   what it loads
+    ``load(tensors, runtime)``                  receives exactly those, on the device
+Mixer additionally:
+    ``kv_spec() -> KVSpec | None``              rows it keeps per token, in pages
+    ``state_spec() -> StateSpec | None``        fixed-size state it keeps per request
+    ``forward(h, ctx: LayerContext) -> branch`` h, branch: [tokens, hidden] engine dtype
+FeedForward:  ``forward(h, ctx) -> branch``
+Norm:         ``forward(x) -> h`` and the attributes ``weight``, ``eps`` that the
+              fused residual kernel reads (``weight is None`` means weightless)
+Position:     ``table() -> float32[rotary_dims / 2] | None`` of inverse frequencies
+Block:        ``entry_norm`` and ``forward(x, h, ctx, exit_norm) -> (x, h_next)``
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+import torch
+
+
+@dataclass(frozen=True)
+class TensorSpec:
+    """A tensor a part loads. `kind` decides the dtype it is kept in:
+    ``matrix`` follows the engine's dtype (bfloat16 or float32), ``vector`` is always
+    float32 (norm weights: a stored 32-bit value is never rounded), ``table_i32`` is
+    an integer table kept as int32."""
+
+    shape: tuple[int, ...]
+    kind: str = "matrix"
+
+
+@dataclass(frozen=True)
+class KVSpec:
+    """Per-token rows a mixer keeps in the paged cache: `kv_heads` keys and values of
+    `head_dim` each. `window` is how many of the latest positions can still be read
+    (None: all of them). Layers with equal specs share one group of pages."""
+
+    kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Fixed-size state a mixer keeps per request (one slot per live request)."""
+
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    """A part as data: the registered name of its class and its parameters."""
+
+    kind: str
+    params: dict[str, Any] = field(default_factory=dict)
+
+    def __hash__(self) -> int:  # params may hold tuples only; good enough for caching
+        return hash((self.kind, tuple(sorted((k, repr(v)) for k, v in self.params.items()))))
+
+
+class Part:
+    """Base of every part. Sub-classes take their sizes and constants as parameters."""
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        return {}
+
+    def load(self, tensors: dict[str, torch.Tensor], runtime: "Runtime") -> None:
+        self.runtime = runtime
+
+
+class Mixer(Part):
+    def kv_spec(self) -> KVSpec | None:
+        return None
+
+    def state_spec(self) -> StateSpec | None:
+        return None
+
+    def forward(self, h: torch.Tensor, ctx: "LayerContext") -> torch.Tensor:  # pragma: no cover
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h: torch.Tensor, ctx: "LayerContext") -> torch.Tensor:  # pragma: no cover
+        raise NotImplementedError
+
+
+class Norm(Part):
+    weight: torch.Tensor | None = None
+    eps: float = 0.0
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:  # pragma: no cover
+        raise NotImplementedError
+
+
+class Position(Part):
+    def table(self) -> torch.Tensor | None:  # pragma: no cover
+        raise NotImplementedError
+
+
+class Block(Part):
+    entry_norm: Norm | None = None
+
+    def forward(self, x, h, ctx: "LayerContext", exit_norm: Norm | None):  # pragma: no cover
+        raise NotImplementedError
+
+
+@dataclass
+class Runtime:
+    """Where and in what precision the engine runs. `dtype` is the dtype of matrices,
+    activations and cache pages; reductions are 32-bit in both."""
+
+    dtype: torch.dtype
+    device: torch.device
+
+    @property
+    def exact(self) -> bool:
+        """True on the 32-bit path: no reduced-precision matrix mode anywhere."""
+        return self.dtype == torch.float32
+
+
+class Registry:
+    """One registry per kind of part: name -> class."""
+
+    def __init__(self, what: str) -> None:
+        self.what = what
+        self._classes: dict[str, Callable[..., Part]] = {}
+
+    def register(self, name: str, cls: Callable[..., Part] | None = None):
+        def put(c):
+            if name in self._classes and self._classes[name] is not c:
+                raise ValueError(f"{self.what} {name!r} is already registered")
+            self._classes[name] = c
+            return c
+
+        return put if cls is None else put(cls)
+
+    def build(self, spec: PartSpec) -> Part:
+        try:
+            cls = self._classes[spec.kind]
+        except KeyError:
+            raise KeyError(f"no {self.what} named {spec.kind!r}; known: {sorted(self._classes)}") from None
+        return cls(**spec.params)
+
+    def names(self) -> list[str]:
+        return sorted(self._classes)
+
+
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+NORMS = Registry("norm")
+POSITIONS = Registry("position encoding")
+BLOCKS = Registry("block")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("head")
+
+register_mixer = MIXERS.register
+register_feed_forward = FEED_FORWARDS.register
+register_norm = NORMS.register
+register_position = POSITIONS.register
+register_block = BLOCKS.register
+register_embedding = EMBEDDINGS.register
+register_head = HEADS.register
+
+
+@dataclass
+class KVView:
+    """One cache entry's pages as a mixer sees them in a step.
+
+    pages:        [num_pages, 2, kv_heads, page_size, head_dim]; index 1 of axis 1 is V
+    block_table:  int32 [num_seqs, max_pages]; physical page of each logical page of
+                  each request, -1 where a page was given back (behind a window)
+    slot_mapping: int64 [tokens]; page * page_size + offset where this step's token goes
+    writes:       False when this entry reads another entry's cache
+    """
+
+    pages: torch.Tensor
+    block_table: torch.Tensor
+    slot_mapping: torch.Tensor
+    page_size: int
+    window: int | None
+    writes: bool = True
+
+
+@dataclass
+class StepContext:
+    """The batch of one step: tokens of several requests, flattened.
+
+    Device tensors are int32 unless said otherwise. Host mirrors (`q_lens`,
+    `seq_lens_host`) are for parts that must loop over requests on the host; kernels
+    read the device copies, so a captured graph can be replayed with new values.
+    """
+
+    num_tokens: int
+    num_seqs: int
+    token_ids: torch.Tensor  # [tokens]
+    positions: torch.Tensor  # [tokens] absolute position of each token in its request
+    cu_seqlens: torch.Tensor  # [num_seqs + 1] offsets of each request's tokens in the batch
+    seq_lens: torch.Tensor  # [num_seqs] tokens of the request held after this step
+    state_slots: torch.Tensor  # [num_seqs] slot of per-request state
+    fresh: torch.Tensor  # [num_seqs] 1 where this is the request's first portion
+    logit_rows: torch.Tensor  # [wanted] rows of the batch whose logits are wanted
+    q_lens: list[int]
+    seq_lens_host: list[int]
+    max_q_len: int
+    max_seq_len: int
+    decode_only: bool
+    groups: dict[int, tuple[torch.Tensor, torch.Tensor]]  # group -> (block_table, slot_mapping)
+    workspace: Any = None
+
+
+@dataclass
+class LayerContext:
+    """What one schedule entry's parts see: the batch, this entry's cache pages and
+    this entry's per-request state."""
+
+    step: StepContext
+    kv: KVView | None
+    state: torch.Tensor | None  # [num_slots, *StateSpec.shape]
+    entry: int

@@ -1,0 +1,228 @@
+"""Each CUDA kernel alone against its plain PyTorch reference, at sizes that are not
+the engine's: widths and vocabularies that are no power of two, head sizes in steps
+of 8, odd page sizes, in float32 and in bfloat16."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import kernel_refs
+from mlx_omnia_b200.parts.base import KVView, StepContext
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return 1e-5 if dtype == torch.float32 else 1e-2
+
+
+def close(a, b, dtype, scale=1.0):
+    a, b = a.float(), b.float()
+    bound = tol(dtype) * scale * max(1.0, float(b.abs().max()))
+    assert float((a - b).abs().max()) <= bound, (float((a - b).abs().max()), bound)
+
+
+@pytest.fixture
+def ops():
+    from mlx_omnia_b200.kernels import ops as module
+    return module
+
+
+def rand(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device="cuda") * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,vocab,eps", [(72, 301, 1e-6), (2048, 1000, 1e-5), (100, 50, None)])
+def test_embed_rmsnorm(ops, dtype, hidden, vocab, eps):
+    table = rand(vocab, hidden, dtype=dtype, scale=0.02)
+    ids = torch.randint(0, vocab, (37,), device="cuda", dtype=torch.int32)
+    close(ops.embed_rmsnorm(ids, table, eps), kernel_refs.embed_rmsnorm(ids, table, eps), torch.float32)
+
+
+def test_embed_flags_bad_token(ops):
+    table = rand(10, 16)
+    ids = torch.tensor([3, 11], device="cuda", dtype=torch.int32)
+    ops.embed_rmsnorm(ids, table, 1e-6)
+    with pytest.raises(ops.KernelError, match="token id"):
+        ops.raise_on_error(table.device)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,hidden", [(5, 72), (33, 2048), (3, 5120), (2, 13000)])
+def test_rmsnorm_and_add_rmsnorm(ops, dtype, rows, hidden):
+    x = rand(rows, hidden, scale=3.0, seed=1)
+    w = 1 + rand(hidden, scale=0.1, seed=2)
+    close(ops.rmsnorm(x, w, 1e-5, dtype), kernel_refs.rmsnorm(x, w, 1e-5, dtype), dtype)
+    close(ops.rmsnorm(x, None, 1e-6, dtype), kernel_refs.rmsnorm(x, None, 1e-6, dtype), dtype)
+    branch = rand(rows, hidden, dtype=dtype, scale=0.3, seed=3)
+    wb, wo = 1 + rand(hidden, scale=0.1, seed=4), 1 + rand(hidden, scale=0.1, seed=5)
+    for args in [(wb, 1e-6, wo, 1e-5), (None, None, wo, 1e-5), (wb, 1e-6, None, None), (None, 1e-6, None, 1e-5)]:
+        x1, x2 = x.clone(), x.clone()
+        h1 = ops.add_rmsnorm(x1, branch, *args)
+        h2 = kernel_refs.add_rmsnorm(x2, branch, *args)
+        close(x1, x2, torch.float32)
+        assert (h1 is None) == (h2 is None)
+        if h1 is not None:
+            close(h1, h2, dtype)
+
+
+def make_kv(tokens, nkv, d, page_size, dtype, num_pages, seed=0):
+    """A cache view with one request per row of `tokens` (a list of lengths): random page
+    placement, every other page poisoned with huge values."""
+    g = torch.Generator().manual_seed(seed)
+    pages = torch.full((num_pages, 2, nkv, page_size, d), 1e4, dtype=dtype, device="cuda")
+    order = torch.randperm(num_pages, generator=g).tolist()
+    tables, width = [], max(-(-n // page_size) for n in tokens)
+    for n in tokens:
+        need = -(-n // page_size)
+        tables.append([order.pop() for _ in range(need)] + [-1] * (width - need))
+    return pages, torch.tensor(tables, dtype=torch.int32, device="cuda")
+
+
+def step_of(q_lens, seq_lens):
+    cu = [0]
+    positions = []
+    for q, s in zip(q_lens, seq_lens):
+        cu.append(cu[-1] + q)
+        positions += list(range(s - q, s))
+    dev = lambda v, dt=torch.int32: torch.tensor(v, dtype=dt, device="cuda")
+    return StepContext(num_tokens=cu[-1], num_seqs=len(q_lens), token_ids=dev([0] * cu[-1]), positions=dev(positions),
+                       cu_seqlens=dev(cu), seq_lens=dev(seq_lens), state_slots=dev([0] * len(q_lens)),
+                       fresh=dev([0] * len(q_lens)), logit_rows=dev([]), q_lens=q_lens, seq_lens_host=seq_lens,
+                       max_q_len=max(q_lens), max_seq_len=max(seq_lens), decode_only=all(q == 1 for q in q_lens),
+                       groups={})
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page,rot", [(4, 2, 16, 4, 16), (8, 1, 24, 8, 24), (6, 3, 128, 16, 128),
+                                                (5, 5, 40, 3, 0), (2, 2, 256, 16, 64)])
+def test_qk_norm_rope_store(ops, dtype, nq, nkv, d, page, rot):
+    q_lens, seq_lens = [5, 1, 9], [12, 30, 9]
+    step = step_of(q_lens, seq_lens)
+    pages, table = make_kv(seq_lens, nkv, d, page, dtype, 40)
+    slots = []
+    for s, (q, n) in enumerate(zip(q_lens, seq_lens)):
+        for pos in range(n - q, n):
+            slots.append(int(table[s, pos // page]) * page + pos % page)
+    slots[3] = -1  # a padded token stores nothing
+    width = (2 * nq + 2 * nkv) * d + 8
+    proj = rand(step.num_tokens, width, dtype=dtype, seed=7)
+    inv_freq = None if rot == 0 else (10000.0 ** (-torch.arange(rot // 2, dtype=torch.float64) * 2 / rot)).float().cuda()
+    q_col, k_col, v_col = 0, 2 * nq * d, 2 * nq * d + nkv * d
+    view1 = KVView(pages.clone(), table, torch.tensor(slots, device="cuda"), page, None)
+    view2 = KVView(pages.clone(), table, torch.tensor(slots, device="cuda"), page, None)
+    for eps in (1e-6, None):
+        q1 = ops.qk_norm_rope_store(proj, q_col, k_col, v_col, nq, nkv, d, eps, inv_freq, step.positions, view1)
+        q2 = kernel_refs.qk_norm_rope_store(proj, q_col, k_col, v_col, nq, nkv, d, eps, inv_freq, step.positions, view2)
+        close(q1, q2, dtype)
+        close(view1.pages, view2.pages, dtype, scale=1e-4 if dtype == torch.float32 else 1e-4)
+    ops.raise_on_error(proj.device)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(4, 2, 16, 4, None), (8, 1, 24, 8, 16), (6, 3, 128, 16, None),
+                                                   (5, 5, 40, 3, 7), (2, 1, 256, 16, 33), (16, 8, 64, 16, None)])
+def test_paged_attention(ops, dtype, nq, nkv, d, page, window):
+    q_lens, seq_lens = [7, 1, 40, 1, 2], [7, 61, 75, 1, 130]
+    step = step_of(q_lens, seq_lens)
+    pages, table = make_kv(seq_lens, nkv, d, page, dtype, 140, seed=3)
+    for s, n in enumerate(seq_lens):  # fill the live positions with ordinary values
+        for pos in range(n):
+            p = int(table[s, pos // page])
+            pages[p, :, :, pos % page, :] = rand(2, nkv, d, dtype=dtype, seed=1000 * s + pos)
+    q = rand(step.num_tokens, nq, d, dtype=dtype, seed=11)
+    gate = rand(step.num_tokens, nq * d + 24, dtype=dtype, seed=12)
+    view = KVView(pages, table, torch.zeros(step.num_tokens, dtype=torch.int64, device="cuda"), page, window)
+    scale = 1.3 * d ** -0.5
+    close(ops.paged_attention(q, view, step, scale), kernel_refs.paged_attention(q, view, step, scale), dtype)
+    close(ops.paged_attention(q, view, step, scale, gate=gate, gate_col=24),
+          kernel_refs.paged_attention(q, view, step, scale, gate=gate, gate_col=24), dtype)
+    ops.raise_on_error(q.device)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_finds_a_far_key(ops, dtype):
+    """One key among hundreds matches the query: the output must be its value."""
+    nq, nkv, d, page = 4, 2, 64, 16
+    seq_lens, q_lens = [700], [1]
+    step = step_of(q_lens, seq_lens)
+    pages, table = make_kv(seq_lens, nkv, d, page, dtype, 50, seed=4)
+    for pos in range(700):
+        pages[int(table[0, pos // page]), :, :, pos % page, :] = rand(2, nkv, d, dtype=dtype, scale=0.1, seed=pos)
+    far = 37
+    q = rand(1, nq, d, dtype=dtype, seed=5)
+    p, off = int(table[0, far // page]), far % page
+    for h in range(nkv):
+        pages[p, 0, h, off] = q[0, h * 2] * 8  # both heads of a group share the key; match the first
+        pages[p, 1, h, off] = 5.0
+    view = KVView(pages, table, torch.zeros(1, dtype=torch.int64, device="cuda"), page, None)
+    out = ops.paged_attention(q, view, step, 1.0).float().reshape(nq, d)
+    close(out, kernel_refs.paged_attention(q, view, step, 1.0).float().reshape(nq, d), dtype)
+    assert float(out[0].mean()) > 4.9 and float(out[2].mean()) > 4.9
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu_softcap_gather(ops, dtype):
+    gu = rand(19, 2 * 321, dtype=dtype, scale=3.0)
+    close(ops.swiglu(gu), kernel_refs.swiglu(gu), dtype)
+    z = rand(7, 1001, dtype=dtype, scale=30.0)
+    close(ops.softcap(z, 0.5, 20.0), kernel_refs.softcap(z, 0.5, 20.0), torch.float32, scale=10)
+    close(ops.softcap(z, 2.0, None), kernel_refs.softcap(z, 2.0, None), torch.float32)
+    rows = torch.tensor([6, 0, 3, 3], dtype=torch.int32, device="cuda")
+    assert torch.equal(ops.gather_rows(z, rows), kernel_refs.gather_rows(z, rows))
+
+
+def test_linear_is_true_float32(ops):
+    a, w = rand(33, 517, seed=1), rand(129, 517, seed=2)
+    expect = (a.double() @ w.double().t()).float()
+    close(ops.linear(a, w), expect, torch.float32, scale=3)
+    ab, wb = a.bfloat16(), w.bfloat16()
+    close(ops.linear(ab, wb), (ab.double() @ wb.double().t()).float(), torch.bfloat16, scale=3)
+
+
+def test_sampling(ops):
+    vocab, rows = 1531, 6
+    logits = rand(rows, vocab, scale=2.0, seed=9)
+    logits[1, 77] = logits[1, 1200] = logits[1].max() + 1  # a tie: greedy takes the first
+    dev = lambda v, dt: torch.tensor(v, dtype=dt, device="cuda")
+    temperature = dev([0.0, 0.0, 0.8, 1.0, 1.3, 0.7], torch.float32)
+    top_k = dev([0, 0, 0, 5, 50, 0], torch.int32)
+    top_p = dev([1.0, 1.0, 1.0, 1.0, 0.9, 0.5], torch.float32)
+    min_p = dev([0.0, 0.0, 0.0, 0.0, 0.0, 0.05], torch.float32)
+    seeds = dev([1, 2, 3, 4, 5, 6], torch.int64)
+    for draw in range(4):
+        draws = dev([draw] * rows, torch.int64)
+        got = ops.sample(logits.clone(), temperature, top_k, top_p, min_p, seeds, draws)
+        expect = kernel_refs.sample(logits.clone(), temperature, top_k, top_p, min_p, seeds, draws)
+        assert got.tolist() == expect.tolist(), (draw, got.tolist(), expect.tolist())
+        assert got[1].item() == 77
+    # With a penalty, the recently seen ids are pushed down before anything else.
+    history = dev([[int(logits[0].argmax()), -1, -1]] + [[-1, -1, -1]] * (rows - 1), torch.int32)
+    penalty = dev([100.0] + [1.0] * (rows - 1), torch.float32)
+    draws = dev([0] * rows, torch.int64)
+    got = ops.sample(logits.clone(), temperature, top_k, top_p, min_p, seeds, draws, penalty, history)
+    expect = kernel_refs.sample(logits.clone(), temperature, top_k, top_p, min_p, seeds, draws, penalty, history)
+    assert got.tolist() == expect.tolist() and got[0].item() != int(logits[0].argmax())
+
+
+def test_sampling_keeps_exactly_the_filtered_set(ops):
+    """Many draws never leave the set that top_k/top_p/min_p keep, and reach all of it."""
+    vocab = 300
+    logits = rand(1, vocab, scale=3.0, seed=21)
+    keep = kernel_refs.kept_mask(logits[0].cpu(), 0.9, 12, 0.8, 0.02)
+    dev = lambda v, dt: torch.tensor(v, dtype=dt, device="cuda")
+    seen = set()
+    rows = 256
+    big = logits.expand(rows, vocab).contiguous()
+    for block in range(4):
+        got = ops.sample(big.clone(), dev([0.9] * rows, torch.float32), dev([12] * rows, torch.int32),
+                         dev([0.8] * rows, torch.float32), dev([0.02] * rows, torch.float32),
+                         dev([7] * rows, torch.int64), dev(list(range(block * rows, (block + 1) * rows)), torch.int64))
+        seen |= set(got.tolist())
+    allowed = set(torch.nonzero(keep).flatten().tolist())
+    assert seen <= allowed and len(seen) >= min(len(allowed), 3)
