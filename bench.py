@@ -1,0 +1,254 @@
+"""Decode and prefill throughput of the engine on one B200, as one JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+The default run builds BASELINE.json's configs[2] (28 layers, hidden 2048, 16/8 heads
+of 128, intermediate 6144, vocabulary 151936, tied head) with random bfloat16 weights,
+holds 8 requests whose contexts end at 4096 tokens, and times K decode steps.
+`value` is decoded tokens per second timed on the device; `e2e` is the same measured
+through the Python entry point's generation loop, which copies every step's inputs
+from pinned host memory and reads the chosen tokens back. `prefill` is one step of
+2,048 prompt tokens; `roofline` relates the decode step's time to the bytes it must
+read (every weight once, and the live requests' cache). `points` holds decode at
+batch 1 and 64. Data is synthetic: seeded uniform-random token ids.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CONFIG2 = {
+    "architectures": ["MuseGlimmerForConditionalGeneration"], "model_type": "muse_glimmer",
+    "text_config": {
+        "hidden_size": 2048, "intermediate_size": 6144, "num_hidden_layers": 28, "num_attention_heads": 16,
+        "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 151936, "rms_norm_eps": 1e-6, "post_norm_eps": 1e-6,
+        "sliding_window": 4096, "qk_scale_factor": 1.0, "output_multiplier": 1.0, "final_logit_softcapping": 30.0,
+        "layer_types": ["full_attention"] * 28, "layer_rope_theta": [1000000.0] * 28,
+        "rope_parameters": {"rope_theta": 1000000.0, "rope_type": "default"}, "eos_token_id": [],
+        "tie_word_embeddings": True,
+    },
+}
+SEED = 2
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            data = json.loads(path.read_text())
+            flat = {}
+            for key in FALLBACK_PEAKS:
+                value = data.get(key)
+                if isinstance(value, dict):
+                    value = value.get("value")
+                flat[key] = float(value) if value else FALLBACK_PEAKS[key]
+            return flat, "measured"
+        except (ValueError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.rows: list[list[str]] = []
+        self.process = None
+
+    def __enter__(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.process = None
+        return self
+
+    def _read(self) -> None:
+        for line in self.process.stdout:
+            self.rows.append([cell.strip() for cell in line.split(",")])
+
+    def __exit__(self, *exc) -> None:
+        if self.process is not None:
+            self.process.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        clocks = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
+        peak = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > i + 2 and r[i + 2] == "Active" for r in self.rows)]
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max(peak) if peak else None,
+                "reasons": reasons, "samples": len(clocks)}
+
+
+def model_bytes(text: dict, layers: int) -> tuple[int, int, int]:
+    """(weight bytes a decode step reads, cache bytes per token of context, parameters)."""
+    h, i, d = text["hidden_size"], text["intermediate_size"], text["head_dim"]
+    q, kv = text["num_attention_heads"] * d, text["num_key_value_heads"] * d
+    per_layer = h * (2 * q + 2 * kv) + q * h + 3 * h * i
+    head = text["vocab_size"] * h
+    params = layers * per_layer + head * (1 if text["tie_word_embeddings"] else 2)
+    return 2 * (layers * per_layer + head), 2 * 2 * layers * kv, params
+
+
+def run(args) -> dict:
+    import torch
+
+    from mlx_omnia_b200.engine.engine import Engine, EngineArgs
+    from mlx_omnia_b200.engine.generate import Generator
+    from mlx_omnia_b200.engine.step import StepEntry
+    from mlx_omnia_b200.kernels import ops
+    from mlx_omnia_b200.sampling import GenerationOptions
+
+    raw = json.loads(json.dumps(CONFIG2))
+    text = raw["text_config"]
+    full_layers = text["num_hidden_layers"]
+    layers = args.layers or full_layers
+    text["num_hidden_layers"] = layers
+    text["layer_types"], text["layer_rope_theta"] = text["layer_types"][:layers], text["layer_rope_theta"][:layers]
+    vocab = text["vocab_size"]
+    measured, peak_source = peaks()
+    weight_bytes, kv_per_token, params = model_bytes(text, layers)
+
+    batches = sorted({1, args.batch, 64})
+    cache_tokens = max(batches) * (CONTEXT + 16) + PREFILL_TOKENS
+    engine = Engine.from_random(raw, SEED, EngineArgs(dtype="bfloat16", page_size=16, cache_tokens=cache_tokens,
+                                                      max_requests=max(batches)))
+    g = torch.Generator().manual_seed(SEED)
+
+    def prompts(count: int, length: int) -> list[list[int]]:
+        return torch.randint(0, vocab, (count, length), generator=g).tolist()
+
+    def events():
+        return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def decode(batch: int, steps: int, warmup: int) -> dict:
+        """Fill `batch` requests so that the timed steps end at CONTEXT tokens, then time them."""
+        generator = Generator(engine, max_tokens_per_step=PREFILL_TOKENS)
+        total = warmup + steps
+        options = GenerationOptions(max_tokens=total + 1, stop=())
+        for p in prompts(batch, CONTEXT - total - 1):
+            generator.add(p, options)
+        while any(r.pending > 1 or not r.generated for r in generator.scheduler.running) or generator.scheduler.waiting:
+            generator.step()
+        for _ in range(warmup):
+            generator.step()
+        torch.cuda.synchronize()
+        start, stop = events()
+        launches = ops.launches
+        wall = time.perf_counter()
+        start.record()
+        for _ in range(steps):
+            outputs = generator.step()
+        stop.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - wall
+        ms = start.elapsed_time(stop) / steps
+        assert len(outputs) == batch
+        context = generator.scheduler.running[0].computed if generator.scheduler.running else CONTEXT
+        generator.run()
+        return {"ms": ms, "tokens_per_s": batch * 1000.0 / ms, "wall_tokens_per_s": batch * steps / wall,
+                "launches": (ops.launches - launches) // steps, "context": context}
+
+    def prefill(tokens: int, steps: int, warmup: int) -> dict:
+        times = []
+        for index in range(warmup + steps):
+            request = engine.cache.open(f"prefill-{index}")
+            ids = prompts(1, tokens)[0]
+            torch.cuda.synchronize()
+            start, stop = events()
+            start.record()
+            engine.runner.run([StepEntry(request, ids, [tokens - 1])])
+            stop.record()
+            torch.cuda.synchronize()
+            engine.cache.close(request.request_id)
+            if index >= warmup:
+                times.append(start.elapsed_time(stop))
+        ms = statistics.median(times)
+        h, d, nq = text["hidden_size"], text["head_dim"], text["num_attention_heads"]
+        matmul = 2 * (weight_bytes // 2 - vocab * h) * tokens + 2 * vocab * h  # the head runs on one row
+        attention = layers * 4 * nq * d * tokens * (tokens + 1) // 2
+        flops = matmul + attention
+        return {"value": tokens * 1000.0 / ms, "tokens": tokens, "ms": ms,
+                "frac": flops / (ms / 1000.0) / (measured["bf16_tflops"] * 1e12), "flops": flops}
+
+    with ClockSampler() as sampler:
+        main = decode(args.batch, args.steps, args.warmup)
+    clocks = sampler.summary()
+    side_steps = max(8, min(args.steps, 32))
+    points = {f"decode_b{b}": round(decode(b, side_steps, 3)["tokens_per_s"], 1) for b in (1, 64)}
+    pre = prefill(PREFILL_TOKENS, 5, 3)
+    ops.raise_on_error(engine.runtime.device)
+
+    step_bytes = weight_bytes + args.batch * main["context"] * kv_per_token
+    achieved = step_bytes / (main["ms"] / 1000.0) / 1e9
+    h2d = 4 * (3 * args.batch + (args.batch + 1) + 2 * args.batch) + 8 * args.batch + \
+        4 * args.batch * -(-main["context"] // 16)
+    return {
+        "metric": "decode tok/s at batch 8 (configs[2], context 4096)", "value": round(main["tokens_per_s"], 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(main["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, random weights N(0, 0.02)",
+        "config": {"model": "muse_glimmer configs[2]", "layers": layers, "layers_full": full_layers,
+                   "hidden": text["hidden_size"], "heads": text["num_attention_heads"],
+                   "kv_heads": text["num_key_value_heads"], "head_dim": text["head_dim"],
+                   "intermediate": text["intermediate_size"], "vocab": vocab, "tied": True, "global_batch": args.batch,
+                   "seq_len": CONTEXT, "context_at_timed_steps": main["context"], "page_size": 16,
+                   "params": params, "parallelism": "single-gpu", "l2": "weights (3.7 GB) exceed L2; no flush",
+                   "peaks": peak_source},
+        "clocks": clocks,
+        "e2e": {"value": round(main["wall_tokens_per_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": main["launches"] * args.steps,
+        "prefill": {"value": round(pre["value"], 1), "tokens": pre["tokens"], "ms": round(pre["ms"], 3),
+                    "frac": round(pre["frac"], 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": measured["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / measured["hbm_gbs"], 4)},
+        "points": points,
+    }
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=4)
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=0, help="run fewer layers than configs[2] has (named in config)")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "gabfssilva/mlx-omnia needs Apple's MLX (Metal) and Python >= 3.13; its offline install "
+                          "fails here (no hatchling build backend, no mlx wheel for Linux)"}))
+        return 0
+    if args.gpus != 1:
+        print("bench.py: this engine runs on one GPU; --gpus must be 1")
+        return 2
+    args.warmup = max(args.warmup, 3)
+    print(json.dumps(run(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,178 @@
+"""Generation: the loop that plans a step, runs it, samples and commits; and the
+`load(path)` -> `model.stream(prompt, GenerationOptions(...))` entry point.
+
+The reference's entry point is `load` (src/mlx_omnia/engine/task.py:486-547) returning a
+facade whose `stream(input, options)` yields segments with `.text`
+(src/mlx_omnia/engine/model.py:201-202, src/mlx_omnia/engine/language.py:483-552), over a
+continuous-batching loop of `begin_batch`/`step_batch`
+(src/mlx_omnia/engine/batching.py:223-341,408-437). Here the loop is the scheduler's
+plan -> the step function -> the sampling kernel -> commit, with one device-to-host
+read of the chosen tokens per step.
+"""
+
+from __future__ import annotations
+
+import itertools
+import secrets
+from collections.abc import Iterator, Sequence
+from dataclasses import dataclass
+from pathlib import Path
+
+import torch
+
+from mlx_omnia_b200.engine.engine import DTYPES, Engine, EngineArgs
+from mlx_omnia_b200.engine.scheduler import Request, Scheduler, StepOutput
+from mlx_omnia_b200.engine.step import StepEntry
+from mlx_omnia_b200.kernels import ops
+from mlx_omnia_b200.sampling.batch import sample_rows
+from mlx_omnia_b200.sampling.options import GenerationOptions
+
+
+@dataclass(frozen=True)
+class Segment:
+    """One piece of a streamed answer."""
+
+    text: str
+    token_id: int
+
+
+@dataclass(frozen=True)
+class Text:
+    """A text prompt, as the reference's `Text` input (src/mlx_omnia/engine/language.py:60-79)."""
+
+    prompt: str | Sequence[int]
+
+
+class TokenIdTokenizer:
+    """Stands in when a model folder has no tokenizer: text is token ids in decimal,
+    separated by spaces, both ways."""
+
+    def encode(self, text: str) -> list[int]:
+        try:
+            return [int(piece) for piece in text.replace(",", " ").split()]
+        except ValueError:
+            raise ValueError("this model folder has no tokenizer.json; give the prompt as token ids "
+                             "(integers separated by spaces) or as a list of ints") from None
+
+    def decode(self, ids: Sequence[int]) -> str:
+        return "".join(f"{i} " for i in ids)
+
+
+class Generator:
+    """Continuous batching over one `Engine`."""
+
+    def __init__(self, engine: Engine, *, max_tokens_per_step: int = 2048, max_running: int | None = None) -> None:
+        self.engine = engine
+        self.scheduler = Scheduler(engine.cache, max_tokens_per_step=max_tokens_per_step, max_running=max_running)
+        self._ids = itertools.count()
+        self._seeds: dict[str, int] = {}
+
+    def add(self, prompt: Sequence[int], options: GenerationOptions, request_id: str | None = None) -> Request:
+        prompt = [int(t) for t in prompt]
+        vocab = self.engine.vocab_size
+        if any(not 0 <= t < vocab for t in prompt):
+            raise ValueError(f"a prompt token lies outside the vocabulary of {vocab}")
+        budget = options.max_tokens
+        if options.context_limit is not None:
+            budget = min(budget, options.context_limit - len(prompt))
+        stop = options.stop if options.stop is not None else self.engine.architecture.stop_tokens(self.engine.config)
+        params = options.params()
+        request = Request(request_id or f"req-{next(self._ids)}", prompt, max(budget, 0), params, frozenset(stop))
+        self.scheduler.add(request)
+        self._seeds[request.request_id] = params.seed if params.seed is not None else secrets.randbits(63)
+        return request
+
+    def abort(self, request_id: str) -> None:
+        self.scheduler.abort(request_id)
+        self._seeds.pop(request_id, None)
+
+    def step(self) -> list[StepOutput]:
+        """Plan, run and commit one step; returns what each sampling request produced."""
+        plan = self.scheduler.plan()
+        if not plan.entries:
+            return []
+        entries = []
+        for planned in plan.entries:
+            tokens = planned.request.tokens[planned.start: planned.start + planned.count]
+            entries.append(StepEntry(planned.request.cache, tokens, [planned.count - 1] if planned.samples else []))
+        try:
+            logits = self.engine.runner.run(entries)
+        except Exception:
+            for planned in plan.entries:  # a failed step fails its requests and frees what they hold
+                self.scheduler._finish(planned.request, "abort")
+            raise
+        sampling = [p.request for p in plan.entries if p.samples]
+        sampled: dict[str, int] = {}
+        if sampling:
+            chosen = sample_rows(logits, [r.sampling for r in sampling], [self._seeds[r.request_id] for r in sampling],
+                                 [len(r.generated) for r in sampling],
+                                 [r.tokens[-r.sampling.penalty_context:] for r in sampling])
+            sampled = dict(zip((r.request_id for r in sampling), chosen.tolist()))
+        outputs = self.scheduler.commit(plan, sampled)
+        for output in outputs:
+            if output.finished:
+                self._seeds.pop(output.request.request_id, None)
+        return outputs
+
+    def run(self) -> None:
+        """Step until every request has finished."""
+        while not self.scheduler.idle:
+            if not self.step() and not self.scheduler.running and self.scheduler.waiting:
+                raise RuntimeError("the scheduler can admit nothing: the cache pool is too small")
+
+    def generate(self, prompts: Sequence[Sequence[int]], options: GenerationOptions) -> list[list[int]]:
+        """Generate for all prompts together; returns the generated ids per prompt."""
+        requests = [self.add(p, options) for p in prompts]
+        self.run()
+        ops.raise_on_error(self.engine.runtime.device)
+        return [r.generated for r in requests]
+
+
+class LanguageModel:
+    """What `load` returns: a model that streams text (or token ids)."""
+
+    def __init__(self, engine: Engine, tokenizer=None, **generator_args) -> None:
+        self.engine = engine
+        self.tokenizer = tokenizer or TokenIdTokenizer()
+        self.generator = Generator(engine, **generator_args)
+
+    def _ids(self, prompt) -> list[int]:
+        if isinstance(prompt, Text):
+            prompt = prompt.prompt
+        return self.tokenizer.encode(prompt) if isinstance(prompt, str) else [int(t) for t in prompt]
+
+    def stream(self, input, options: GenerationOptions) -> Iterator[Segment]:
+        """Generate for one prompt, yielding each token as it is chosen."""
+        request = self.generator.add(self._ids(input), options)
+        try:
+            while request.status != "finished":
+                for output in self.generator.step():
+                    if output.request is request and output.token is not None:
+                        yield Segment(self.tokenizer.decode([output.token]), output.token)
+        finally:
+            if request.status != "finished":
+                self.generator.abort(request.request_id)
+
+    def generate(self, inputs: Sequence, options: GenerationOptions) -> list[list[int]]:
+        """Generate for several prompts in one continuous batch; ids per prompt."""
+        return self.generator.generate([self._ids(p) for p in inputs], options)
+
+
+def load(model: str | Path, *, dtype=None, quantize=None, page_size: int = 16, cache_tokens: int = 32768,
+         max_requests: int = 64, max_tokens_per_step: int = 2048, device: str = "cuda:0") -> LanguageModel:
+    """Load a model folder (config.json + safetensors).
+
+    dtype: None or "bfloat16" keeps the checkpoint's bfloat16; "float32" runs everything
+    in true 32-bit. `quantize` exists in the reference's signature; this engine has no
+    quantised path and refuses it. The remaining arguments size the engine: tokens per
+    cache page, tokens the page pool holds, live requests, tokens per step."""
+    if quantize is not None:
+        raise ValueError("quantised weights are not part of this engine")
+    if isinstance(dtype, torch.dtype):
+        dtype = {v: k for k, v in DTYPES.items()}[dtype]
+    folder = Path(model)
+    if not (folder / "config.json").exists():
+        raise ValueError(f"{folder} is not a model folder (no config.json); hub downloads are not part of this engine")
+    engine = Engine.from_folder(folder, EngineArgs(dtype=dtype or "bfloat16", page_size=page_size,
+                                                   cache_tokens=cache_tokens, max_requests=max_requests, device=device))
+    return LanguageModel(engine, max_tokens_per_step=max_tokens_per_step)

@@ -51,7 +51,13 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+launches = 0
+"""How many of this package's own kernels have been launched by this process."""
+
+
 def _check(code: int, what: str) -> None:
+    global launches
+    launches += 1
     if code != 0:
         raise KernelError(f"{what}: CUDA error {code} at launch (bad sizes for this kernel, or an earlier fault)")
 

@@ -1,0 +1,87 @@
+"""Generation through the entry point on the GPU: greedy ids equal the plain
+implementation's, in 32-bit and bfloat16; sampled ids can be redrawn on the host from
+the plain implementation's logits with the same random stream; long decoding and the
+first tokens of a sequence; the command line."""
+
+from __future__ import annotations
+
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import kernel_refs
+import plain_impl
+import tiny_configs
+from mlx_omnia_b200 import GenerationOptions, load, sampler, temperature, top_k, top_p
+from trace_tools import ROOT, write_folder
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name,dtype,page", [("A", "float32", 4), ("B", "float32", 8), ("A", "bfloat16", 4),
+                                             ("B", "bfloat16", 8)])
+def test_greedy_through_the_entry_point(tmp_path, name, dtype, page):
+    raw, weights = write_folder(tmp_path / "m", name)
+    vocab = raw["text_config"]["vocab_size"]
+    lengths = (5, 9, 13) if name == "A" else (3, 17, 31, 40)
+    prompts = [tiny_configs.prompt(n, vocab, 40 + n) for n in lengths]
+    model = load(tmp_path / "m", dtype=dtype, page_size=page, cache_tokens=512, max_requests=4,
+                 max_tokens_per_step=8)
+    got = model.generate(prompts, GenerationOptions(max_tokens=8, stop=()))
+    if dtype == "float32":
+        assert got == [plain_impl.greedy_generate(raw, weights, p, 8) for p in prompts]
+    else:
+        # In bfloat16 a near-tie may break the other way; every chosen token must be (nearly) the
+        # plain implementation's best given the same history.
+        for prompt, ids in zip(prompts, got):
+            logits = plain_impl.forward(raw, weights, prompt + ids)[len(prompt) - 1: -1]
+            chosen = logits[torch.arange(len(ids)), torch.tensor(ids)]
+            assert float((logits.max(dim=-1).values - chosen).max()) < 0.03 * float(logits.abs().max())
+    streamed = [s.token_id for s in model.stream(prompts[0], GenerationOptions(max_tokens=8, stop=()))]
+    assert streamed == got[0]
+    assert not model.engine.cache.requests
+
+
+def test_sampled_ids_can_be_redrawn_on_the_host(tmp_path):
+    raw, weights = write_folder(tmp_path / "m", "B")
+    model = load(tmp_path / "m", dtype="float32", page_size=8, cache_tokens=512, max_requests=4, max_tokens_per_step=8)
+    prompts = [tiny_configs.prompt(n, 1000, 70 + n) for n in (3, 17, 31, 40)]
+    chosen = sampler(temperature(0.8), top_k(50), top_p(0.95), seed=1234)
+    got = model.generate(prompts, GenerationOptions(max_tokens=6, sampler=chosen, stop=()))
+    for prompt, ids in zip(prompts, got):
+        for draw, token in enumerate(ids):
+            logits = plain_impl.forward(raw, weights, prompt + ids[:draw])[-1]
+            keep = kernel_refs.kept_mask(logits, 0.8, 50, 0.95, 0.0)
+            scores = {t: float(logits[t]) / 0.8 + kernel_refs.gumbel(1234, draw, t)
+                      for t in torch.nonzero(keep).flatten().tolist()}
+            assert token in scores and scores[token] >= max(scores.values()) - 1e-3
+    again = model.generate(prompts, GenerationOptions(max_tokens=6, sampler=chosen, stop=()))
+    assert again == got
+
+
+def test_long_decoding_and_first_tokens(tmp_path):
+    """300 tokens decoded one by one from a two-token prompt stay on the plain
+    implementation's logits, across many pages and past the window of B's sliding layers."""
+    raw, weights = write_folder(tmp_path / "m", "B")
+    model = load(tmp_path / "m", dtype="float32", page_size=8, cache_tokens=1024, max_requests=2)
+    prompt = tiny_configs.prompt(2, 1000, 5)
+    ids = model.generate([prompt], GenerationOptions(max_tokens=300, stop=()))[0]
+    expect = plain_impl.forward(raw, weights, prompt + ids)
+    assert ids == expect[1:-1].argmax(dim=-1).tolist()
+
+
+def test_command_line(tmp_path):
+    raw, weights = write_folder(tmp_path / "m", "A")
+    prompt = tiny_configs.prompt(7, 512, 3)
+    done = subprocess.run([sys.executable, str(ROOT / "bin" / "omnia"), "run", "-m", str(tmp_path / "m"),
+                           "--max-tokens", "5", "--temperature", "0", "--dtype", "float32", *map(str, prompt)],
+                          capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0, done.stderr[-2000:]
+    expect = plain_impl.greedy_generate(raw, weights, prompt, 5)
+    cut = expect.index(0) if 0 in expect else len(expect)  # token 0 is this configuration's eos
+    assert done.stdout.split() == [str(t) for t in expect[:cut]]
+    empty = subprocess.run([sys.executable, str(ROOT / "bin" / "omnia"), "run", "-m", str(tmp_path / "m")],
+                           capture_output=True, text=True, stdin=subprocess.DEVNULL, timeout=120)
+    assert empty.returncode == 2 and "nothing to say" in empty.stderr

@@ -1,0 +1,241 @@
+"""Each part alone against the plain implementation's function for it, and the
+generality of the composition: a schedule that names a layer twice or lets a layer
+read another's cache, and a toy mixer with state of its own that is registered, built
+and stepped from this file without touching the framework."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import plain_impl
+import tiny_configs
+from mlx_omnia_b200.cache import CacheManager
+from mlx_omnia_b200.engine.engine import Engine, EngineArgs
+from mlx_omnia_b200.engine.step import StepEntry, StepRunner
+from mlx_omnia_b200.parts import (DecoderModel, LayerSpec, ModelSpec, PartSpec, Runtime, ScheduleEntry, StateSpec,
+                                  register_mixer)
+from mlx_omnia_b200.parts.base import FEED_FORWARDS, HEADS, EMBEDDINGS, MIXERS, NORMS, POSITIONS, Mixer, TensorSpec
+from mlx_omnia_b200.architectures.muse_glimmer import model_spec, parse
+
+pytestmark = pytest.mark.gpu
+CUDA = torch.device("cuda:0")
+
+
+def runtime(dtype=torch.float32):
+    return Runtime(dtype, CUDA)
+
+
+def test_norm_part():
+    x = torch.randn(7, 96, device=CUDA)
+    w = torch.randn(96, device=CUDA) * 0.1
+    for convention, expect_w in [("plain", w), ("centred", w + 1), ("none", None)]:
+        norm = NORMS.build(PartSpec("rms_norm", {"size": 96, "eps": 1e-5, "weight": convention}))
+        assert set(norm.tensors()) == (set() if convention == "none" else {"weight"})
+        norm.load({"weight": w} if convention != "none" else {}, runtime())
+        assert plain_impl.relative_diff(norm.forward(x), plain_impl.rms_norm(x, expect_w, 1e-5)) < 1e-5
+
+
+def test_position_part():
+    rotary = POSITIONS.build(PartSpec("rotary", {"dims": 24, "theta": 1e6}))
+    rotary.load({}, runtime())
+    expect = 1e6 ** (-torch.arange(12, dtype=torch.float64) * 2 / 24)
+    assert torch.allclose(rotary.table().cpu().double(), expect, rtol=1e-7)
+    none = POSITIONS.build(PartSpec("none"))
+    none.load({}, runtime())
+    assert none.table() is None
+
+
+def test_feed_forward_part():
+    ff = FEED_FORWARDS.build(PartSpec("gated_mlp", {"hidden": 96, "inner": 320}))
+    w = {"gate_proj.weight": torch.randn(320, 96, device=CUDA) * 0.1, "up_proj.weight": torch.randn(320, 96, device=CUDA) * 0.1,
+         "down_proj.weight": torch.randn(96, 320, device=CUDA) * 0.1}
+    assert {k: v.shape for k, v in ff.tensors().items()} == {k: tuple(v.shape) for k, v in w.items()}
+    ff.load(w, runtime())
+    h = torch.randn(11, 96, device=CUDA)
+    assert plain_impl.relative_diff(ff.forward(h, None), plain_impl.swiglu(h, w)) < 1e-5
+
+
+def test_embedding_and_head_parts():
+    table = torch.randn(301, 72, device=CUDA)
+    embedding = EMBEDDINGS.build(PartSpec("token_embedding", {"vocab": 301, "hidden": 72, "norm_eps": 1e-6}))
+    embedding.load({"weight": table}, runtime())
+    ids = torch.randint(0, 301, (9,), device=CUDA, dtype=torch.int32)
+    assert plain_impl.relative_diff(embedding.forward(ids), plain_impl.embed(ids.long(), table, 1e-6)) < 1e-6
+    for tied in (True, False):
+        head = HEADS.build(PartSpec("lm_head", {"vocab": 301, "hidden": 72, "tied": tied, "multiplier": 0.5, "softcap": 20.0}))
+        lm = torch.randn(301, 72, device=CUDA)
+        head.load({} if tied else {"weight": lm}, runtime())
+        head.bind(table)
+        n = torch.randn(4, 72, device=CUDA) * 3
+        assert plain_impl.relative_diff(head.forward(n), plain_impl.head(n, table if tied else lm, 0.5, 20.0)) < 1e-5
+
+
+def single_layer_engine(name, layer, schedule=None, dtype="float32"):
+    raw, weights = tiny_configs.config(name), tiny_configs.tensors(name)
+    engine = Engine.from_tensors(raw, weights, EngineArgs(dtype=dtype, page_size=4, cache_tokens=256, max_requests=2))
+    return engine, raw, weights
+
+
+@pytest.mark.parametrize("name,layer", [("A", 0), ("B", 0), ("B", 1)])
+def test_attention_mixer_and_block_alone(name, layer):
+    """One block of the loaded model, stepped in two portions, against the plain block."""
+    engine, raw, weights = single_layer_engine(name, layer)
+    cfg = raw["text_config"]
+    block = engine.model.blocks[layer]
+    tokens = 29
+    x = torch.randn(tokens, cfg["hidden_size"], device=CUDA)
+    named = {plain_impl.trunk_name(k): v.to(CUDA) for k, v in weights.items()}
+    w = plain_impl.sub(named, f"layers.{layer}.")
+    expect_x, _ = plain_impl.block(x.clone(), torch.arange(tokens, device=CUDA), w, cfg, cfg["layer_types"][layer],
+                                   cfg["layer_rope_theta"][layer])
+    request = engine.cache.open("r")
+    got = []
+    for lo, hi in ((0, 18), (18, 29)):
+        step = engine.runner.build_context([StepEntry(request, [0] * (hi - lo), [])])
+        ctx = engine.runner.layer_contexts(step)[layer]
+        part = x[lo:hi].clone()
+        h = block.entry_norm.forward(part)
+        out, _ = block.forward(part, h, ctx, None)
+        got.append(out)
+        engine.cache.release_behind_window(request)
+    assert plain_impl.relative_diff(torch.cat(got), expect_x) < 2e-5
+
+
+def spec_with_schedule(raw, schedule):
+    base = model_spec(parse(raw))
+    return ModelSpec(base.embedding, base.layers, tuple(ScheduleEntry(*s) for s in schedule), base.final_norm, base.head)
+
+
+@pytest.mark.parametrize("schedule", [[(0, None), (1, None), (0, None)], [(0, None), (1, 0)],
+                                      [(1, None), (0, None), (1, 1), (0, None)]])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_schedule_is_data(schedule, dtype):
+    """A layer may run twice (each run with a cache of its own) and a layer may read the
+    cache of an earlier entry; the plain implementation takes the same list."""
+    raw, weights = tiny_configs.config("A"), tiny_configs.tensors("A")
+    rt = runtime(dtype)
+    model = DecoderModel(spec_with_schedule(raw, schedule))
+    named = {}
+    for k, v in weights.items():
+        name = "model." + plain_impl.trunk_name(k) if not k.startswith("lm_head") else k
+        kind = model.tensors()[name].kind
+        named[name] = v.to(CUDA).to(torch.float32 if kind == "vector" else dtype)
+    model.load(named, rt)
+    cache = CacheManager(model.cache_needs(), page_size=4, pages_per_group=40, max_requests=2, dtype=dtype, device=CUDA)
+    assert len(cache.groups[0].entries) == sum(1 for _, reads in schedule if reads is None)
+    runner = StepRunner(model, cache, rt)
+    ids = tiny_configs.prompt(33, 512, 8)
+    request = cache.open("r")
+    got = torch.cat([runner.run([StepEntry(request, ids[:20], list(range(20)))]),
+                     runner.run([StepEntry(request, ids[20:31], list(range(11)))]),
+                     runner.run([StepEntry(request, ids[31:32], [0])]), runner.run([StepEntry(request, ids[32:], [0])])])
+    expect = plain_impl.forward(raw, weights, ids, schedule=schedule)
+    assert plain_impl.relative_diff(got, expect) < (1e-4 if dtype == torch.float32 else 3e-2)
+
+
+# ---- a toy mixer with state of its own, defined here --------------------------------------
+
+
+@register_mixer("toy_decay_mixer")
+class ToyDecayMixer(Mixer):
+    """s_t = decay * s_{t-1} + h_t W_in ; out_t = s_t W_out. Its state is one vector per
+    request, kept in a state slot between steps; it keeps no pages."""
+
+    def __init__(self, hidden: int, width: int, decay: float) -> None:
+        self.hidden, self.width, self.decay = hidden, width, decay
+
+    def state_spec(self):
+        return StateSpec((self.width,), torch.float32)
+
+    def tensors(self):
+        return {"in_proj.weight": TensorSpec((self.width, self.hidden)), "out_proj.weight": TensorSpec((self.hidden, self.width))}
+
+    def load(self, tensors, runtime):
+        super().load(tensors, runtime)
+        self.w_in, self.w_out = tensors["in_proj.weight"], tensors["out_proj.weight"]
+
+    def forward(self, h, ctx):
+        u = (h.float() @ self.w_in.float().t())
+        out = torch.empty_like(u)
+        slots = ctx.step.state_slots.tolist()
+        start = 0
+        for slot, count in zip(slots, ctx.step.q_lens):
+            state = ctx.state[slot]
+            for t in range(start, start + count):
+                state = self.decay * state + u[t]
+                out[t] = state
+            ctx.state[slot] = state
+            start += count
+        return (out @ self.w_out.float().t()).to(h.dtype)
+
+
+def toy_spec(hidden=32, vocab=50):
+    norm = PartSpec("rms_norm", {"size": hidden, "eps": 1e-6, "weight": "plain"})
+    ff = PartSpec("gated_mlp", {"hidden": hidden, "inner": 48})
+    toy = PartSpec("pre_norm", {"mixer": PartSpec("toy_decay_mixer", {"hidden": hidden, "width": 24, "decay": 0.9}),
+                                "feed_forward": ff, "norms": {"input_layernorm": norm, "post_attention_layernorm": norm},
+                                "mixer_name": "mixer"})
+    attention = PartSpec("pre_norm", {"mixer": PartSpec("gqa_attention", {
+        "hidden": hidden, "heads": 2, "kv_heads": 1, "head_dim": 16, "scale": 0.25,
+        "position": PartSpec("rotary", {"dims": 8, "theta": 100.0})}), "feed_forward": ff,
+        "norms": {"input_layernorm": norm, "post_attention_layernorm": norm}})
+    return ModelSpec(PartSpec("token_embedding", {"vocab": vocab, "hidden": hidden}),
+                     (LayerSpec(toy, "layers.0"), LayerSpec(attention, "layers.1")),
+                     (ScheduleEntry(0), ScheduleEntry(1)), norm, PartSpec("lm_head", {"vocab": vocab, "hidden": hidden}),
+                     embedding_prefix="embed", final_norm_prefix="final_norm", head_prefix="head")
+
+
+def toy_plain(w, ids):
+    """The toy model, whole sequence, plain PyTorch."""
+    x = w["embed.weight"][ids]
+    rms = lambda v, name: plain_impl.rms_norm(v, w[name], 1e-6)
+    h = rms(x, "layers.0.input_layernorm.weight")
+    u = h @ w["layers.0.mixer.in_proj.weight"].t()
+    state, rows = torch.zeros(24), []
+    for t in range(len(ids)):
+        state = 0.9 * state + u[t]
+        rows.append(state)
+    x = x + torch.stack(rows) @ w["layers.0.mixer.out_proj.weight"].t()
+    x = x + plain_impl.swiglu(rms(x, "layers.0.post_attention_layernorm.weight"), plain_impl.sub(w, "layers.0.mlp."))
+    h = rms(x, "layers.1.input_layernorm.weight")
+    positions = torch.arange(len(ids))
+    a = plain_impl.sub(w, "layers.1.self_attn.")
+    q = (h @ a["q_proj.weight"].t()).reshape(-1, 2, 16)
+    k = (h @ a["k_proj.weight"].t()).reshape(-1, 1, 16)
+    v = (h @ a["v_proj.weight"].t()).reshape(-1, 1, 16)
+    rot = lambda z: torch.cat([plain_impl.rope(z[..., :8], positions, 100.0), z[..., 8:]], dim=-1)
+    att = plain_impl.attention_core(rot(q), rot(k), v, plain_impl.visible(positions, positions, None), 0.25)
+    x = x + att @ a["o_proj.weight"].t()
+    x = x + plain_impl.swiglu(rms(x, "layers.1.post_attention_layernorm.weight"), plain_impl.sub(w, "layers.1.mlp."))
+    return rms(x, "final_norm.weight") @ w["head.weight"].t()
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped():
+    spec = toy_spec()
+    model = DecoderModel(spec)
+    g = torch.Generator().manual_seed(4)
+    w = {name: (torch.randn(*s.shape, generator=g) * (0.2 if s.kind == "matrix" else 0.1) + (s.kind == "vector"))
+         for name, s in model.tensors().items()}
+    rt = runtime()
+    model.load({k: v.to(CUDA) for k, v in w.items()}, rt)
+    needs = model.cache_needs()
+    assert needs[0].kv is None and needs[0].state == StateSpec((24,)) and needs[1].kv is not None
+    cache = CacheManager(needs, page_size=4, pages_per_group=24, max_requests=2, dtype=torch.float32, device=CUDA)
+    runner = StepRunner(model, cache, rt)
+    a, b = tiny_configs.prompt(21, 50, 1), tiny_configs.prompt(14, 50, 2)
+    ra, rb = cache.open("a"), cache.open("b")
+    got_a = [runner.run([StepEntry(ra, a[:9], list(range(9)))])]
+    mixed = runner.run([StepEntry(ra, a[9:10], [0]), StepEntry(rb, b[:8], list(range(8)))])
+    got_a.append(mixed[:1])
+    got_b = [mixed[1:]]
+    mixed = runner.run([StepEntry(rb, b[8:], list(range(6))), StepEntry(ra, a[10:], list(range(11)))])
+    got_b.append(mixed[:6])
+    got_a.append(mixed[6:])
+    assert plain_impl.relative_diff(torch.cat(got_a), toy_plain(w, a)) < 2e-5
+    assert plain_impl.relative_diff(torch.cat(got_b), toy_plain(w, b)) < 2e-5
+    # a slot that is reused starts from zero state again
+    cache.close("a")
+    rc = cache.open("c")
+    again = runner.run([StepEntry(rc, a, list(range(21)))])
+    assert plain_impl.relative_diff(again, toy_plain(w, a)) < 2e-5
