@@ -144,13 +144,14 @@ def run(args) -> dict:
 
     def decode(batch: int, steps: int, warmup: int) -> dict:
         """Fill `batch` requests so that the timed steps end at CONTEXT tokens, then time them."""
-        generator = Generator(engine, max_tokens_per_step=PREFILL_TOKENS)
         total = warmup + steps
+        length = CONTEXT - total - 1
+        # One step reads all prompts whole, so every request decodes in lockstep afterwards.
+        generator = Generator(engine, max_tokens_per_step=batch * length)
         options = GenerationOptions(max_tokens=total + 1, stop=())
-        for p in prompts(batch, CONTEXT - total - 1):
+        for p in prompts(batch, length):
             generator.add(p, options)
-        while any(r.pending > 1 or not r.generated for r in generator.scheduler.running) or generator.scheduler.waiting:
-            generator.step()
+        assert len(generator.step()) == batch
         for _ in range(warmup):
             generator.step()
         torch.cuda.synchronize()

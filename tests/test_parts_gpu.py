@@ -85,9 +85,9 @@ def test_attention_mixer_and_block_alone(name, layer):
     block = engine.model.blocks[layer]
     tokens = 29
     x = torch.randn(tokens, cfg["hidden_size"], device=CUDA)
-    named = {plain_impl.trunk_name(k): v.to(CUDA) for k, v in weights.items()}
+    named = {plain_impl.trunk_name(k): v for k, v in weights.items()}
     w = plain_impl.sub(named, f"layers.{layer}.")
-    expect_x, _ = plain_impl.block(x.clone(), torch.arange(tokens, device=CUDA), w, cfg, cfg["layer_types"][layer],
+    expect_x, _ = plain_impl.block(x.cpu(), torch.arange(tokens), w, cfg, cfg["layer_types"][layer],
                                    cfg["layer_rope_theta"][layer])
     request = engine.cache.open("r")
     got = []
@@ -99,7 +99,7 @@ def test_attention_mixer_and_block_alone(name, layer):
         out, _ = block.forward(part, h, ctx, None)
         got.append(out)
         engine.cache.release_behind_window(request)
-    assert plain_impl.relative_diff(torch.cat(got), expect_x) < 2e-5
+    assert plain_impl.relative_diff(torch.cat(got).cpu(), expect_x) < 2e-5
 
 
 def spec_with_schedule(raw, schedule):
