@@ -1,0 +1,525 @@
+// Paged causal attention in bfloat16 on the tensor cores (mma.sync m16n8k16, float32
+// accumulation and softmax), compiled for one head size and one group size:
+//   -DHEAD_DIM=d   (a multiple of 8, at most 256; rows are zero-padded to a multiple of 16)
+//   -DGROUP=g      (query heads per key/value head, at most 16)
+//
+// Rows of a tile are (token, query head of the group) pairs of ONE key/value head, so a
+// key/value tile fetched from the cache serves the whole group. Two kernels share the
+// tile arithmetic:
+//   prefill:  a block of 4 warps owns 64 rows (64 / g tokens of one request) and walks
+//             the visible keys in tiles of 64, double-buffered with cp.async; it writes
+//             the final output (optionally times sigmoid(gate)).
+//   decode:   one warp per block owns the g rows of one single-token request and one
+//             fixed chunk of DECODE_CHUNK keys (chunks are aligned to absolute key
+//             positions, so the partition never depends on the batch); it writes an
+//             unnormalised partial (max, sum, accumulator) to scratch memory, and the
+//             combine kernel merges a token's chunks in ascending order.
+// Keys and values are addressed row by row through the block table, so any page size
+// works. Rows outside the visible range are zero-filled in shared memory (never read
+// from the cache), which keeps stale or poisoned pages out of the arithmetic.
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 128
+#endif
+#ifndef GROUP
+#define GROUP 2
+#endif
+
+namespace {
+
+constexpr int D = HEAD_DIM;
+constexpr int DP = (D + 15) / 16 * 16;   // padded head size
+constexpr int ROW = DP + 8;              // shared-memory row stride (elements): odd in 16-byte units
+constexpr int CH = D / 8;                // 16-byte chunks of a stored row
+constexpr int CHP = DP / 8;              // 16-byte chunks of a padded row
+constexpr int KSTEPS = DP / 16;
+constexpr int NT_O = DP / 8;             // output n-tiles
+constexpr int BM = 64;                   // rows per prefill block
+constexpr int BN = 64;                   // keys per prefill tile
+constexpr int TOKENS_PER_BLOCK = BM / GROUP;
+constexpr int DECODE_BN = 32;            // keys per decode tile
+constexpr int DECODE_STAGES = 3;
+constexpr float LOG2E = 1.4426950408889634f;
+
+static_assert(D % 8 == 0 && D <= 256, "head size must be a multiple of 8, at most 256");
+static_assert(GROUP >= 1 && GROUP <= 16, "group size must be 1..16");
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3,
+                                            const bf16* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2,
+                                                  unsigned& r3, const bf16* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+struct CacheRef {
+  const bf16* pages;   // [num_pages, 2, nkv, page_size, D]
+  const int* table;    // this request's block-table row
+  int num_pages, nkv, kvh, page_size;
+};
+
+// The address of key (which = 0) or value (which = 1) row `pos`; null when its page is bad.
+__device__ __forceinline__ const bf16* cache_row(const CacheRef& c, int pos, int which, int* err) {
+  const int page = c.table[pos / c.page_size];
+  if (page < 0 || page >= c.num_pages) {
+    atomicOr(err, OMNIA_ERR_PAGE);
+    return nullptr;
+  }
+  return c.pages + ((((size_t)page * 2 + which) * c.nkv + c.kvh) * c.page_size + pos % c.page_size) * D;
+}
+
+// One tile of the online softmax for the 16 rows of a warp.
+//   qf:      the warp's query fragments (KSTEPS x 4 registers)
+//   ks, vs:  shared-memory tiles [NKEYS][ROW]
+//   key0:    absolute position of the tile's first key
+//   row_lo/row_hi[2]: visible key range of the warp's rows g and g + 8 (inclusive; lo > hi: none)
+template <int NKEYS>
+__device__ __forceinline__ void attend_tile(const unsigned (*qf)[4], const bf16* ks, const bf16* vs,
+                                            int key0, const int* row_lo, const int* row_hi,
+                                            float sl2, float* m, float* l, float (*o)[4]) {
+  const int lane = threadIdx.x & 31;
+  const int t = lane & 3;
+  constexpr int NT = NKEYS / 8;
+  float s[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+  for (int kstep = 0; kstep < KSTEPS; ++kstep) {
+#pragma unroll
+    for (int j2 = 0; j2 < NT / 2; ++j2) {
+      unsigned b0, b1, b2, b3;
+      const int mat = lane >> 3;
+      ldmatrix_x4(b0, b1, b2, b3,
+                  ks + (j2 * 16 + (mat >> 1) * 8 + (lane & 7)) * ROW + kstep * 16 + (mat & 1) * 8);
+      mma_bf16(s[2 * j2], qf[kstep], b0, b1);
+      mma_bf16(s[2 * j2 + 1], qf[kstep], b2, b3);
+    }
+  }
+  // Mask, then the running maximum of rows g (elements 0,1) and g + 8 (elements 2,3).
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int key = key0 + 8 * j + 2 * t + (e & 1);
+      const int r = e >> 1;
+      if (key < row_lo[r] || key > row_hi[r]) s[j][e] = -INFINITY;
+      mx[r] = fmaxf(mx[r], s[j][e]);
+    }
+  }
+  float alpha[2], base[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    const float m_new = fmaxf(m[r], mx[r]);
+    base[r] = m_new == -INFINITY ? 0.f : m_new * sl2;
+    alpha[r] = m[r] == -INFINITY ? 0.f : exp2f(m[r] * sl2 - base[r]);
+    m[r] = m_new;
+    l[r] *= alpha[r];
+  }
+#pragma unroll
+  for (int j = 0; j < NT_O; ++j) {
+    o[j][0] *= alpha[0];
+    o[j][1] *= alpha[0];
+    o[j][2] *= alpha[1];
+    o[j][3] *= alpha[1];
+  }
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float p = exp2f(s[j][e] * sl2 - base[e >> 1]);  // exp2(-inf) = 0 for masked keys
+      s[j][e] = p;
+      l[e >> 1] += p;
+    }
+  }
+#pragma unroll
+  for (int kk = 0; kk < NKEYS / 16; ++kk) {
+    unsigned a[4];
+    a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+    for (int j2 = 0; j2 < NT_O / 2; ++j2) {
+      unsigned b0, b1, b2, b3;
+      const int mat = lane >> 3;
+      ldmatrix_x4_trans(b0, b1, b2, b3,
+                        vs + (kk * 16 + (mat & 1) * 8 + (lane & 7)) * ROW + j2 * 16 + (mat >> 1) * 8);
+      mma_bf16(o[2 * j2], a, b0, b1);
+      mma_bf16(o[2 * j2 + 1], a, b2, b3);
+    }
+  }
+}
+
+// Load the warp's 16 query rows as A fragments. qs: [16 or more rows][ROW].
+__device__ __forceinline__ void load_q_fragments(const bf16* qs, unsigned (*qf)[4]) {
+  const int lane = threadIdx.x & 31, mat = lane >> 3;
+#pragma unroll
+  for (int kstep = 0; kstep < KSTEPS; ++kstep)
+    ldmatrix_x4(qf[kstep][0], qf[kstep][1], qf[kstep][2], qf[kstep][3],
+                qs + ((mat & 1) * 8 + (lane & 7)) * ROW + kstep * 16 + (mat >> 1) * 8);
+}
+
+// Zero the padding chunks (dims D..DP-1) of `rows` shared-memory rows.
+__device__ __forceinline__ void zero_padding(bf16* tile, int rows, int tid, int threads) {
+  if constexpr (CHP != CH) {
+    constexpr int PAD = CHP - CH;
+    for (int i = tid; i < rows * PAD; i += threads) {
+      const int r = i / PAD, c = CH + i % PAD;
+      *reinterpret_cast<uint4*>(tile + r * ROW + c * 8) = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+// Prefill: grid (blocks of the work list, nkv); 128 threads.
+__global__ void __launch_bounds__(128)
+attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages,
+                         const int* __restrict__ block_table, const int* __restrict__ cu_seqlens,
+                         const int* __restrict__ seq_lens, const int* __restrict__ work,
+                         const bf16* __restrict__ gate, int gate_stride, bf16* __restrict__ out,
+                         int max_pages, int num_pages, int nq, int nkv, int page_size, int window,
+                         float scale, int* err) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [BM][ROW]
+  bf16* kv = qs + BM * ROW;                       // 2 stages x (K [BN][ROW], V [BN][ROW])
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int seq = work[2 * blockIdx.x], tok0 = work[2 * blockIdx.x + 1];
+  const int kvh = blockIdx.y;
+  const int q_begin = cu_seqlens[seq], q_len = cu_seqlens[seq + 1] - q_begin;
+  const int pos0 = seq_lens[seq] - q_len + tok0;  // position of the block's first token
+  const int tokens = min(TOKENS_PER_BLOCK, q_len - tok0);
+  const int rows = tokens * GROUP;
+  CacheRef cache{pages, block_table + (size_t)seq * max_pages, num_pages, nkv, kvh, page_size};
+
+  // Query rows: row r = (token r / GROUP, head kvh * GROUP + r % GROUP).
+  for (int i = tid; i < BM * CHP; i += 128) {
+    const int r = i / CHP, c = i % CHP;
+    const bool valid = r < rows && c < CH;
+    const bf16* src = q + ((size_t)(q_begin + tok0 + r / GROUP) * nq + kvh * GROUP + r % GROUP) * D + c * 8;
+    cp_async16(qs + r * ROW + c * 8, valid ? src : q, valid);
+  }
+  cp_async_commit();
+  for (int stage = 0; stage < 2; ++stage) {
+    zero_padding(kv + stage * 2 * BN * ROW, 2 * BN, tid, 128);
+  }
+
+  const int last = pos0 + tokens - 1;                                    // last key any row sees
+  const int first = window > 0 ? max(0, pos0 - window + 1) : 0;          // first key any row sees
+  const int tile0 = first / BN, tiles = last / BN - tile0 + 1;
+
+  auto load_tile = [&](int tile, int stage) {
+    bf16* kt = kv + stage * 2 * BN * ROW;
+    bf16* vt = kt + BN * ROW;
+    const int key = tid >> 1, sub = tid & 1;
+    const int pos = (tile0 + tile) * BN + key;
+    const bool visible = pos >= first && pos <= last;
+    const bf16* kp = visible ? cache_row(cache, pos, 0, err) : nullptr;
+    const bf16* vp = kp ? kp + (size_t)nkv * page_size * D : nullptr;
+#pragma unroll
+    for (int c = sub; c < CH; c += 2) {
+      cp_async16(kt + key * ROW + c * 8, kp ? kp + c * 8 : pages, kp != nullptr);
+      cp_async16(vt + key * ROW + c * 8, vp ? vp + c * 8 : pages, kp != nullptr);
+    }
+  };
+
+  load_tile(0, 0);
+  cp_async_commit();
+
+  unsigned qf[KSTEPS][4];
+  float o[NT_O][4];
+#pragma unroll
+  for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  // Visible key range of this lane's two rows.
+  int row_lo[2], row_hi[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = warp * 16 + (lane >> 2) + 8 * r;
+    const int pos = pos0 + row / GROUP;
+    row_hi[r] = row < rows ? pos : -1;
+    row_lo[r] = row < rows ? (window > 0 ? max(0, pos - window + 1) : 0) : 0;
+  }
+  const float sl2 = scale * LOG2E;
+
+  for (int tile = 0; tile < tiles; ++tile) {
+    if (tile + 1 < tiles) load_tile(tile + 1, (tile + 1) & 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (tile == 0) load_q_fragments(qs + warp * 16 * ROW, qf);
+    const bf16* kt = kv + (tile & 1) * 2 * BN * ROW;
+    // A warp whose rows see nothing of this tile skips it (rows are ordered by position).
+    const int key0 = (tile0 + tile) * BN;
+    const int warp_last = pos0 + min(rows - 1, warp * 16 + 15) / GROUP;
+    if (warp * 16 < rows && key0 <= warp_last)
+      attend_tile<BN>(qf, kt, kt + BN * ROW, key0, row_lo, row_hi, sl2, m, l, o);
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+
+  // Normalise, gate, store.
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+  const int t = lane & 3;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = warp * 16 + (lane >> 2) + 8 * r;
+    if (row >= rows) continue;
+    const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+    const size_t token = (size_t)(q_begin + tok0 + row / GROUP);
+    const int head = kvh * GROUP + row % GROUP;
+    bf16* dst = out + (token * nq + head) * D;
+    const bf16* gp = gate ? gate + token * gate_stride + (size_t)head * D : nullptr;
+#pragma unroll
+    for (int j = 0; j < NT_O; ++j) {
+      const int dim = 8 * j + 2 * t;
+      if (dim >= D) continue;
+      float v0 = o[j][2 * r] * inv, v1 = o[j][2 * r + 1] * inv;
+      if (gp) {
+        v0 *= 1.f / (1.f + expf(-__bfloat162float(gp[dim])));
+        v1 *= 1.f / (1.f + expf(-__bfloat162float(gp[dim + 1])));
+      }
+      *reinterpret_cast<__nv_bfloat162*>(dst + dim) = __floats2bfloat162_rn(v0, v1);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Decode: grid (chunks, nkv, requests); 32 threads. Request s is the single-token
+// request seq_ids[s] (or s when seq_ids is null). Partials:
+//   part_o  [tokens, nq, max_chunks, D] float32 (unnormalised), part_ml [tokens, nq, max_chunks, 2]
+__global__ void __launch_bounds__(32)
+attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages,
+                        const int* __restrict__ block_table, const int* __restrict__ cu_seqlens,
+                        const int* __restrict__ seq_lens, const int* __restrict__ seq_ids,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int chunk_keys,
+                        int max_chunks, int max_pages, int num_pages, int nq, int nkv, int page_size,
+                        int window, float scale, int* err) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);  // [16][ROW]
+  bf16* kv = qs + 16 * ROW;                      // DECODE_STAGES x (K [32][ROW], V [32][ROW])
+  const int lane = threadIdx.x;
+  const int seq = seq_ids ? seq_ids[blockIdx.z] : blockIdx.z;
+  const int kvh = blockIdx.y, chunk = blockIdx.x;
+  const int pos = seq_lens[seq] - 1;
+  if (pos < 0) return;
+  const int first = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = max(first, chunk * chunk_keys), hi = min(pos, (chunk + 1) * chunk_keys - 1);
+  if (lo > hi) return;
+  const size_t token = (size_t)cu_seqlens[seq];
+  CacheRef cache{pages, block_table + (size_t)seq * max_pages, num_pages, nkv, kvh, page_size};
+
+  for (int i = lane; i < 16 * CHP; i += 32) {
+    const int r = i / CHP, c = i % CHP;
+    const bool valid = r < GROUP && c < CH;
+    cp_async16(qs + r * ROW + c * 8, valid ? q + (token * nq + kvh * GROUP + r) * D + c * 8 : q, valid);
+  }
+  cp_async_commit();
+  for (int stage = 0; stage < DECODE_STAGES; ++stage)
+    zero_padding(kv + stage * 2 * DECODE_BN * ROW, 2 * DECODE_BN, lane, 32);
+
+  const int tile0 = lo / DECODE_BN, tiles = hi / DECODE_BN - tile0 + 1;
+  auto load_tile = [&](int tile, int stage) {
+    bf16* kt = kv + stage * 2 * DECODE_BN * ROW;
+    bf16* vt = kt + DECODE_BN * ROW;
+    const int p = (tile0 + tile) * DECODE_BN + lane;
+    const bool visible = p >= lo && p <= hi;
+    const bf16* kp = visible ? cache_row(cache, p, 0, err) : nullptr;
+    const bf16* vp = kp ? kp + (size_t)nkv * page_size * D : nullptr;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      cp_async16(kt + lane * ROW + c * 8, kp ? kp + c * 8 : pages, kp != nullptr);
+      cp_async16(vt + lane * ROW + c * 8, vp ? vp + c * 8 : pages, kp != nullptr);
+    }
+  };
+#pragma unroll
+  for (int s = 0; s < DECODE_STAGES - 1; ++s) {
+    if (s < tiles) load_tile(s, s);
+    cp_async_commit();
+  }
+
+  unsigned qf[KSTEPS][4];
+  float o[NT_O][4];
+#pragma unroll
+  for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  int row_lo[2], row_hi[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = (lane >> 2) + 8 * r;
+    row_lo[r] = lo;
+    row_hi[r] = row < GROUP ? hi : -1;
+  }
+  const float sl2 = scale * LOG2E;
+
+  for (int tile = 0; tile < tiles; ++tile) {
+    const int ahead = tile + DECODE_STAGES - 1;
+    if (ahead < tiles) load_tile(ahead, ahead % DECODE_STAGES);
+    cp_async_commit();
+    cp_async_wait<DECODE_STAGES - 1>();
+    __syncwarp();
+    if (tile == 0) load_q_fragments(qs, qf);
+    const bf16* kt = kv + (tile % DECODE_STAGES) * 2 * DECODE_BN * ROW;
+    attend_tile<DECODE_BN>(qf, kt, kt + DECODE_BN * ROW, (tile0 + tile) * DECODE_BN, row_lo, row_hi,
+                           sl2, m, l, o);
+    __syncwarp();
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+  const int t = lane & 3;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = (lane >> 2) + 8 * r;
+    if (row >= GROUP) continue;
+    const size_t slot = ((token * nq + kvh * GROUP + row) * max_chunks + chunk);
+    float* dst = part_o + slot * D;
+#pragma unroll
+    for (int j = 0; j < NT_O; ++j) {
+      const int dim = 8 * j + 2 * t;
+      if (dim >= D) continue;
+      *reinterpret_cast<float2*>(dst + dim) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
+    }
+    if (t == 0) {
+      part_ml[slot * 2] = m[r] * sl2;  // the maximum in the exponent's units (log2)
+      part_ml[slot * 2 + 1] = l[r];
+    }
+  }
+}
+
+// Merge the chunks of each (request, head), ascending, then gate and round.
+// grid (requests, nq); D threads or fewer (each thread strides over dims).
+__global__ void attention_combine_kernel(const float* __restrict__ part_o,
+                                         const float* __restrict__ part_ml,
+                                         const int* __restrict__ cu_seqlens,
+                                         const int* __restrict__ seq_lens,
+                                         const int* __restrict__ seq_ids,
+                                         const bf16* __restrict__ gate, int gate_stride,
+                                         bf16* __restrict__ out, int chunk_keys, int max_chunks,
+                                         int nq, int window) {
+  const int seq = seq_ids ? seq_ids[blockIdx.x] : blockIdx.x;
+  const int head = blockIdx.y;
+  const int pos = seq_lens[seq] - 1;
+  if (pos < 0) return;
+  const size_t token = (size_t)cu_seqlens[seq];
+  const int first = window > 0 ? max(0, pos - window + 1) : 0;
+  const int c0 = first / chunk_keys, c1 = pos / chunk_keys;
+  const size_t base = (token * nq + head) * max_chunks;
+  float mx = -INFINITY;
+  for (int c = c0; c <= c1; ++c) mx = fmaxf(mx, part_ml[(base + c) * 2]);
+  float total = 0.f;
+  for (int c = c0; c <= c1; ++c) total += part_ml[(base + c) * 2 + 1] * exp2f(part_ml[(base + c) * 2] - mx);
+  const float inv = total > 0.f ? 1.f / total : 0.f;
+  for (int dim = threadIdx.x; dim < D; dim += blockDim.x) {
+    float acc = 0.f;
+    for (int c = c0; c <= c1; ++c)
+      acc += part_o[(base + c) * D + dim] * exp2f(part_ml[(base + c) * 2] - mx);
+    float v = acc * inv;
+    if (gate) v *= 1.f / (1.f + expf(-__bfloat162float(gate[token * gate_stride + (size_t)head * D + dim])));
+    out[(token * nq + head) * D + dim] = __float2bfloat16_rn(v);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+
+extern "C" int omnia_attention_tc_info(int* head_dim, int* group, int* tokens_per_block) {
+  *head_dim = HEAD_DIM;
+  *group = GROUP;
+  *tokens_per_block = TOKENS_PER_BLOCK;
+  return 0;
+}
+
+extern "C" int omnia_attention_prefill_tc(const void* q, const void* pages, const int* block_table,
+                                          const int* cu_seqlens, const int* seq_lens,
+                                          const int* work, int blocks, const void* gate,
+                                          int gate_stride, void* out, int max_pages, int num_pages,
+                                          int nq, int nkv, int page_size, int window, float scale,
+                                          int* err, cudaStream_t stream) {
+  if (blocks == 0) return 0;
+  if (nq != nkv * GROUP) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)(BM + 4 * BN) * ROW * sizeof(bf16);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  attention_prefill_kernel<<<dim3(blocks, nkv), 128, smem, stream>>>(
+      (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, work, (const bf16*)gate,
+      gate_stride, (bf16*)out, max_pages, num_pages, nq, nkv, page_size, window, scale, err);
+  return OMNIA_LAUNCH_RESULT();
+}
+
+extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const int* block_table,
+                                         const int* cu_seqlens, const int* seq_lens,
+                                         const int* seq_ids, int requests, float* part_o,
+                                         float* part_ml, int chunk_keys, int max_chunks,
+                                         const void* gate, int gate_stride, void* out,
+                                         int max_pages, int num_pages, int nq, int nkv,
+                                         int page_size, int window, float scale, int* err,
+                                         cudaStream_t stream) {
+  if (requests == 0) return 0;
+  if (nq != nkv * GROUP || chunk_keys % DECODE_BN != 0 || max_chunks < 1) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)(16 + DECODE_STAGES * 2 * DECODE_BN) * ROW * sizeof(bf16);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  attention_decode_kernel<<<dim3(max_chunks, nkv, requests), 32, smem, stream>>>(
+      (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
+      chunk_keys, max_chunks, max_pages, num_pages, nq, nkv, page_size, window, scale, err);
+  int code = OMNIA_LAUNCH_RESULT();
+  if (code) return code;
+  attention_combine_kernel<<<dim3(requests, nq), D < 128 ? D : 128, 0, stream>>>(
+      part_o, part_ml, cu_seqlens, seq_lens, seq_ids, (const bf16*)gate, gate_stride, (bf16*)out,
+      chunk_keys, max_chunks, nq, window);
+  return OMNIA_LAUNCH_RESULT();
+}

@@ -151,22 +151,87 @@ def qk_norm_rope_store(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, n
     return q
 
 
+DECODE_CHUNK = 128
+"""Keys per split of the decode attention kernel (chunks are aligned to absolute positions)."""
+
+_scratch: dict[tuple[int, str], torch.Tensor] = {}
+
+
+def scratch(device: torch.device, name: str, numel: int, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """A reusable buffer of at least `numel` elements (contents undefined)."""
+    key = (device.index or 0, name)
+    held = _scratch.get(key)
+    if held is None or held.numel() < numel or held.dtype != dtype:
+        held = _scratch[key] = torch.empty(max(numel, 1), dtype=dtype, device=device)
+    return held
+
+
+def tiled_attention_supported(dtype: torch.dtype, nq: int, nkv: int, d: int) -> bool:
+    """The tensor-core kernels take bfloat16, head sizes in steps of 8 up to 256 and up to
+    16 query heads per key/value head; everything else runs on the generic kernel."""
+    return dtype == torch.bfloat16 and d % 8 == 0 and d <= 256 and nq % nkv == 0 and nq // nkv <= 16
+
+
+def _prefill_work(step: StepContext, tokens_per_block: int, device: torch.device) -> torch.Tensor:
+    """(request, first token) of every block of `tokens_per_block` query tokens; built once
+    per step and shared by all layers."""
+    if step.workspace is None:
+        step.workspace = {}
+    key = ("prefill_work", tokens_per_block)
+    work = step.workspace.get(key)
+    if work is None:
+        items = [(s, t0) for s, n in enumerate(step.q_lens) for t0 in range(0, n, tokens_per_block)]
+        work = torch.tensor(items, dtype=torch.int32).pin_memory().to(device, non_blocking=True)
+        step.workspace[key] = work
+    return work
+
+
 def paged_attention(q: torch.Tensor, kv: KVView, step: StepContext, scale: float,
                     gate: torch.Tensor | None = None, gate_col: int = 0) -> torch.Tensor:
     """Causal (windowed) attention of this step's queries over the paged cache, the
     output multiplied by sigmoid(gate) when `gate` (the projected rows; the gate's
-    columns start at `gate_col`) is given.  -> [tokens, nq * d]"""
+    columns start at `gate_col`) is given.  -> [tokens, nq * d]
+
+    bfloat16 with a supported head size runs on the tensor-core kernels: the split-key
+    decode kernel when every request brings one token, the tiled prefill kernel
+    otherwise. Other cases (the 32-bit path among them) run on the generic kernel."""
     tokens, nq, d = q.shape
     nkv = kv.pages.shape[2]
     out = torch.empty(tokens, nq * d, dtype=q.dtype, device=q.device)
     gate_ptr = None if gate is None else gate.data_ptr() + gate_col * gate.element_size()
-    fn = _function("attention_generic", "omnia_paged_attention_generic",
-                   [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-                    c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
-    _check(fn(_ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.positions), gate_ptr,
-              0 if gate is None else gate.shape[1], _ptr(out), tokens, step.num_seqs, kv.block_table.shape[1],
-              kv.pages.shape[0], nq, nkv, d, kv.page_size, kv.window or 0, scale, _code(q.dtype),
-              _ptr(error_word(q.device)), _stream()), "paged_attention")
+    gate_stride = 0 if gate is None else gate.shape[1]
+    err = _ptr(error_word(q.device))
+    max_pages, num_pages = kv.block_table.shape[1], kv.pages.shape[0]
+    if not tiled_attention_supported(q.dtype, nq, nkv, d):
+        fn = _function("attention_generic", "omnia_paged_attention_generic",
+                       [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+        _check(fn(_ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.positions),
+                  gate_ptr, gate_stride, _ptr(out), tokens, step.num_seqs, max_pages, num_pages, nq, nkv, d,
+                  kv.page_size, kv.window or 0, scale, _code(q.dtype), err, _stream()), "paged_attention")
+        return out
+    defines = {"HEAD_DIM": d, "GROUP": nq // nkv}
+    if step.decode_only:
+        max_chunks = -(-step.max_seq_len // DECODE_CHUNK)
+        part_o = scratch(q.device, "attention_part_o", tokens * nq * max_chunks * d)
+        part_ml = scratch(q.device, "attention_part_ml", tokens * nq * max_chunks * 2)
+        fn = _function("attention_tc", "omnia_attention_decode_tc",
+                       [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                        c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                        c_void_p], defines)
+        _check(fn(_ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.seq_lens), None,
+                  step.num_seqs, _ptr(part_o), _ptr(part_ml), DECODE_CHUNK, max_chunks, gate_ptr, gate_stride,
+                  _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size, kv.window or 0, scale, err, _stream()),
+               "attention_decode")
+        return out
+    tokens_per_block = 64 // (nq // nkv)
+    work = _prefill_work(step, tokens_per_block, q.device)
+    fn = _function("attention_tc", "omnia_attention_prefill_tc",
+                   [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                    c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p], defines)
+    _check(fn(_ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.seq_lens), _ptr(work),
+              work.shape[0], gate_ptr, gate_stride, _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size,
+              kv.window or 0, scale, err, _stream()), "attention_prefill")
     return out
 
 

@@ -264,8 +264,8 @@ def greedy_generate(config, weights, prompt, steps, *, dtype=torch.float32) -> l
 
 def relative_diff(a: torch.Tensor, b: torch.Tensor) -> float:
     """``max|a - b| / max|b|`` in 64-bit.  tests/conftest.py:49-59 of the reference."""
-    a = a.double()
-    b = b.double()
+    a = a.detach().cpu().double()
+    b = b.detach().cpu().double()
     return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
 
 

@@ -146,6 +146,31 @@ def test_paged_attention(ops, dtype, nq, nkv, d, page, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(4, 2, 16, 4, None), (8, 1, 24, 8, 16), (6, 3, 128, 16, None),
+                                                   (6, 3, 128, 16, 200), (5, 5, 40, 3, 130), (16, 8, 64, 16, None),
+                                                   (10, 2, 96, 16, None)])
+def test_paged_attention_decode_only(ops, dtype, nq, nkv, d, page, window):
+    """Every request brings one token: the split-key kernel, at lengths around its chunk
+    and tile edges."""
+    seq_lens = [1, 31, 32, 33, 127, 128, 129, 257, 700]
+    q_lens = [1] * len(seq_lens)
+    step = step_of(q_lens, seq_lens)
+    pages, table = make_kv(seq_lens, nkv, d, page, dtype, 1 + sum(-(-n // page) for n in seq_lens), seed=6)
+    for s, n in enumerate(seq_lens):
+        for first in range(0, n, page):
+            p = int(table[s, first // page])
+            count = min(page, n - first)
+            pages[p, :, :, :count, :] = rand(2, nkv, count, d, dtype=dtype, seed=100 * s + first)
+    q = rand(step.num_tokens, nq, d, dtype=dtype, seed=13)
+    gate = rand(step.num_tokens, nq * d, dtype=dtype, seed=14)
+    view = KVView(pages, table, torch.zeros(step.num_tokens, dtype=torch.int64, device="cuda"), page, window)
+    scale = 0.9 * d ** -0.5
+    close(ops.paged_attention(q, view, step, scale, gate=gate), kernel_refs.paged_attention(q, view, step, scale, gate=gate),
+          dtype)
+    ops.raise_on_error(q.device)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_paged_attention_finds_a_far_key(ops, dtype):
     """One key among hundreds matches the query: the output must be its value."""
     nq, nkv, d, page = 4, 2, 64, 16
