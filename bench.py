@@ -130,8 +130,8 @@ def run(args) -> dict:
     measured, peak_source = peaks()
     weight_bytes, kv_per_token, params = model_bytes(text, layers)
 
-    batches = sorted({1, args.batch, 64})
-    cache_tokens = max(batches) * (CONTEXT + 16) + PREFILL_TOKENS
+    batches = sorted({1, args.batch, 64}) if args.only == "all" else [args.batch]
+    cache_tokens = max(batches) * (args.context + 16) + max(PREFILL_TOKENS, args.prefill_tokens)
     engine = Engine.from_random(raw, SEED, EngineArgs(dtype="bfloat16", page_size=16, cache_tokens=cache_tokens,
                                                       max_requests=max(batches)))
     g = torch.Generator().manual_seed(SEED)
@@ -145,7 +145,7 @@ def run(args) -> dict:
     def decode(batch: int, steps: int, warmup: int) -> dict:
         """Fill `batch` requests so that the timed steps end at CONTEXT tokens, then time them."""
         total = warmup + steps
-        length = CONTEXT - total - 1
+        length = args.context - total - 1
         # One step reads all prompts whole, so every request decodes in lockstep afterwards.
         generator = Generator(engine, max_tokens_per_step=batch * length)
         options = GenerationOptions(max_tokens=total + 1, stop=())
@@ -193,6 +193,14 @@ def run(args) -> dict:
         return {"value": tokens * 1000.0 / ms, "tokens": tokens, "ms": ms,
                 "frac": flops / (ms / 1000.0) / (measured["bf16_tflops"] * 1e12), "flops": flops}
 
+    if args.only == "decode":  # a small case for profilers: one batch size, no prefill timing
+        part = decode(args.batch, args.steps, args.warmup)
+        return {"only": "decode", "batch": args.batch, "layers": layers, "ms_per_step": round(part["ms"], 4),
+                "tokens_per_s": round(part["tokens_per_s"], 1), "context": part["context"]}
+    if args.only == "prefill":
+        part = prefill(args.prefill_tokens, args.steps, args.warmup)
+        return {"only": "prefill", "layers": layers, "tokens": args.prefill_tokens, "ms": round(part["ms"], 3),
+                "frac": round(part["frac"], 4)}
     with ClockSampler() as sampler:
         main = decode(args.batch, args.steps, args.warmup)
     clocks = sampler.summary()
@@ -214,7 +222,7 @@ def run(args) -> dict:
                    "hidden": text["hidden_size"], "heads": text["num_attention_heads"],
                    "kv_heads": text["num_key_value_heads"], "head_dim": text["head_dim"],
                    "intermediate": text["intermediate_size"], "vocab": vocab, "tied": True, "global_batch": args.batch,
-                   "seq_len": CONTEXT, "context_at_timed_steps": main["context"], "page_size": 16,
+                   "seq_len": args.context, "context_at_timed_steps": main["context"], "page_size": 16,
                    "params": params, "parallelism": "single-gpu", "l2": "weights (3.7 GB) exceed L2; no flush",
                    "peaks": peak_source},
         "clocks": clocks,
@@ -237,6 +245,10 @@ def main() -> int:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="run fewer layers than configs[2] has (named in config)")
+    parser.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
+                        help="time one part only (small cases for profilers); prints a short record")
+    parser.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds at the last timed step")
+    parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -246,7 +258,8 @@ def main() -> int:
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
         return 2
-    args.warmup = max(args.warmup, 3)
+    if args.only == "all":
+        args.warmup = max(args.warmup, 3)
     print(json.dumps(run(args)))
     return 0
 

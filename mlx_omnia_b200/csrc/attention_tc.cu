@@ -40,6 +40,7 @@ constexpr int BN = 64;                   // keys per prefill tile
 constexpr int TOKENS_PER_BLOCK = BM / GROUP;
 constexpr int DECODE_BN = 32;            // keys per decode tile
 constexpr int DECODE_STAGES = 3;
+constexpr int DECODE_TABLE = 64;         // block-table entries a decode block stages in shared memory
 constexpr float LOG2E = 1.4426950408889634f;
 
 static_assert(D % 8 == 0 && D <= 256, "head size must be a multiple of 8, at most 256");
@@ -86,18 +87,19 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 
 struct CacheRef {
   const bf16* pages;   // [num_pages, 2, nkv, page_size, D]
-  const int* table;    // this request's block-table row
-  int num_pages, nkv, kvh, page_size;
+  const int* table;    // block-table entries, entry 0 being logical page `first_page`
+  int first_page, num_pages, nkv, kvh, page_size;
 };
 
 // The address of key (which = 0) or value (which = 1) row `pos`; null when its page is bad.
 __device__ __forceinline__ const bf16* cache_row(const CacheRef& c, int pos, int which, int* err) {
-  const int page = c.table[pos / c.page_size];
+  const int logical = pos / c.page_size;
+  const int page = c.table[logical - c.first_page];
   if (page < 0 || page >= c.num_pages) {
     atomicOr(err, OMNIA_ERR_PAGE);
     return nullptr;
   }
-  return c.pages + ((((size_t)page * 2 + which) * c.nkv + c.kvh) * c.page_size + pos % c.page_size) * D;
+  return c.pages + ((((size_t)page * 2 + which) * c.nkv + c.kvh) * c.page_size + (pos - logical * c.page_size)) * D;
 }
 
 // One tile of the online softmax for the 16 rows of a warp.
@@ -196,8 +198,8 @@ __device__ __forceinline__ void load_q_fragments(const bf16* qs, unsigned (*qf)[
 
 // Zero the padding chunks (dims D..DP-1) of `rows` shared-memory rows.
 __device__ __forceinline__ void zero_padding(bf16* tile, int rows, int tid, int threads) {
-  if constexpr (CHP != CH) {
-    constexpr int PAD = CHP - CH;
+  if (CHP != CH) {
+    constexpr int PAD = CHP != CH ? CHP - CH : 1;
     for (int i = tid; i < rows * PAD; i += threads) {
       const int r = i / PAD, c = CH + i % PAD;
       *reinterpret_cast<uint4*>(tile + r * ROW + c * 8) = make_uint4(0, 0, 0, 0);
@@ -226,7 +228,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pa
   const int pos0 = seq_lens[seq] - q_len + tok0;  // position of the block's first token
   const int tokens = min(TOKENS_PER_BLOCK, q_len - tok0);
   const int rows = tokens * GROUP;
-  CacheRef cache{pages, block_table + (size_t)seq * max_pages, num_pages, nkv, kvh, page_size};
+  CacheRef cache{pages, block_table + (size_t)seq * max_pages, 0, num_pages, nkv, kvh, page_size};
 
   // Query rows: row r = (token r / GROUP, head kvh * GROUP + r % GROUP).
   for (int i = tid; i < BM * CHP; i += 128) {
@@ -347,7 +349,16 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
   const int lo = max(first, chunk * chunk_keys), hi = min(pos, (chunk + 1) * chunk_keys - 1);
   if (lo > hi) return;
   const size_t token = (size_t)cu_seqlens[seq];
-  CacheRef cache{pages, block_table + (size_t)seq * max_pages, num_pages, nkv, kvh, page_size};
+  // The chunk's block-table entries are read once, up front: a tile's loads then never wait
+  // for a table lookup. (Chunks of more than DECODE_TABLE pages read the table directly.)
+  __shared__ int table_s[DECODE_TABLE];
+  const int page_lo = lo / page_size, page_hi = hi / page_size;
+  const int* table_row = block_table + (size_t)seq * max_pages;
+  const bool staged = page_hi - page_lo < DECODE_TABLE;
+  if (staged)
+    for (int i = lane; i <= page_hi - page_lo; i += 32) table_s[i] = table_row[page_lo + i];
+  CacheRef cache{pages, staged ? table_s : table_row, staged ? page_lo : 0, num_pages, nkv, kvh, page_size};
+  __syncwarp();
 
   for (int i = lane; i < 16 * CHP; i += 32) {
     const int r = i / CHP, c = i % CHP;
@@ -431,34 +442,60 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
   }
 }
 
-// Merge the chunks of each (request, head), ascending, then gate and round.
-// grid (requests, nq); D threads or fewer (each thread strides over dims).
-__global__ void attention_combine_kernel(const float* __restrict__ part_o,
-                                         const float* __restrict__ part_ml,
-                                         const int* __restrict__ cu_seqlens,
-                                         const int* __restrict__ seq_lens,
-                                         const int* __restrict__ seq_ids,
-                                         const bf16* __restrict__ gate, int gate_stride,
-                                         bf16* __restrict__ out, int chunk_keys, int max_chunks,
-                                         int nq, int window) {
+// Merge the chunks of each (request, head), ascending, then gate and round. One warp per
+// (request, head): lanes hold the chunks' weights (32 chunks per round, rescaled online
+// across rounds), then every lane accumulates its own dims over the chunks.
+// grid (requests, ceil(nq / 4)); 128 threads.
+__global__ void __launch_bounds__(128)
+attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                         const int* __restrict__ cu_seqlens, const int* __restrict__ seq_lens,
+                         const int* __restrict__ seq_ids, const bf16* __restrict__ gate,
+                         int gate_stride, bf16* __restrict__ out, int chunk_keys, int max_chunks,
+                         int nq, int window) {
   const int seq = seq_ids ? seq_ids[blockIdx.x] : blockIdx.x;
-  const int head = blockIdx.y;
+  const int lane = threadIdx.x & 31;
+  const int head = blockIdx.y * 4 + (threadIdx.x >> 5);
+  if (head >= nq) return;
   const int pos = seq_lens[seq] - 1;
   if (pos < 0) return;
   const size_t token = (size_t)cu_seqlens[seq];
   const int first = window > 0 ? max(0, pos - window + 1) : 0;
   const int c0 = first / chunk_keys, c1 = pos / chunk_keys;
   const size_t base = (token * nq + head) * max_chunks;
-  float mx = -INFINITY;
-  for (int c = c0; c <= c1; ++c) mx = fmaxf(mx, part_ml[(base + c) * 2]);
-  float total = 0.f;
-  for (int c = c0; c <= c1; ++c) total += part_ml[(base + c) * 2 + 1] * exp2f(part_ml[(base + c) * 2] - mx);
+  constexpr int PER_LANE = (D + 31) / 32;
+  float acc[PER_LANE];
+#pragma unroll
+  for (int k = 0; k < PER_LANE; ++k) acc[k] = 0.f;
+  float mx = -INFINITY, total = 0.f;
+  for (int r0 = c0; r0 <= c1; r0 += 32) {
+    const int c = r0 + lane;
+    const bool live = c <= c1;
+    const float mc = live ? part_ml[(base + c) * 2] : -INFINITY;
+    const float lc = live ? part_ml[(base + c) * 2 + 1] : 0.f;
+    const float mx_new = fmaxf(mx, warp_max(mc));
+    const float rescale = mx == -INFINITY ? 0.f : exp2f(mx - mx_new);
+    const float w = live ? exp2f(mc - mx_new) : 0.f;
+    total = total * rescale + warp_sum(lc * w);
+    mx = mx_new;
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k) acc[k] *= rescale;
+    const int count = min(32, c1 - r0 + 1);
+    for (int j = 0; j < count; ++j) {
+      const float wj = __shfl_sync(0xffffffffu, w, j);
+      const float* src = part_o + (base + r0 + j) * D;
+#pragma unroll
+      for (int k = 0; k < PER_LANE; ++k) {
+        const int dim = lane + 32 * k;
+        if (dim < D) acc[k] += src[dim] * wj;
+      }
+    }
+  }
   const float inv = total > 0.f ? 1.f / total : 0.f;
-  for (int dim = threadIdx.x; dim < D; dim += blockDim.x) {
-    float acc = 0.f;
-    for (int c = c0; c <= c1; ++c)
-      acc += part_o[(base + c) * D + dim] * exp2f(part_ml[(base + c) * 2] - mx);
-    float v = acc * inv;
+#pragma unroll
+  for (int k = 0; k < PER_LANE; ++k) {
+    const int dim = lane + 32 * k;
+    if (dim >= D) continue;
+    float v = acc[k] * inv;
     if (gate) v *= 1.f / (1.f + expf(-__bfloat162float(gate[token * gate_stride + (size_t)head * D + dim])));
     out[(token * nq + head) * D + dim] = __float2bfloat16_rn(v);
   }
@@ -518,7 +555,7 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
       chunk_keys, max_chunks, max_pages, num_pages, nq, nkv, page_size, window, scale, err);
   int code = OMNIA_LAUNCH_RESULT();
   if (code) return code;
-  attention_combine_kernel<<<dim3(requests, nq), D < 128 ? D : 128, 0, stream>>>(
+  attention_combine_kernel<<<dim3(requests, (nq + 3) / 4), 128, 0, stream>>>(
       part_o, part_ml, cu_seqlens, seq_lens, seq_ids, (const bf16*)gate, gate_stride, (bf16*)out,
       chunk_keys, max_chunks, nq, window);
   return OMNIA_LAUNCH_RESULT();

@@ -109,10 +109,111 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
   }
 }
 
+// The same residual step with the whole row in registers: every load of the row (branch, x
+// and both weights) is issued before the first reduction, so a row costs one memory round
+// trip instead of three. hidden % 4 == 0 and hidden <= 4 * ITERS * blockDim.
+template <typename T>
+struct Vec4;
+template <>
+struct Vec4<float> {
+  static __device__ __forceinline__ void load(const float* p, float* v) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <>
+struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 t;
+    t.x = *reinterpret_cast<unsigned*>(&a);
+    t.y = *reinterpret_cast<unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = t;
+  }
+};
+
+template <typename T, int ITERS>
+__global__ void add_rmsnorm_reg_kernel(float* __restrict__ x, const T* __restrict__ branch,
+                                       const float* __restrict__ wb, float eps_b, int norm_branch,
+                                       const float* __restrict__ wo, float eps_o, int norm_out,
+                                       T* __restrict__ h, int hidden) {
+  __shared__ float scratch[33];
+  float* xr = x + (size_t)blockIdx.x * hidden;
+  const T* br = branch + (size_t)blockIdx.x * hidden;
+  float a[ITERS][4], xv[ITERS][4], gb[ITERS][4], go[ITERS][4];
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = (it * blockDim.x + threadIdx.x) * 4;
+    const bool live = i < hidden;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) a[it][k] = xv[it][k] = 0.f, gb[it][k] = go[it][k] = 1.f;
+    if (live) {
+      Vec4<T>::load(br + i, a[it]);
+      Vec4<float>::load(xr + i, xv[it]);
+      if (norm_branch && wb) Vec4<float>::load(wb + i, gb[it]);
+      if (norm_out && wo) Vec4<float>::load(wo + i, go[it]);
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) ss += a[it][k] * a[it][k];
+  float scale_b = 1.f;
+  if (norm_branch) scale_b = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps_b);
+  ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float v = a[it][k];
+      if (norm_branch) v = v * scale_b * gb[it][k];
+      xv[it][k] += v;
+      ss += xv[it][k] * xv[it][k];
+    }
+    const int i = (it * blockDim.x + threadIdx.x) * 4;
+    if (i < hidden) Vec4<float>::store(xr + i, xv[it]);
+  }
+  if (!norm_out) return;
+  const float scale_o = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps_o);
+  T* out = h + (size_t)blockIdx.x * hidden;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = (it * blockDim.x + threadIdx.x) * 4;
+    if (i >= hidden) continue;
+    float v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = xv[it][k] * scale_o * go[it][k];
+    Vec4<T>::store(out + i, v);
+  }
+}
+
 extern "C" int omnia_add_rmsnorm(float* x, const void* branch, const float* wb, float eps_b,
                                  int norm_branch, const float* wo, float eps_o, int norm_out,
                                  void* h, int rows, int hidden, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
+  if (hidden % 4 == 0 && hidden <= 8192) {
+    const int threads = hidden <= 1024 ? 128 : hidden <= 4096 ? 256 : 512;
+    const int iters = (hidden + threads * 4 - 1) / (threads * 4);
+    OMNIA_DISPATCH_DTYPE(dtype, {
+      if (iters <= 2)
+        add_rmsnorm_reg_kernel<T, 2><<<rows, threads, 0, stream>>>(
+            x, (const T*)branch, wb, eps_b, norm_branch, wo, eps_o, norm_out, (T*)h, hidden);
+      else
+        add_rmsnorm_reg_kernel<T, 4><<<rows, threads, 0, stream>>>(
+            x, (const T*)branch, wb, eps_b, norm_branch, wo, eps_o, norm_out, (T*)h, hidden);
+    });
+    return OMNIA_LAUNCH_RESULT();
+  }
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   OMNIA_DISPATCH_DTYPE(dtype, {

@@ -180,6 +180,52 @@ sample_kernel(float* __restrict__ logits, long long stride, int vocab,
   if (threadIdx.x == 0) out[row] = pick.i;
 }
 
+// Greedy choice for many rows at once: stage 1 finds the best of each of ARGMAX_PARTS slices
+// of a row, stage 2 the best of those (ties go to the lower index in both).
+#define ARGMAX_PARTS 32
+
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, long long stride, int vocab,
+                      float* __restrict__ part_v, int* __restrict__ part_i) {
+  __shared__ ArgMax ascratch[33];
+  const int row = blockIdx.y, part = blockIdx.x;
+  const float* z = logits + (size_t)row * stride;
+  const int per = (vocab + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
+  const int begin = part * per, end = min(vocab, begin + per);
+  ArgMax best{-INFINITY, 0x7fffffff};
+  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) best = better(best, ArgMax{z[i], i});
+  best = block_argmax(best, ascratch);
+  if (threadIdx.x == 0) {
+    part_v[row * ARGMAX_PARTS + part] = best.v;
+    part_i[row * ARGMAX_PARTS + part] = best.i;
+  }
+}
+
+__global__ void __launch_bounds__(32)
+argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
+                    int* __restrict__ out) {
+  const int row = blockIdx.x, lane = threadIdx.x;
+  ArgMax a{part_v[row * ARGMAX_PARTS + lane], part_i[row * ARGMAX_PARTS + lane]};
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax b;
+    b.v = __shfl_xor_sync(0xffffffffu, a.v, o);
+    b.i = __shfl_xor_sync(0xffffffffu, a.i, o);
+    a = better(a, b);
+  }
+  if (lane == 0) out[row] = a.i;
+}
+
+// part_v, part_i: scratch of rows * 32 elements each.
+extern "C" int omnia_argmax(const float* logits, long long stride, int rows, int vocab,
+                            float* part_v, int* part_i, int* out, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  argmax_partial_kernel<<<dim3(ARGMAX_PARTS, rows), 256, 0, stream>>>(logits, stride, vocab, part_v,
+                                                                     part_i);
+  argmax_final_kernel<<<rows, 32, 0, stream>>>(part_v, part_i, out);
+  return OMNIA_LAUNCH_RESULT();
+}
+
 extern "C" int omnia_sample(float* logits, long long stride, int rows, int vocab,
                             const float* temperature, const int* top_k, const float* top_p,
                             const float* min_p, const float* penalty, const int* history,

@@ -29,6 +29,7 @@ class EngineArgs:
     cache_tokens:   how many tokens the page pool of each group can hold
     max_requests:   live requests (state slots) at most
     device:         the CUDA device
+    cuda_graphs:    replay single-token steps from captured CUDA graphs
     """
 
     dtype: str = "bfloat16"
@@ -36,6 +37,7 @@ class EngineArgs:
     cache_tokens: int = 8192
     max_requests: int = 64
     device: str = "cuda:0"
+    cuda_graphs: bool = True
 
 
 def _runtime(args: EngineArgs) -> Runtime:
@@ -87,7 +89,7 @@ class Engine:
         pages = -(-args.cache_tokens // args.page_size)
         self.cache = CacheManager(model.cache_needs(), page_size=args.page_size, pages_per_group=pages,
                                   max_requests=args.max_requests, dtype=runtime.dtype, device=runtime.device)
-        self.runner = StepRunner(model, self.cache, runtime)
+        self.runner = StepRunner(model, self.cache, runtime, cuda_graphs=args.cuda_graphs)
 
     @property
     def vocab_size(self) -> int:

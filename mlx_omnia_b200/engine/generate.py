@@ -96,7 +96,7 @@ class Generator:
             tokens = planned.request.tokens[planned.start: planned.start + planned.count]
             entries.append(StepEntry(planned.request.cache, tokens, [planned.count - 1] if planned.samples else []))
         try:
-            logits = self.engine.runner.run(entries)
+            logits = self.engine.runner.run(entries, copy=False)
         except Exception:
             for planned in plan.entries:  # a failed step fails its requests and frees what they hold
                 self.scheduler._finish(planned.request, "abort")

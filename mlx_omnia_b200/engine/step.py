@@ -34,9 +34,15 @@ class StepEntry:
 class StepRunner:
     """Owns nothing but the glue: the model, the cache manager and the runtime."""
 
-    def __init__(self, model: DecoderModel, cache: CacheManager, runtime: Runtime) -> None:
+    def __init__(self, model: DecoderModel, cache: CacheManager, runtime: Runtime, cuda_graphs: bool = False) -> None:
         self.model, self.cache, self.runtime = model, cache, runtime
         self.steps_run = 0
+        self.graphs = None
+        if cuda_graphs and runtime.device.type == "cuda":
+            from mlx_omnia_b200.engine.decode_graph import DecodeGraphs
+
+            if DecodeGraphs.supported(model):
+                self.graphs = DecodeGraphs(self)
 
     # -- metadata ----------------------------------------------------------------------
     def _device(self, array: np.ndarray) -> torch.Tensor:
@@ -117,14 +123,20 @@ class StepRunner:
         return contexts
 
     # -- the step ----------------------------------------------------------------------
-    def run(self, entries: list[StepEntry]) -> torch.Tensor:
-        step = self.build_context(entries)
+    def run(self, entries: list[StepEntry], copy: bool = True) -> torch.Tensor:
+        """One step. Steps in which every request brings a single token are replayed
+        from a captured CUDA graph when graphs are on; `copy=False` then returns the
+        graph's own logits buffer, which the next step overwrites."""
         fresh_slots = [e.request.slot for e in entries if e.request.fresh]
         if fresh_slots and self.cache.state:
             index = torch.as_tensor(fresh_slots, device=self.runtime.device)
             for state in self.cache.state.values():
                 state.index_fill_(0, index, 0)
-        logits = self.model.forward(step, self.layer_contexts(step))
+        if self.graphs is not None and entries and all(len(e.tokens) == 1 and e.want in ([], [0]) for e in entries):
+            logits = self.graphs.run(entries, copy)
+        else:
+            step = self.build_context(entries)
+            logits = self.model.forward(step, self.layer_contexts(step))
         for entry in entries:
             entry.request.fresh = False
             self.cache.release_behind_window(entry.request)

@@ -213,8 +213,11 @@ def paged_attention(q: torch.Tensor, kv: KVView, step: StepContext, scale: float
     defines = {"HEAD_DIM": d, "GROUP": nq // nkv}
     if step.decode_only:
         max_chunks = -(-step.max_seq_len // DECODE_CHUNK)
-        part_o = scratch(q.device, "attention_part_o", tokens * nq * max_chunks * d)
-        part_ml = scratch(q.device, "attention_part_ml", tokens * nq * max_chunks * 2)
+        held = step.workspace if isinstance(step.workspace, dict) else {}
+        part_o, part_ml = held.get("attention_part_o"), held.get("attention_part_ml")
+        if part_o is None or part_o.numel() < tokens * nq * max_chunks * d:
+            part_o = scratch(q.device, "attention_part_o", tokens * nq * max_chunks * d)
+            part_ml = scratch(q.device, "attention_part_ml", tokens * nq * max_chunks * 2)
         fn = _function("attention_tc", "omnia_attention_decode_tc",
                        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                         c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
@@ -262,14 +265,67 @@ def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def linear(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    """a [rows, k] times weight [n, k] transposed -> [rows, n], float32 accumulation.
-    The matrix product itself is the vendor library's (as the reference's is MLX's);
-    on the 32-bit path it runs without any reduced-precision mode."""
+SKINNY_ROWS = 16
+"""Up to this many activation rows, bfloat16 products run on the weight-streaming kernel."""
+
+
+def _skinny(a: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < a.shape[0] <= SKINNY_ROWS
+            and a.shape[1] % 8 == 0 and a.is_cuda)
+
+
+def _gemm_skinny(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, multiplier: float = 1.0,
+                 cap: float = 0.0) -> torch.Tensor:
+    fn = _function("gemm_skinny", "omnia_gemm_skinny",
+                   [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+    _check(fn(_ptr(a), _ptr(weight), _ptr(out), a.shape[0], weight.shape[0], a.shape[1], epilogue, multiplier, cap,
+              _stream()), "gemm_skinny")
+    return out
+
+
+def _library_mm(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     if a.dtype == torch.float32 and (torch.backends.cuda.matmul.allow_tf32
                                       or torch.get_float32_matmul_precision() != "highest"):
         raise KernelError("the 32-bit path needs true float32 matrix products; TF32 is switched on")
     return torch.mm(a, weight.t())
+
+
+def linear(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """a [rows, k] times weight [n, k] transposed -> [rows, n], float32 accumulation.
+    A few bfloat16 rows (a decode step) run on this package's weight-streaming kernel.
+    Otherwise the matrix product is the vendor library's (as the reference's is MLX's);
+    on the 32-bit path it runs without any reduced-precision mode."""
+    if _skinny(a, weight):
+        out = torch.empty(a.shape[0], weight.shape[0], dtype=a.dtype, device=a.device)
+        return _gemm_skinny(a, weight, out, 0)
+    return _library_mm(a, weight)
+
+
+def linear_swiglu(a: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(a @ gate^T) * (a @ up^T) with gate_up = [gate rows | up rows] -> [rows, inner]."""
+    if _skinny(a, gate_up):
+        out = torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device)
+        return _gemm_skinny(a, gate_up, out, 1)
+    return swiglu(_library_mm(a, gate_up))
+
+
+def linear_softcap(a: torch.Tensor, weight: torch.Tensor, multiplier: float, cap: float | None) -> torch.Tensor:
+    """float32 logits = cap * tanh((a @ weight^T) * multiplier / cap) -> [rows, n]."""
+    if _skinny(a, weight):
+        out = torch.empty(a.shape[0], weight.shape[0], dtype=torch.float32, device=a.device)
+        return _gemm_skinny(a, weight, out, 2, multiplier, cap or 0.0)
+    return softcap(_library_mm(a, weight), multiplier, cap)
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """The first largest entry of each row of float32 `logits` [rows, vocab]. -> int32 [rows]"""
+    rows, vocab = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    part_v = scratch(logits.device, "argmax_v", rows * 32)
+    part_i = scratch(logits.device, "argmax_i", rows * 32, torch.int32)
+    fn = _function("sampling", "omnia_argmax", [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(logits), logits.stride(0), rows, vocab, _ptr(part_v), _ptr(part_i), _ptr(out), _stream()), "argmax")
+    return out
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,

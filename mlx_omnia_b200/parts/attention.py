@@ -28,6 +28,8 @@ class GQAAttention(Mixer):
     own_kv:    False for a layer that only reads another layer's cache (no k/v weights)
     """
 
+    graph_safe = True  # no host-side work per request: a decode step can be captured
+
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, scale: float,
                  window: int | None = None, qk_norm_eps: float | None = None, gated: bool = False,
                  position: PartSpec | None = None, own_kv: bool = True) -> None:

@@ -61,4 +61,4 @@ class LMHead(Part):
             self.weight = table
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return ops.softcap(ops.linear(h, self.weight), self.multiplier, self.softcap)
+        return ops.linear_softcap(h, self.weight, self.multiplier, self.softcap)

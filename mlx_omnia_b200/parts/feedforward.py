@@ -36,5 +36,4 @@ class GatedMLP(FeedForward):
         self.down = tensors["down_proj.weight"].contiguous()
 
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
-        gu = ops.linear(h, self.gate_up)
-        return ops.linear(ops.swiglu(gu), self.down)
+        return ops.linear(ops.linear_swiglu(h, self.gate_up), self.down)

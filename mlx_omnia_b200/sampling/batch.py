@@ -21,9 +21,7 @@ def sample_rows(logits: torch.Tensor, params: list[SamplingParams], seeds: list[
         return torch.from_numpy(np.asarray(values, dtype=dtype)).to(device, non_blocking=True)
 
     if all(p.greedy and p.repetition_penalty == 1.0 for p in params):
-        zeros = dev([0.0] * len(params), np.float32)
-        return ops.sample(logits, zeros, None, None, None, dev([0] * len(params), np.int64),
-                          dev([0] * len(params), np.int64))
+        return ops.argmax(logits)
     penalty = history = None
     if any(p.repetition_penalty != 1.0 for p in params):
         width = max(p.penalty_context for p in params)

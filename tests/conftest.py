@@ -35,7 +35,8 @@ def cpu_ops(monkeypatch):
     from mlx_omnia_b200.kernels import ops
 
     for name in ("embed_rmsnorm", "rmsnorm", "add_rmsnorm", "qk_norm_rope_store", "paged_attention", "swiglu",
-                 "softcap", "gather_rows", "linear", "sample"):
+                 "softcap", "gather_rows", "linear", "linear_swiglu", "linear_softcap", "sample",
+                 "argmax"):
         monkeypatch.setattr(ops, name, getattr(kernel_refs, name))
     monkeypatch.setattr(ops, "raise_on_error", lambda device: None)
     return ops

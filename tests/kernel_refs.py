@@ -124,6 +124,14 @@ def linear(a, weight):
     return (a.float() @ weight.float().t()).to(a.dtype)
 
 
+def linear_swiglu(a, gate_up):
+    return swiglu(linear(a, gate_up))
+
+
+def linear_softcap(a, weight, multiplier, cap):
+    return softcap(linear(a, weight), multiplier, cap)
+
+
 # ---- sampling ------------------------------------------------------------------------
 
 _M0, _M1, _W0, _W1 = 0xD2511F53, 0xCD9E8D57, 0x9E3779B9, 0xBB67AE85
@@ -163,6 +171,10 @@ def kept_mask(logits: torch.Tensor, temperature: float, top_k: int, top_p: float
     if min_p > 0:
         keep &= e >= min_p
     return keep
+
+
+def argmax(logits):
+    return torch.argmax(logits.float(), dim=-1).to(torch.int32)
 
 
 def sample(logits, temperature, top_k, top_p, min_p, seeds, draws, penalty=None, history=None):

@@ -85,3 +85,35 @@ def test_command_line(tmp_path):
     empty = subprocess.run([sys.executable, str(ROOT / "bin" / "omnia"), "run", "-m", str(tmp_path / "m")],
                            capture_output=True, text=True, stdin=subprocess.DEVNULL, timeout=120)
     assert empty.returncode == 2 and "nothing to say" in empty.stderr
+
+
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("C", "bfloat16")])
+def test_captured_decode_steps_equal_eager_ones(name, dtype):
+    """Single-token steps replayed from a CUDA graph give the logits of the same steps
+    launched one kernel at a time, with three requests of different lengths in flight."""
+    from mlx_omnia_b200.engine.engine import Engine, EngineArgs
+    from mlx_omnia_b200.engine.step import StepEntry
+
+    raw, weights = tiny_configs.config(name), tiny_configs.tensors(name)
+    vocab = raw["text_config"]["vocab_size"]
+    prompts = [tiny_configs.prompt(n, vocab, 90 + n) for n in (70, 9, 33)]
+    results = []
+    for graphs in (False, True):
+        engine = Engine.from_tensors(raw, weights, EngineArgs(dtype=dtype, page_size=8, cache_tokens=512,
+                                                              max_requests=4, cuda_graphs=graphs))
+        requests = [engine.cache.open(f"r{i}") for i in range(3)]
+        engine.runner.run([StepEntry(r, p[:-20], []) for r, p in zip(requests, prompts) if len(p) > 20])
+        rows = []
+        for k in range(20):
+            live = [(r, p[len(p) - 20 + k]) for r, p in zip(requests, prompts) if len(p) > 20 or k >= 20 - len(p)]
+            rows.append(engine.runner.run([StepEntry(r, [t], [0]) for r, t in live]))
+        assert (engine.runner.graphs is not None and engine.runner.graphs.replays > 0) == graphs
+        results.append(torch.cat(rows))
+    assert torch.equal(results[0], results[1])
+    expect = plain_impl.forward(raw, weights, prompts[0])[-20:]
+    picks, at = [], 0
+    for k in range(20):
+        live = [i for i, p in enumerate(prompts) if len(p) > 20 or k >= 20 - len(p)]
+        picks.append(results[1][at + live.index(0)])
+        at += len(live)
+    assert plain_impl.relative_diff(torch.stack(picks), expect) < (1e-4 if dtype == "float32" else 3e-2)

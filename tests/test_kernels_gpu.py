@@ -210,6 +210,23 @@ def test_linear_is_true_float32(ops):
     close(ops.linear(ab, wb), (ab.double() @ wb.double().t()).float(), torch.bfloat16, scale=3)
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 11, 16])
+@pytest.mark.parametrize("n,k", [(2048, 2048), (6144, 2048), (2048, 6144), (1000, 96), (777, 160), (50, 8), (5000, 520)])
+def test_skinny_products(ops, m, n, k):
+    """The weight-streaming kernel and its fused epilogues against float64 products of the
+    same bfloat16 operands, at sizes with ragged edges in every dimension."""
+    a = rand(m, k, dtype=torch.bfloat16, seed=m)
+    w = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=n + k)
+    exact = a.double() @ w.double().t()
+    close(ops.linear(a, w), exact, torch.bfloat16)
+    z = exact.float().bfloat16().double()
+    close(ops.linear_softcap(a, w, 3.0, 7.0), 7.0 * torch.tanh(z * 3.0 / 7.0), torch.bfloat16)
+    close(ops.linear_softcap(a, w, 0.5, None), z * 0.5, torch.bfloat16)
+    if n % 2 == 0:
+        g, u = z[:, : n // 2], z[:, n // 2:]
+        close(ops.linear_swiglu(a, w), g * torch.sigmoid(g) * u, torch.bfloat16)
+
+
 def test_sampling(ops):
     vocab, rows = 1531, 6
     logits = rand(rows, vocab, scale=2.0, seed=9)
@@ -233,6 +250,14 @@ def test_sampling(ops):
     got = ops.sample(logits.clone(), temperature, top_k, top_p, min_p, seeds, draws, penalty, history)
     expect = kernel_refs.sample(logits.clone(), temperature, top_k, top_p, min_p, seeds, draws, penalty, history)
     assert got.tolist() == expect.tolist() and got[0].item() != int(logits[0].argmax())
+
+
+def test_argmax_takes_the_first_of_a_tie(ops):
+    logits = rand(9, 151936 // 8 + 3, scale=2.0, seed=3)
+    logits[2, 5] = logits[2, 18000] = 50.0
+    logits[4, -1] = 60.0
+    got = ops.argmax(logits)
+    assert got.tolist() == torch.argmax(logits, dim=-1).tolist() and got[2].item() == 5
 
 
 def test_sampling_keeps_exactly_the_filtered_set(ops):
