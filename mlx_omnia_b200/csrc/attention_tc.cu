@@ -12,8 +12,9 @@
 //   decode:   one warp per block owns the g rows of one single-token request and one
 //             fixed chunk of DECODE_CHUNK keys (chunks are aligned to absolute key
 //             positions, so the partition never depends on the batch); it writes an
-//             unnormalised partial (max, sum, accumulator) to scratch memory, and the
-//             combine kernel merges a token's chunks in ascending order.
+//             unnormalised partial (max, sum, accumulator) to scratch memory and takes a
+//             ticket; the block that draws the last ticket of a (request, head group)
+//             merges that group's chunks in ascending order (nobody waits for anybody).
 // Keys and values are addressed row by row through the block table, so any page size
 // works. Rows outside the visible range are zero-filled in shared memory (never read
 // from the cache), which keeps stale or poisoned pages out of the arithmetic.
@@ -39,7 +40,7 @@ constexpr int BM = 64;                   // rows per prefill block
 constexpr int BN = 64;                   // keys per prefill tile
 constexpr int TOKENS_PER_BLOCK = BM / GROUP;
 constexpr int DECODE_BN = 32;            // keys per decode tile
-constexpr int DECODE_STAGES = 3;
+constexpr int DECODE_STAGES = 2;
 constexpr int DECODE_TABLE = 64;         // block-table entries a decode block stages in shared memory
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -326,20 +327,80 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pa
   }
 }
 
+// Merge chunks c0..c1 of one (token, head), ascending, then gate and round; run by one warp.
+// Lanes hold the chunks' weights (32 chunks per round, rescaled online across rounds), then
+// every lane accumulates its own dims over the chunks. Partials are read from L2.
+__device__ __forceinline__ void combine_head(const float* __restrict__ part_o,
+                                             const float* __restrict__ part_ml, size_t base,
+                                             int c0, int c1, const bf16* gate_row, bf16* out_row) {
+  const int lane = threadIdx.x & 31;
+  constexpr int PER_LANE = (D + 31) / 32;
+  float acc[PER_LANE];
+#pragma unroll
+  for (int k = 0; k < PER_LANE; ++k) acc[k] = 0.f;
+  float mx = -INFINITY, total = 0.f;
+  for (int r0 = c0; r0 <= c1; r0 += 32) {
+    const int c = r0 + lane;
+    const bool live = c <= c1;
+    const float mc = live ? __ldcg(part_ml + (base + c) * 2) : -INFINITY;
+    const float lc = live ? __ldcg(part_ml + (base + c) * 2 + 1) : 0.f;
+    const float mx_new = fmaxf(mx, warp_max(mc));
+    const float rescale = mx == -INFINITY ? 0.f : exp2f(mx - mx_new);
+    const float w = live ? exp2f(mc - mx_new) : 0.f;
+    total = total * rescale + warp_sum(lc * w);
+    mx = mx_new;
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k) acc[k] *= rescale;
+    const int count = min(32, c1 - r0 + 1);
+    for (int j0 = 0; j0 < count; j0 += 8) {
+      float vals[8][PER_LANE];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {  // the loads of eight chunks are in flight together
+        const float* src = part_o + (base + r0 + min(j0 + u, count - 1)) * D;
+#pragma unroll
+        for (int k = 0; k < PER_LANE; ++k) {
+          const int dim = lane + 32 * k;
+          vals[u][k] = dim < D ? __ldcg(src + dim) : 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float wj = __shfl_sync(0xffffffffu, w, (j0 + u) & 31);
+        if (j0 + u < count) {
+#pragma unroll
+          for (int k = 0; k < PER_LANE; ++k) acc[k] += vals[u][k] * wj;
+        }
+      }
+    }
+  }
+  const float inv = total > 0.f ? 1.f / total : 0.f;
+#pragma unroll
+  for (int k = 0; k < PER_LANE; ++k) {
+    const int dim = lane + 32 * k;
+    if (dim >= D) continue;
+    float v = acc[k] * inv;
+    if (gate_row) v *= 1.f / (1.f + expf(-__bfloat162float(gate_row[dim])));
+    out_row[dim] = __float2bfloat16_rn(v);
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // Decode: grid (chunks, nkv, requests); 32 threads. Request s is the single-token
 // request seq_ids[s] (or s when seq_ids is null). Partials:
 //   part_o  [tokens, nq, max_chunks, D] float32 (unnormalised), part_ml [tokens, nq, max_chunks, 2]
+//   tickets [requests, nkv] int32, zero before the first launch; the merging block zeroes its
+//   ticket again, so the array is ready for the next launch.
 __global__ void __launch_bounds__(32)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages,
                         const int* __restrict__ block_table, const int* __restrict__ cu_seqlens,
                         const int* __restrict__ seq_lens, const int* __restrict__ seq_ids,
-                        float* __restrict__ part_o, float* __restrict__ part_ml, int chunk_keys,
-                        int max_chunks, int max_pages, int num_pages, int nq, int nkv, int page_size,
-                        int window, float scale, int* err) {
+                        float* __restrict__ part_o, float* __restrict__ part_ml,
+                        int* __restrict__ tickets, const bf16* __restrict__ gate, int gate_stride,
+                        bf16* __restrict__ out, int chunk_keys, int max_chunks, int max_pages,
+                        int num_pages, int nq, int nkv, int page_size, int window, float scale,
+                        int* err) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* qs = reinterpret_cast<bf16*>(smem_raw);  // [16][ROW]
-  bf16* kv = qs + 16 * ROW;                      // DECODE_STAGES x (K [32][ROW], V [32][ROW])
+  bf16* kv = reinterpret_cast<bf16*>(smem_raw);  // DECODE_STAGES x (K [32][ROW], V [32][ROW])
   const int lane = threadIdx.x;
   const int seq = seq_ids ? seq_ids[blockIdx.z] : blockIdx.z;
   const int kvh = blockIdx.y, chunk = blockIdx.x;
@@ -360,27 +421,28 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
   CacheRef cache{pages, staged ? table_s : table_row, staged ? page_lo : 0, num_pages, nkv, kvh, page_size};
   __syncwarp();
 
-  for (int i = lane; i < 16 * CHP; i += 32) {
-    const int r = i / CHP, c = i % CHP;
-    const bool valid = r < GROUP && c < CH;
-    cp_async16(qs + r * ROW + c * 8, valid ? q + (token * nq + kvh * GROUP + r) * D + c * 8 : q, valid);
-  }
-  cp_async_commit();
   for (int stage = 0; stage < DECODE_STAGES; ++stage)
     zero_padding(kv + stage * 2 * DECODE_BN * ROW, 2 * DECODE_BN, lane, 32);
 
   const int tile0 = lo / DECODE_BN, tiles = hi / DECODE_BN - tile0 + 1;
+  // A tile's loads: lane l looks up the row of key l once; then the warp copies the tile in
+  // flat order (consecutive lanes take consecutive 16-byte chunks of a row, so every
+  // request covers whole 128-byte lines), fetching each row's address by shuffle.
   auto load_tile = [&](int tile, int stage) {
     bf16* kt = kv + stage * 2 * DECODE_BN * ROW;
     bf16* vt = kt + DECODE_BN * ROW;
     const int p = (tile0 + tile) * DECODE_BN + lane;
     const bool visible = p >= lo && p <= hi;
-    const bf16* kp = visible ? cache_row(cache, p, 0, err) : nullptr;
-    const bf16* vp = kp ? kp + (size_t)nkv * page_size * D : nullptr;
+    const bf16* mine = visible ? cache_row(cache, p, 0, err) : nullptr;
+    const size_t v_offset = (size_t)nkv * page_size * D;
 #pragma unroll
-    for (int c = 0; c < CH; ++c) {
-      cp_async16(kt + lane * ROW + c * 8, kp ? kp + c * 8 : pages, kp != nullptr);
-      cp_async16(vt + lane * ROW + c * 8, vp ? vp + c * 8 : pages, kp != nullptr);
+    for (int it = 0; it < CH; ++it) {
+      const int flat = it * 32 + lane;
+      const int key = flat / CH, c = flat % CH;
+      const bf16* kp = reinterpret_cast<const bf16*>(
+          __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(mine), key));
+      cp_async16(kt + key * ROW + c * 8, kp ? kp + c * 8 : pages, kp != nullptr);
+      cp_async16(vt + key * ROW + c * 8, kp ? kp + v_offset + c * 8 : pages, kp != nullptr);
     }
   };
 #pragma unroll
@@ -389,7 +451,26 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     cp_async_commit();
   }
 
+  // Query fragments straight from global memory: row g of the A operand is query head g of
+  // the group (rows at or beyond GROUP are zero), columns 2t, 2t+1 (+8) of each 16-wide step.
   unsigned qf[KSTEPS][4];
+  {
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int kstep = 0; kstep < KSTEPS; ++kstep) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int dim = kstep * 16 + half * 8 + 2 * t;
+        unsigned lo_row = 0u, hi_row = 0u;
+        if (dim < D) {
+          if (g < GROUP) lo_row = __ldg(reinterpret_cast<const unsigned*>(q + (token * nq + kvh * GROUP + g) * D + dim));
+          if (g + 8 < GROUP) hi_row = __ldg(reinterpret_cast<const unsigned*>(q + (token * nq + kvh * GROUP + g + 8) * D + dim));
+        }
+        qf[kstep][2 * half] = lo_row;
+        qf[kstep][2 * half + 1] = hi_row;
+      }
+    }
+  }
   float o[NT_O][4];
 #pragma unroll
   for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
@@ -409,7 +490,6 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     cp_async_commit();
     cp_async_wait<DECODE_STAGES - 1>();
     __syncwarp();
-    if (tile == 0) load_q_fragments(qs, qf);
     const bf16* kt = kv + (tile % DECODE_STAGES) * 2 * DECODE_BN * ROW;
     attend_tile<DECODE_BN>(qf, kt, kt + DECODE_BN * ROW, (tile0 + tile) * DECODE_BN, row_lo, row_hi,
                            sl2, m, l, o);
@@ -440,64 +520,24 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
       part_ml[slot * 2 + 1] = l[r];
     }
   }
-}
-
-// Merge the chunks of each (request, head), ascending, then gate and round. One warp per
-// (request, head): lanes hold the chunks' weights (32 chunks per round, rescaled online
-// across rounds), then every lane accumulates its own dims over the chunks.
-// grid (requests, ceil(nq / 4)); 128 threads.
-__global__ void __launch_bounds__(128)
-attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                         const int* __restrict__ cu_seqlens, const int* __restrict__ seq_lens,
-                         const int* __restrict__ seq_ids, const bf16* __restrict__ gate,
-                         int gate_stride, bf16* __restrict__ out, int chunk_keys, int max_chunks,
-                         int nq, int window) {
-  const int seq = seq_ids ? seq_ids[blockIdx.x] : blockIdx.x;
-  const int lane = threadIdx.x & 31;
-  const int head = blockIdx.y * 4 + (threadIdx.x >> 5);
-  if (head >= nq) return;
-  const int pos = seq_lens[seq] - 1;
-  if (pos < 0) return;
-  const size_t token = (size_t)cu_seqlens[seq];
-  const int first = window > 0 ? max(0, pos - window + 1) : 0;
+  // Whoever finishes last merges: publish the partial, take a ticket, and if it is the last
+  // one of this (request, head group), read all partials back and write the output.
+  __threadfence();
+  __syncwarp();
   const int c0 = first / chunk_keys, c1 = pos / chunk_keys;
-  const size_t base = (token * nq + head) * max_chunks;
-  constexpr int PER_LANE = (D + 31) / 32;
-  float acc[PER_LANE];
-#pragma unroll
-  for (int k = 0; k < PER_LANE; ++k) acc[k] = 0.f;
-  float mx = -INFINITY, total = 0.f;
-  for (int r0 = c0; r0 <= c1; r0 += 32) {
-    const int c = r0 + lane;
-    const bool live = c <= c1;
-    const float mc = live ? part_ml[(base + c) * 2] : -INFINITY;
-    const float lc = live ? part_ml[(base + c) * 2 + 1] : 0.f;
-    const float mx_new = fmaxf(mx, warp_max(mc));
-    const float rescale = mx == -INFINITY ? 0.f : exp2f(mx - mx_new);
-    const float w = live ? exp2f(mc - mx_new) : 0.f;
-    total = total * rescale + warp_sum(lc * w);
-    mx = mx_new;
-#pragma unroll
-    for (int k = 0; k < PER_LANE; ++k) acc[k] *= rescale;
-    const int count = min(32, c1 - r0 + 1);
-    for (int j = 0; j < count; ++j) {
-      const float wj = __shfl_sync(0xffffffffu, w, j);
-      const float* src = part_o + (base + r0 + j) * D;
-#pragma unroll
-      for (int k = 0; k < PER_LANE; ++k) {
-        const int dim = lane + 32 * k;
-        if (dim < D) acc[k] += src[dim] * wj;
-      }
-    }
-  }
-  const float inv = total > 0.f ? 1.f / total : 0.f;
-#pragma unroll
-  for (int k = 0; k < PER_LANE; ++k) {
-    const int dim = lane + 32 * k;
-    if (dim >= D) continue;
-    float v = acc[k] * inv;
-    if (gate) v *= 1.f / (1.f + expf(-__bfloat162float(gate[token * gate_stride + (size_t)head * D + dim])));
-    out[(token * nq + head) * D + dim] = __float2bfloat16_rn(v);
+  int ticket = 0;
+  int* counter = tickets + (size_t)blockIdx.z * nkv + kvh;
+  if (lane == 0) ticket = atomicAdd(counter, 1);
+  ticket = __shfl_sync(0xffffffffu, ticket, 0);
+  if (ticket != c1 - c0) return;
+  if (lane == 0) *counter = 0;
+  __threadfence();
+#pragma unroll 1
+  for (int r = 0; r < GROUP; ++r) {
+    const int head = kvh * GROUP + r;
+    combine_head(part_o, part_ml, (token * nq + head) * max_chunks, c0, c1,
+                 gate ? gate + token * gate_stride + (size_t)head * D : nullptr,
+                 out + (token * nq + head) * D);
   }
 }
 
@@ -535,14 +575,14 @@ extern "C" int omnia_attention_prefill_tc(const void* q, const void* pages, cons
 extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const int* block_table,
                                          const int* cu_seqlens, const int* seq_lens,
                                          const int* seq_ids, int requests, float* part_o,
-                                         float* part_ml, int chunk_keys, int max_chunks,
-                                         const void* gate, int gate_stride, void* out,
-                                         int max_pages, int num_pages, int nq, int nkv,
+                                         float* part_ml, int* tickets, int chunk_keys,
+                                         int max_chunks, const void* gate, int gate_stride,
+                                         void* out, int max_pages, int num_pages, int nq, int nkv,
                                          int page_size, int window, float scale, int* err,
                                          cudaStream_t stream) {
   if (requests == 0) return 0;
   if (nq != nkv * GROUP || chunk_keys % DECODE_BN != 0 || max_chunks < 1) return (int)cudaErrorInvalidValue;
-  const size_t smem = (size_t)(16 + DECODE_STAGES * 2 * DECODE_BN) * ROW * sizeof(bf16);
+  const size_t smem = (size_t)(DECODE_STAGES * 2 * DECODE_BN) * ROW * sizeof(bf16);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel,
@@ -552,11 +592,7 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
   }
   attention_decode_kernel<<<dim3(max_chunks, nkv, requests), 32, smem, stream>>>(
       (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
-      chunk_keys, max_chunks, max_pages, num_pages, nq, nkv, page_size, window, scale, err);
-  int code = OMNIA_LAUNCH_RESULT();
-  if (code) return code;
-  attention_combine_kernel<<<dim3(requests, (nq + 3) / 4), 128, 0, stream>>>(
-      part_o, part_ml, cu_seqlens, seq_lens, seq_ids, (const bf16*)gate, gate_stride, (bf16*)out,
-      chunk_keys, max_chunks, nq, window);
+      tickets, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
+      num_pages, nq, nkv, page_size, window, scale, err);
   return OMNIA_LAUNCH_RESULT();
 }

@@ -103,6 +103,8 @@ class DecodeGraphs:
             "attention_part_ml": torch.empty(batch * max((getattr(b.mixer, "heads", 1) for b in runner.model.blocks),
                                                          default=1) * max_chunks * 2,
                                              dtype=torch.float32, device=device),
+            "attention_tickets": torch.zeros(batch * max((getattr(b.mixer, "kv_heads", 1) for b in runner.model.blocks),
+                                                         default=1), dtype=torch.int32, device=device),
         }
         step = StepContext(
             num_tokens=batch, num_seqs=batch, token_ids=view("token_ids"), positions=view("positions"),

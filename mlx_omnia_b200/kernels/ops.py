@@ -157,12 +157,15 @@ DECODE_CHUNK = 128
 _scratch: dict[tuple[int, str], torch.Tensor] = {}
 
 
-def scratch(device: torch.device, name: str, numel: int, dtype: torch.dtype = torch.float32) -> torch.Tensor:
-    """A reusable buffer of at least `numel` elements (contents undefined)."""
+def scratch(device: torch.device, name: str, numel: int, dtype: torch.dtype = torch.float32,
+            zeroed: bool = False) -> torch.Tensor:
+    """A reusable buffer of at least `numel` elements. Its contents are undefined unless
+    `zeroed`, in which case it is zero when created and its users leave it zero."""
     key = (device.index or 0, name)
     held = _scratch.get(key)
     if held is None or held.numel() < numel or held.dtype != dtype:
-        held = _scratch[key] = torch.empty(max(numel, 1), dtype=dtype, device=device)
+        make = torch.zeros if zeroed else torch.empty
+        held = _scratch[key] = make(max(numel, 1), dtype=dtype, device=device)
     return held
 
 
@@ -215,15 +218,18 @@ def paged_attention(q: torch.Tensor, kv: KVView, step: StepContext, scale: float
         max_chunks = -(-step.max_seq_len // DECODE_CHUNK)
         held = step.workspace if isinstance(step.workspace, dict) else {}
         part_o, part_ml = held.get("attention_part_o"), held.get("attention_part_ml")
+        tickets = held.get("attention_tickets")
         if part_o is None or part_o.numel() < tokens * nq * max_chunks * d:
             part_o = scratch(q.device, "attention_part_o", tokens * nq * max_chunks * d)
             part_ml = scratch(q.device, "attention_part_ml", tokens * nq * max_chunks * 2)
+            tickets = scratch(q.device, "attention_tickets", tokens * nkv, torch.int32, zeroed=True)
         fn = _function("attention_tc", "omnia_attention_decode_tc",
-                       [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
-                        c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-                        c_void_p], defines)
+                       [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                        c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                        c_float, c_void_p, c_void_p], defines)
         _check(fn(_ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.seq_lens), None,
-                  step.num_seqs, _ptr(part_o), _ptr(part_ml), DECODE_CHUNK, max_chunks, gate_ptr, gate_stride,
+                  step.num_seqs, _ptr(part_o), _ptr(part_ml), _ptr(tickets), DECODE_CHUNK, max_chunks, gate_ptr,
+                  gate_stride,
                   _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size, kv.window or 0, scale, err, _stream()),
                "attention_decode")
         return out
