@@ -39,8 +39,14 @@ constexpr int NT_O = DP / 8;             // output n-tiles
 constexpr int BM = 64;                   // rows per prefill block
 constexpr int BN = 64;                   // keys per prefill tile
 constexpr int TOKENS_PER_BLOCK = BM / GROUP;
-constexpr int DECODE_BN = 32;            // keys per decode tile
-constexpr int DECODE_STAGES = 2;
+#ifndef DECODE_TILE_KEYS
+#define DECODE_TILE_KEYS 32
+#endif
+#ifndef DECODE_PIPELINE
+#define DECODE_PIPELINE 2
+#endif
+constexpr int DECODE_BN = DECODE_TILE_KEYS;   // keys per decode tile (16, 32 or 64)
+constexpr int DECODE_STAGES = DECODE_PIPELINE;
 constexpr int DECODE_TABLE = 64;         // block-table entries a decode block stages in shared memory
 constexpr float LOG2E = 1.4426950408889634f;
 
