@@ -602,3 +602,86 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
       num_pages, nq, nkv, page_size, window, scale, err);
   return OMNIA_LAUNCH_RESULT();
 }
+
+// ---------------------------------------------------------------------------------------
+// The decode kernel for callers that cannot allocate (see attention_static.h): the three
+// scratch buffers are carved out of one array in the library's device image.
+#include "attention_static.h"
+
+#include <stdio.h>
+
+static __device__ __align__(256) unsigned char static_scratch[OMNIA_STATIC_SCRATCH_BYTES];
+
+static thread_local char static_error[256] = "";
+
+extern "C" const char* omnia_attention_static_error(void) { return static_error; }
+
+extern "C" int omnia_attention_decode_tc_static(const void* q, const void* pages,
+                                                const int* block_table, const int* cu_seqlens,
+                                                const int* seq_lens, const int* seq_ids,
+                                                int requests, int chunk_keys, int max_chunks,
+                                                const void* gate, int gate_stride, void* out,
+                                                int max_pages, int num_pages, int nq, int nkv,
+                                                int page_size, int window, float scale, int* err,
+                                                cudaStream_t stream) {
+  static_error[0] = 0;
+  if (requests == 0) return 0;
+  if (nq != nkv * GROUP || chunk_keys % DECODE_BN != 0 || max_chunks < 1) {
+    snprintf(static_error, sizeof static_error,
+             "this library is compiled for %d query heads per key/value head and chunks that are a "
+             "multiple of %d keys", GROUP, DECODE_BN);
+    return (int)cudaErrorInvalidValue;
+  }
+  const long long slots = (long long)requests * nq * max_chunks;
+  const long long floats = slots * (D + 2), tickets = (long long)requests * nkv;
+  if (floats > OMNIA_STATIC_SCRATCH_FLOATS || tickets > OMNIA_STATIC_TICKETS) {
+    snprintf(static_error, sizeof static_error,
+             "the call needs %lld scratch floats and %lld tickets; the static scratch holds %d and %d "
+             "(requests * nq * max_chunks * (head_dim + 2) floats, requests * nkv tickets)",
+             floats, tickets, OMNIA_STATIC_SCRATCH_FLOATS, OMNIA_STATIC_TICKETS);
+    return OMNIA_STATIC_TOO_LARGE;
+  }
+  // Once per device, with that device current: the array's name is only a host-side handle;
+  // the kernel needs the address the symbol has on this device.
+  constexpr int MAX_DEVICES = 64;
+  static unsigned char* device_address[MAX_DEVICES] = {nullptr};
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= MAX_DEVICES) {
+    snprintf(static_error, sizeof static_error, "cudaGetDevice failed or device %d is beyond %d", device,
+             MAX_DEVICES);
+    return e != cudaSuccess ? (int)e : OMNIA_STATIC_NO_DEVICE;
+  }
+  if (device_address[device] == nullptr) {
+    unsigned char* address = nullptr;
+    e = cudaGetSymbolAddress((void**)&address, static_scratch);
+    if (e != cudaSuccess) {
+      snprintf(static_error, sizeof static_error, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      return (int)e;
+    }
+    const size_t smem = (size_t)(DECODE_STAGES * 2 * DECODE_BN) * ROW * sizeof(bf16);
+    e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      snprintf(static_error, sizeof static_error, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      return (int)e;
+    }
+    device_address[device] = address;
+  }
+  float* part_o = reinterpret_cast<float*>(device_address[device]);
+  float* part_ml = part_o + slots * D;
+  int* ticket_area = reinterpret_cast<int*>(device_address[device] + (size_t)OMNIA_STATIC_SCRATCH_FLOATS * 4);
+  // The tickets must start at zero, whatever an earlier call left behind.
+  e = cudaMemsetAsync(ticket_area, 0, (size_t)tickets * sizeof(int), stream);
+  if (e != cudaSuccess) {
+    snprintf(static_error, sizeof static_error, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  const size_t smem = (size_t)(DECODE_STAGES * 2 * DECODE_BN) * ROW * sizeof(bf16);
+  attention_decode_kernel<<<dim3(max_chunks, nkv, requests), 32, smem, stream>>>(
+      (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
+      ticket_area, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
+      num_pages, nq, nkv, page_size, window, scale, err);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) snprintf(static_error, sizeof static_error, "launch: %s", cudaGetErrorString(e));
+  return (int)e;
+}
