@@ -1,0 +1,367 @@
+// out[m, n] = sum_k a[m, k] * w[n, k] in bfloat16 on the 5th-generation tensor cores:
+// TMA (cp.async.bulk.tensor) stages 128-byte-swizzled tiles of both operands in shared
+// memory, one elected thread issues tcgen05.mma with the accumulator in tensor memory,
+// and four warps read the accumulator back with tcgen05.ld for the epilogue.
+//
+// One block computes one 128 x BLOCK_N tile of the output (BLOCK_N = 256, or 128 for narrow
+// problems) over all of k in steps of 64, through a ring of STAGES shared-memory stages:
+//   warp 0   producer: waits for a free stage, arms its "full" barrier with the byte count
+//            and issues the two TMA loads (rows beyond m or n and columns beyond k are
+//            zero-filled by the TMA unit);
+//   warp 1   allocates tensor memory, then its elected lane waits for a full stage and issues
+//            four MMAs (k = 16 each); tcgen05.commit frees the stage when they have read it,
+//            and after the last step signals "accumulator ready";
+//   warps 2-5  wait for that signal, read their 32 accumulator rows 32 columns at a time,
+//            apply the epilogue and store.
+// Epilogues: 0 store bfloat16; 1 SwiGLU: the B tile holds 128 gate rows and the matching
+// 128 up rows of w, the block stores silu(gate) * up (BLOCK_N 256 only); 2 soft cap to float32.
+//
+// Every wait on a barrier is bounded: when the bound is hit the block raises OMNIA_ERR_TIMEOUT
+// in the error word, every role leaves its loop, the block waits (bounded again) for the TMA
+// loads it still has in flight, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define OMNIA_ERR_TIMEOUT 8
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 64;   // 128 bytes of bfloat16: one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;  // producer warp, MMA warp, four epilogue warps
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_SOFTCAP = 2 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait; false when the block is giving up (its own limit, or another role's).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
+// eight-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);  // start address
+  d |= (uint64_t)1 << 16;                       // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                       // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
+  return d;
+}
+
+// kind::f16 instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t addr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(addr));
+}
+
+template <int BLOCK_N, int STAGES, int EPI>
+__global__ void __launch_bounds__(THREADS)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    void* __restrict__ out, int m, int n, int k, int pair_offset, float multiplier,
+                    float cap, int* err) {
+  constexpr uint32_t A_BYTES = BLOCK_M * BLOCK_K * sizeof(bf16);
+  constexpr uint32_t B_BYTES = BLOCK_N * BLOCK_K * sizeof(bf16);
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
+  // bars[0..S) full, bars[S..2S) empty, bars[2S] accumulator ready
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BLOCK_M;
+  const int n0 = blockIdx.x * (EPI == EPI_SWIGLU ? BLOCK_N / 2 : BLOCK_N);
+  const int k_blocks = (k + BLOCK_K - 1) / BLOCK_K;
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), ready = smem_u32(bars + 2 * STAGES);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(ready, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
+                 "r"((uint32_t)BLOCK_N));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ---- producer ----------------------------------------------------------------------
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % STAGES;
+        if (kb >= STAGES && !mbar_wait(empty0 + 8 * s, ((kb / STAGES) - 1) & 1, abort_flag)) break;
+        const uint32_t a_dst = smem_u32(tiles + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
+        mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+        tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * BLOCK_K, m0);
+        if (EPI == EPI_SWIGLU) {
+          tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BLOCK_K, n0);
+          tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, kb * BLOCK_K, pair_offset + n0);
+        } else {
+          tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BLOCK_K, n0);
+        }
+        issued = kb + 1;
+      }
+      if (*abort_flag) {
+        // Giving up: let the loads already issued land before the block's memory goes away.
+        for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
+          const int s = kb % STAGES;
+          for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(full0 + 8 * s, (kb / STAGES) & 1); ++i) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BLOCK_M, BLOCK_N);
+      bool ok = true;
+      for (int kb = 0; kb < k_blocks && ok; ++kb) {
+        const int s = kb % STAGES;
+        ok = mbar_wait(full0 + 8 * s, (kb / STAGES) & 1, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+          const uint64_t a_desc = umma_desc(a_addr + kk * UMMA_K * sizeof(bf16));
+          const uint64_t b_desc = umma_desc(b_addr + kk * UMMA_K * sizeof(bf16));
+          umma(tmem_base, a_desc, b_desc, idesc, (kb | kk) != 0);
+        }
+        umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
+      }
+      if (ok) umma_commit(ready);
+    }
+  } else {
+    // ---- epilogue (warps 2..5 own accumulator rows 32 * (warp % 4) .. + 31) -------------------
+    const int quarter = warp & 3;
+    const int row = m0 + quarter * 32 + lane;
+    const bool ok = mbar_wait(ready, 0, abort_flag);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      if (EPI == EPI_SWIGLU) {
+        bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)row * pair_offset + n0;
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N / 2; c += 32) {
+          uint32_t gate[32], up[32];
+          tmem_load32(lane_base + c, gate);
+          tmem_load32(lane_base + BLOCK_N / 2 + c, up);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (row < m) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              float v[2];
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                // Both halves are rounded to bfloat16 first, as a separate product would round them.
+                const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gate[j + e])));
+                const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[j + e])));
+                v[e] = g / (1.f + expf(-g)) * u;
+              }
+              const int col = n0 + c + j;
+              if (col + 1 < pair_offset && (pair_offset & 1) == 0) {
+                *reinterpret_cast<__nv_bfloat162*>(dst + c + j) = __floats2bfloat162_rn(v[0], v[1]);
+              } else {
+                if (col < pair_offset) dst[c + j] = __float2bfloat16_rn(v[0]);
+                if (col + 1 < pair_offset) dst[c + j + 1] = __float2bfloat16_rn(v[1]);
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N; c += 32) {
+          uint32_t acc[32];
+          tmem_load32(lane_base + c, acc);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (row >= m) continue;
+          if (EPI == EPI_SOFTCAP) {
+            float* dst = reinterpret_cast<float*>(out) + (size_t)row * n + n0 + c;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (n0 + c + j >= n) break;
+              const float z = __bfloat162float(__float2bfloat16_rn(__uint_as_float(acc[j]))) * multiplier;
+              dst[j] = cap > 0.f ? cap * tanhf(z / cap) : z;
+            }
+          } else {
+            bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)row * n + n0 + c;
+            if (n0 + c + 32 <= n && (n & 7) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 packed;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]));
+                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(acc[j + 2]), __uint_as_float(acc[j + 3]));
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(acc[j + 4]), __uint_as_float(acc[j + 5]));
+                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(acc[j + 6]), __uint_as_float(acc[j + 7]));
+                packed.x = *reinterpret_cast<uint32_t*>(&p0);
+                packed.y = *reinterpret_cast<uint32_t*>(&p1);
+                packed.z = *reinterpret_cast<uint32_t*>(&p2);
+                packed.w = *reinterpret_cast<uint32_t*>(&p3);
+                *reinterpret_cast<uint4*>(dst + j) = packed;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + c + j < n) dst[j] = __float2bfloat16_rn(__uint_as_float(acc[j]));
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown: everyone meets, the allocating warp frees the tensor memory ---------------
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BLOCK_N));
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicOr(err, OMNIA_ERR_TIMEOUT);
+}
+
+// ---- host side ---------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+  static EncodeTiled fn = nullptr;
+  if (fn == nullptr) {
+    void* symbol = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(symbol);
+  }
+  return fn;
+}
+
+// A [rows, k] bfloat16 row-major matrix as a 2-D tensor map with boxes of 64 x box_rows, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
+  EncodeTiled encode = encode_tiled();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)k * sizeof(bf16)};
+  const cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BLOCK_N, int STAGES, int EPI>
+int launch(const void* a, const void* w, void* out, int m, int n, int k, int pair_offset, float multiplier,
+           float cap, int* err, cudaStream_t stream) {
+  CUtensorMap map_a, map_b;
+  const int b_box = EPI == EPI_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
+  if (!make_map(&map_a, a, m, k, BLOCK_M) || !make_map(&map_b, w, n, k, b_box)) return (int)cudaErrorInvalidValue;
+  constexpr size_t smem = (size_t)STAGES * (BLOCK_M + BLOCK_N) * BLOCK_K * sizeof(bf16) + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BLOCK_N, STAGES, EPI>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int cols = EPI == EPI_SWIGLU ? pair_offset : n;
+  const int tile_cols = EPI == EPI_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
+  dim3 grid((cols + tile_cols - 1) / tile_cols, (m + BLOCK_M - 1) / BLOCK_M);
+  gemm_tcgen05_kernel<BLOCK_N, STAGES, EPI><<<grid, THREADS, smem, stream>>>(map_a, map_b, out, m, n, k, pair_offset,
+                                                                            multiplier, cap, err);
+  return OMNIA_LAUNCH_RESULT();
+}
+
+}  // namespace
+
+// epilogue: 0 store bfloat16 [m, n]; 1 SwiGLU, w = [gate rows | up rows] with n = 2 * inner,
+// out bfloat16 [m, inner]; 2 soft cap, out float32 [m, n]. a and w must be 16-byte aligned and
+// k a multiple of 8 (rows of both matrices start on 16 bytes).
+extern "C" int omnia_gemm_tcgen05(const void* a, const void* w, void* out, int m, int n, int k, int epilogue,
+                                  float multiplier, float cap, int* err, cudaStream_t stream) {
+  if (m == 0 || n == 0) return 0;
+  if (k <= 0 || k % 8 != 0 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorInvalidValue;
+  if (epilogue == EPI_SWIGLU) {
+    if (n % 2) return (int)cudaErrorInvalidValue;
+    return launch<256, 4, EPI_SWIGLU>(a, w, out, m, n, k, n / 2, 1.f, 0.f, err, stream);
+  }
+  if (epilogue == EPI_SOFTCAP) return launch<256, 4, EPI_SOFTCAP>(a, w, out, m, n, k, 0, multiplier, cap, err, stream);
+  if (epilogue != EPI_STORE) return (int)cudaErrorInvalidValue;
+  // Narrow or small problems take 128-wide tiles so that more blocks are in flight.
+  const long long wide_tiles = (long long)((n + 255) / 256) * ((m + 127) / 128);
+  if (wide_tiles >= 148) return launch<256, 4, EPI_STORE>(a, w, out, m, n, k, 0, 1.f, 0.f, err, stream);
+  return launch<128, 6, EPI_STORE>(a, w, out, m, n, k, 0, 1.f, 0.f, err, stream);
+}

@@ -21,7 +21,7 @@ from mlx_omnia_b200.parts.base import KVView, StepContext
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
 ERROR_BITS = {1: "a token id outside the embedding table", 2: "a cache slot outside the page pool",
-              4: "a block-table entry outside the page pool"}
+              4: "a block-table entry outside the page pool", 8: "a bounded wait inside a kernel ran out"}
 
 
 class KernelError(RuntimeError):
@@ -289,6 +289,25 @@ def _gemm_skinny(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilo
     return out
 
 
+USE_TCGEN05 = True
+"""bfloat16 products with more than SKINNY_ROWS rows run on this package's tcgen05 kernel;
+False hands them to the vendor library instead (kept for measuring one against the other)."""
+
+
+def _tensor_core(a: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (USE_TCGEN05 and a.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and a.is_cuda
+            and a.shape[0] > SKINNY_ROWS and a.shape[1] % 8 == 0 and a.is_contiguous() and weight.is_contiguous())
+
+
+def _gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, multiplier: float = 1.0,
+                  cap: float = 0.0) -> torch.Tensor:
+    fn = _function("gemm_tcgen05", "omnia_gemm_tcgen05",
+                   [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p])
+    _check(fn(_ptr(a), _ptr(weight), _ptr(out), a.shape[0], weight.shape[0], a.shape[1], epilogue, multiplier, cap,
+              _ptr(error_word(a.device)), _stream()), "gemm_tcgen05")
+    return out
+
+
 def _library_mm(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     if a.dtype == torch.float32 and (torch.backends.cuda.matmul.allow_tf32
                                       or torch.get_float32_matmul_precision() != "highest"):
@@ -304,6 +323,9 @@ def linear(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     if _skinny(a, weight):
         out = torch.empty(a.shape[0], weight.shape[0], dtype=a.dtype, device=a.device)
         return _gemm_skinny(a, weight, out, 0)
+    if _tensor_core(a, weight):
+        out = torch.empty(a.shape[0], weight.shape[0], dtype=a.dtype, device=a.device)
+        return _gemm_tcgen05(a, weight, out, 0)
     return _library_mm(a, weight)
 
 
@@ -312,6 +334,9 @@ def linear_swiglu(a: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
     if _skinny(a, gate_up):
         out = torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device)
         return _gemm_skinny(a, gate_up, out, 1)
+    if _tensor_core(a, gate_up):
+        out = torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device)
+        return _gemm_tcgen05(a, gate_up, out, 1)
     return swiglu(_library_mm(a, gate_up))
 
 
@@ -320,6 +345,9 @@ def linear_softcap(a: torch.Tensor, weight: torch.Tensor, multiplier: float, cap
     if _skinny(a, weight):
         out = torch.empty(a.shape[0], weight.shape[0], dtype=torch.float32, device=a.device)
         return _gemm_skinny(a, weight, out, 2, multiplier, cap or 0.0)
+    if _tensor_core(a, weight):
+        out = torch.empty(a.shape[0], weight.shape[0], dtype=torch.float32, device=a.device)
+        return _gemm_tcgen05(a, weight, out, 2, multiplier, cap or 0.0)
     return softcap(_library_mm(a, weight), multiplier, cap)
 
 

@@ -227,6 +227,23 @@ def test_skinny_products(ops, m, n, k):
         close(ops.linear_swiglu(a, w), g * torch.sigmoid(g) * u, torch.bfloat16)
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 128, 128), (17, 1000, 96), (200, 300, 136), (300, 778, 160),
+                                   (2048, 2048, 2048), (1000, 6144, 2048), (260, 2048, 6144), (130, 12288, 512)])
+def test_tcgen05_products(ops, m, n, k):
+    """The tcgen05/TMA kernel and its epilogues against float64 products of the same bfloat16
+    operands: whole tiles, ragged edges in m, n and k, wide and narrow tilings."""
+    a = rand(m, k, dtype=torch.bfloat16, seed=m)
+    w = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=n + k)
+    exact = a.double() @ w.double().t()
+    close(ops.linear(a, w), exact, torch.bfloat16)
+    ops.raise_on_error(a.device)
+    z = exact.float().bfloat16().double()
+    close(ops.linear_softcap(a, w, 3.0, 7.0), 7.0 * torch.tanh(z * 3.0 / 7.0), torch.bfloat16)
+    g, u = z[:, : n // 2], z[:, n // 2:]
+    close(ops.linear_swiglu(a, w), g * torch.sigmoid(g) * u, torch.bfloat16)
+    ops.raise_on_error(a.device)
+
+
 def test_sampling(ops):
     vocab, rows = 1531, 6
     logits = rand(rows, vocab, scale=2.0, seed=9)
