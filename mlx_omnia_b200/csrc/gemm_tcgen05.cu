@@ -3,16 +3,18 @@
 // memory, one elected thread issues tcgen05.mma with the accumulator in tensor memory,
 // and four warps read the accumulator back with tcgen05.ld for the epilogue.
 //
-// One block computes one 128 x BLOCK_N tile of the output (BLOCK_N = 256, or 128 for narrow
-// problems) over all of k in steps of 64, through a ring of STAGES shared-memory stages:
+// Blocks are persistent (one per SM) and take 128 x BLOCK_N tiles of the output round-robin
+// (BLOCK_N = 256, or 128 for narrow problems), each over all of k in steps of 64, through a
+// ring of STAGES shared-memory stages and two accumulators in tensor memory, so the epilogue
+// of one tile runs while the next tile is being multiplied:
 //   warp 0   producer: waits for a free stage, arms its "full" barrier with the byte count
 //            and issues the two TMA loads (rows beyond m or n and columns beyond k are
 //            zero-filled by the TMA unit);
-//   warp 1   allocates tensor memory, then its elected lane waits for a full stage and issues
-//            four MMAs (k = 16 each); tcgen05.commit frees the stage when they have read it,
-//            and after the last step signals "accumulator ready";
+//   warp 1   allocates tensor memory, then its elected lane waits for a drained accumulator and
+//            for each full stage issues four MMAs (k = 16 each); tcgen05.commit frees the
+//            stage when they have read it, and after the last step signals "accumulator full";
 //   warps 2-5  wait for that signal, read their 32 accumulator rows 32 columns at a time,
-//            apply the epilogue and store.
+//            apply the epilogue, store, and signal "accumulator empty".
 // Epilogues: 0 store bfloat16; 1 SwiGLU: the B tile holds 128 gate rows and the matching
 // 128 up rows of w, the block stores silu(gate) * up (BLOCK_N 256 only); 2 soft cap to float32.
 //
@@ -120,35 +122,39 @@ template <int BLOCK_N, int STAGES, int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     void* __restrict__ out, int m, int n, int k, int pair_offset, float multiplier,
-                    float cap, int* err) {
+                    float cap, int m_tiles, int n_tiles, int* err) {
   constexpr uint32_t A_BYTES = BLOCK_M * BLOCK_K * sizeof(bf16);
   constexpr uint32_t B_BYTES = BLOCK_N * BLOCK_K * sizeof(bf16);
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TILE_COLS = EPI == EPI_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
-  // bars[0..S) full, bars[S..2S) empty, bars[2S] accumulator ready
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+  // bars: [0, S) stage full, [S, 2S) stage empty, [2S, 2S+2) accumulator full, [2S+2, 2S+4) accumulator empty
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * BLOCK_M;
-  const int n0 = blockIdx.x * (EPI == EPI_SWIGLU ? BLOCK_N / 2 : BLOCK_N);
   const int k_blocks = (k + BLOCK_K - 1) / BLOCK_K;
-  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), ready = smem_u32(bars + 2 * STAGES);
+  const int total_tiles = m_tiles * n_tiles;
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+  const uint32_t acc_full0 = smem_u32(bars + 2 * STAGES), acc_empty0 = smem_u32(bars + 2 * STAGES + 2);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
-    mbar_init(ready, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full0 + 8 * b, 1);
+      mbar_init(acc_empty0 + 8 * b, 4);  // one arrival per epilogue warp
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
-                 "r"((uint32_t)BLOCK_N));
+                 "r"((uint32_t)(2 * BLOCK_N)));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -156,29 +162,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_holder;
 
+  // Tiles are dealt round-robin; consecutive tiles share the same columns of the output (the
+  // same rows of w), so blocks running side by side read the same weight tile out of L2.
   if (warp == 0) {
     // ---- producer ----------------------------------------------------------------------
     if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < k_blocks; ++kb) {
-        const int s = kb % STAGES;
-        if (kb >= STAGES && !mbar_wait(empty0 + 8 * s, ((kb / STAGES) - 1) & 1, abort_flag)) break;
-        const uint32_t a_dst = smem_u32(tiles + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
-        mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-        tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * BLOCK_K, m0);
-        if (EPI == EPI_SWIGLU) {
-          tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BLOCK_K, n0);
-          tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, kb * BLOCK_K, pair_offset + n0);
-        } else {
-          tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BLOCK_K, n0);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * BLOCK_M, n0 = (tile / m_tiles) * TILE_COLS;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          const uint32_t a_dst = smem_u32(tiles + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
+          mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * BLOCK_K, m0);
+          if (EPI == EPI_SWIGLU) {
+            tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BLOCK_K, n0);
+            tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, kb * BLOCK_K, pair_offset + n0);
+          } else {
+            tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BLOCK_K, n0);
+          }
         }
-        issued = kb + 1;
       }
       if (*abort_flag) {
         // Giving up: let the loads already issued land before the block's memory goes away.
-        for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
-          const int s = kb % STAGES;
-          for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(full0 + 8 * s, (kb / STAGES) & 1); ++i) {
+        for (uint32_t back = 0; back < (uint32_t)STAGES && back < it; ++back) {
+          const uint32_t j = it - 1 - back;
+          for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(full0 + 8 * (j % STAGES), (j / STAGES) & 1); ++i) {
           }
         }
       }
@@ -187,31 +199,44 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // ---- MMA issuer ----------------------------------------------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc(BLOCK_M, BLOCK_N);
+      uint32_t it = 0, local = 0;
       bool ok = true;
-      for (int kb = 0; kb < k_blocks && ok; ++kb) {
-        const int s = kb % STAGES;
-        ok = mbar_wait(full0 + 8 * s, (kb / STAGES) & 1, abort_flag);
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+        const uint32_t buf = local & 1;
+        ok = mbar_wait(acc_empty0 + 8 * buf, ((local >> 1) & 1) ^ 1, abort_flag);  // the epilogue has drained it
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+        const uint32_t acc = tmem_base + buf * BLOCK_N;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
-          const uint64_t a_desc = umma_desc(a_addr + kk * UMMA_K * sizeof(bf16));
-          const uint64_t b_desc = umma_desc(b_addr + kk * UMMA_K * sizeof(bf16));
-          umma(tmem_base, a_desc, b_desc, idesc, (kb | kk) != 0);
+          for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+            const uint64_t a_desc = umma_desc(a_addr + kk * UMMA_K * sizeof(bf16));
+            const uint64_t b_desc = umma_desc(b_addr + kk * UMMA_K * sizeof(bf16));
+            umma(acc, a_desc, b_desc, idesc, (kb | kk) != 0);
+          }
+          umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
         }
-        umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
+        if (ok) umma_commit(acc_full0 + 8 * buf);
       }
-      if (ok) umma_commit(ready);
     }
   } else {
     // ---- epilogue (warps 2..5 own accumulator rows 32 * (warp % 4) .. + 31) -------------------
     const int quarter = warp & 3;
-    const int row = m0 + quarter * 32 + lane;
-    const bool ok = mbar_wait(ready, 0, abort_flag);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
-      const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    uint32_t local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+      const int m0 = (tile % m_tiles) * BLOCK_M, n0 = (tile / m_tiles) * TILE_COLS;
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t buf = local & 1;
+      ok = mbar_wait(acc_full0 + 8 * buf, (local >> 1) & 1, abort_flag);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t lane_base = tmem_base + buf * BLOCK_N + ((uint32_t)(quarter * 32) << 16);
       if (EPI == EPI_SWIGLU) {
         bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)row * pair_offset + n0;
 #pragma unroll 1
@@ -229,7 +254,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 // Both halves are rounded to bfloat16 first, as a separate product would round them.
                 const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gate[j + e])));
                 const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[j + e])));
-                v[e] = g / (1.f + expf(-g)) * u;
+                v[e] = g / (1.f + __expf(-g)) * u;
               }
               const int col = n0 + c + j;
               if (col + 1 < pair_offset && (pair_offset & 1) == 0) {
@@ -280,6 +305,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
+      // This warp has read its rows of the accumulator: hand the buffer back to the MMA warp.
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
     }
   }
 
@@ -287,7 +316,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BLOCK_N));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BLOCK_N)));
   }
   if (threadIdx.x == 0 && *abort_flag) atomicOr(err, OMNIA_ERR_TIMEOUT);
 }
@@ -339,9 +368,18 @@ int launch(const void* a, const void* w, void* out, int m, int n, int k, int pai
   }
   const int cols = EPI == EPI_SWIGLU ? pair_offset : n;
   const int tile_cols = EPI == EPI_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
-  dim3 grid((cols + tile_cols - 1) / tile_cols, (m + BLOCK_M - 1) / BLOCK_M);
-  gemm_tcgen05_kernel<BLOCK_N, STAGES, EPI><<<grid, THREADS, smem, stream>>>(map_a, map_b, out, m, n, k, pair_offset,
-                                                                            multiplier, cap, err);
+  const int n_tiles = (cols + tile_cols - 1) / tile_cols, m_tiles = (m + BLOCK_M - 1) / BLOCK_M;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  const long long total = (long long)n_tiles * m_tiles;
+  const int grid = (int)(total < sm_count ? total : sm_count);  // one persistent block per SM
+  gemm_tcgen05_kernel<BLOCK_N, STAGES, EPI><<<grid, THREADS, smem, stream>>>(
+      map_a, map_b, out, m, n, k, pair_offset, multiplier, cap, m_tiles, n_tiles, err);
   return OMNIA_LAUNCH_RESULT();
 }
 
@@ -360,8 +398,11 @@ extern "C" int omnia_gemm_tcgen05(const void* a, const void* w, void* out, int m
   }
   if (epilogue == EPI_SOFTCAP) return launch<256, 4, EPI_SOFTCAP>(a, w, out, m, n, k, 0, multiplier, cap, err, stream);
   if (epilogue != EPI_STORE) return (int)cudaErrorInvalidValue;
-  // Narrow or small problems take 128-wide tiles so that more blocks are in flight.
-  const long long wide_tiles = (long long)((n + 255) / 256) * ((m + 127) / 128);
-  if (wide_tiles >= 148) return launch<256, 4, EPI_STORE>(a, w, out, m, n, k, 0, 1.f, 0.f, err, stream);
+  // 256-wide tiles do twice the work per byte staged; 128-wide tiles win only when they fill
+  // SMs that the wide tiling would leave idle. Cost in units of one wide tile per round of 148.
+  const long long m_tiles = (m + 127) / 128;
+  const long long wide_rounds = (((n + 255) / 256) * m_tiles + 147) / 148;
+  const long long narrow_rounds = (((n + 127) / 128) * m_tiles + 147) / 148;
+  if (wide_rounds * 100 <= narrow_rounds * 65) return launch<256, 4, EPI_STORE>(a, w, out, m, n, k, 0, 1.f, 0.f, err, stream);
   return launch<128, 6, EPI_STORE>(a, w, out, m, n, k, 0, 1.f, 0.f, err, stream);
 }
