@@ -1,0 +1,511 @@
+// Paged causal prefill attention in bfloat16 on the 5th-generation tensor cores, compiled for
+// one head size and one group size:
+//   -DHEAD_DIM=64|128   -DGROUP=g (query heads per key/value head, g <= 16)
+//
+// A block owns up to 128 rows, each row a (token, query head of the group) pair of ONE
+// key/value head and one request, and walks the visible keys in tiles of 128:
+//   S = Q K^T   tcgen05.mma (M 128, N 128) over the head size, accumulator in tensor memory
+//   softmax     four warps, one thread per row: tcgen05.ld the scores, mask, running maximum and
+//               sum in float32, exp2, P rounded to bfloat16 into shared memory (128-byte swizzle)
+//   O += P V    tcgen05.mma (M 128, N head size) over the tile's keys, accumulator in tensor memory;
+//               when a row's maximum grows its accumulator is rescaled in tensor memory first
+// Warp 0 feeds the ring of K/V stages with TMA, one box of 16 keys x 64 dims per page group (the
+// block table is read there; page sizes must be multiples of 16); warp 1 issues the MMAs; warps
+// 2-5 are the softmax and the epilogue (normalise, optional sigmoid gate, store). The score
+// accumulator is double-buffered, so S of the next tile is computed while this tile's softmax runs.
+// Key groups whose page is not loaded (beyond the request, or given back behind a window) are
+// masked in S and skipped in P V, so stale shared memory never reaches the arithmetic.
+//
+// Every wait on a barrier is bounded: when the bound is hit the block raises OMNIA_ERR_TIMEOUT
+// in the error word, every role leaves its loop, the producer waits (bounded) for loads in
+// flight, the block frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define OMNIA_ERR_TIMEOUT 8
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 128
+#endif
+#ifndef GROUP
+#define GROUP 2
+#endif
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int D = HEAD_DIM;
+static_assert(D == 64 || D == 128, "the tcgen05 attention kernel takes head sizes 64 and 128");
+static_assert(GROUP >= 1 && GROUP <= 16, "group size must be 1..16");
+constexpr int DH = D / 64;                 // 64-wide halves of a head
+constexpr int BM = 128, BN = 128;
+constexpr int TOKENS = BM / GROUP;         // tokens per block
+constexpr int ROWS = TOKENS * GROUP;       // rows in use (<= 128)
+constexpr int KV_STAGES = 2;
+constexpr int THREADS = 192;
+constexpr uint32_t HALF_BYTES = 128 * 128;           // 128 rows of 128 bytes
+constexpr uint32_t Q_BYTES = DH * HALF_BYTES;
+constexpr uint32_t P_BYTES = 2 * HALF_BYTES;         // 128 keys = two 64-key halves
+constexpr uint32_t K_BYTES = DH * HALF_BYTES, V_BYTES = DH * HALF_BYTES;
+constexpr uint32_t STAGE_BYTES = K_BYTES + V_BYTES;
+constexpr uint32_t GROUP_BYTES = 16 * 128;           // one TMA box: 16 keys x 64 dims
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t S_COL = 0, O_COL = 256;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
+// Matrix descriptors of 128-byte-swizzled tiles (rows of 128 bytes, 8-row groups 1024 bytes apart).
+// K-major: the contraction index runs along the 128-byte row. MN-major: the other index does, and
+// a second 64-wide half of that index lies `leading` bytes away.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+  return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t leading) {
+  return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((leading >> 4) & 0x3FFF) << 16) |
+         ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// kind::f16: float32 accumulator, bfloat16 operands, A K-major, B K-major or MN-major.
+__host__ __device__ constexpr uint32_t idesc(int m, int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t instr, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(instr), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t addr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(addr));
+}
+__device__ __forceinline__ void tmem_store32(uint32_t addr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+}  // namespace
+
+// grid (blocks of the work list, nkv); 192 threads. work[b] = (request, first token of the block
+// among the request's tokens of this step).
+__global__ void __launch_bounds__(THREADS)
+attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                                 const int* __restrict__ block_table, const int* __restrict__ cu_seqlens,
+                                 const int* __restrict__ seq_lens, const int* __restrict__ work,
+                                 const bf16* __restrict__ gate, int gate_stride, bf16* __restrict__ out,
+                                 int max_pages, int num_pages, int nq, int nkv, int page_size, int window,
+                                 float scale, int* err) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* q_s = base;
+  unsigned char* p_s = q_s + Q_BYTES;
+  unsigned char* kv_s = p_s + P_BYTES;  // KV_STAGES x (K, V)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + KV_STAGES * STAGE_BYTES);
+  // bars: 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5,6 s_full | 7 p_full | 8 o_done
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  volatile uint32_t* group_mask = reinterpret_cast<volatile uint32_t*>(tmem_holder + 2);  // [KV_STAGES]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq = work[2 * blockIdx.x], tok0 = work[2 * blockIdx.x + 1];
+  const int kvh = blockIdx.y;
+  const int q_begin = cu_seqlens[seq], q_len = cu_seqlens[seq + 1] - q_begin;
+  const int pos0 = seq_lens[seq] - q_len + tok0;      // position of the block's first token
+  const int tokens = min(TOKENS, q_len - tok0);
+  const int rows = tokens * GROUP;
+  const int last = pos0 + tokens - 1;                                   // last key any row sees
+  const int first = window > 0 ? max(0, pos0 - window + 1) : 0;         // first key any row sees
+  const int tile0 = first / BN, n_tiles = last / BN - tile0 + 1;
+
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t q_full = bar0, kv_full0 = bar0 + 8, kv_empty0 = bar0 + 24, s_full0 = bar0 + 40,
+                 p_full = bar0 + 56, o_done = bar0 + 64;
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(kv_full0 + 8 * s, 1);
+      mbar_init(kv_empty0 + 8 * s, 1);
+      mbar_init(s_full0 + 8 * s, 1);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(o_done, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
+                 "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ---- producer: Q once, then K/V tiles through the ring -------------------------------------
+    if (lane == 0) {
+      mbar_expect_tx(q_full, DH * ROWS * 128);
+      for (int h = 0; h < DH; ++h)
+        tma_load_3d(smem_u32(q_s) + h * HALF_BYTES, &map_q, q_full, h * 64, kvh * GROUP, q_begin + tok0);
+    }
+    const int* table = block_table + (size_t)seq * max_pages;
+    bool ok = true;
+    int issued = 0;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j % KV_STAGES;
+      if (lane == 0) ok = mbar_wait(kv_empty0 + 8 * s, ((j / KV_STAGES) & 1) ^ 1, abort_flag);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      // Lanes 0..7 own the tile's eight groups of 16 keys.
+      const int pos = (tile0 + j) * BN + lane * 16;
+      bool load = lane < 8 && pos <= last && pos + 15 >= first;
+      int page = -1;
+      if (load) {
+        page = table[pos / page_size];
+        if (page < 0 || page >= num_pages) {
+          // A page behind the window may have been given back; one the block really reads may not.
+          if (pos >= first) atomicOr(err, OMNIA_ERR_PAGE);
+          load = false;
+        }
+      }
+      const uint32_t mask = __ballot_sync(0xffffffffu, load) & 0xffu;
+      if (lane == 0) {
+        group_mask[s] = mask;
+        mbar_expect_tx(kv_full0 + 8 * s, __popc(mask) * 2 * DH * GROUP_BYTES);
+      }
+      __syncwarp();
+      if (load) {
+        const int y = (((page * 2) * nkv + kvh) * page_size) + pos % page_size;   // the key rows
+        const int yv = y + nkv * page_size;                                       // the value rows
+        const uint32_t k_dst = smem_u32(kv_s + s * STAGE_BYTES) + lane * GROUP_BYTES;
+        for (int h = 0; h < DH; ++h) {
+          tma_load_2d(k_dst + h * HALF_BYTES, &map_kv, kv_full0 + 8 * s, h * 64, y);
+          tma_load_2d(k_dst + K_BYTES + h * HALF_BYTES, &map_kv, kv_full0 + 8 * s, h * 64, yv);
+        }
+      }
+      issued = j + 1;
+    }
+    if (lane == 0 && *abort_flag) {
+      for (int j = max(0, issued - KV_STAGES); j < issued; ++j)
+        for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(kv_full0 + 8 * (j % KV_STAGES), (j / KV_STAGES) & 1); ++i) {
+        }
+      for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(q_full, 0); ++i) {
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ------------------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t instr_s = idesc(BM, BN, false), instr_o = idesc(BM, D, true);
+      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      auto scores = [&](int j) {  // S[j & 1] = Q K_j^T
+        const uint32_t k_addr = smem_u32(kv_s + (j % KV_STAGES) * STAGE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * HALF_BYTES + (kk % 4) * 32;
+          umma(tmem_base + S_COL + (j & 1) * BN, desc_k_major(q_addr + off), desc_k_major(k_addr + off), instr_s, kk != 0);
+        }
+        umma_commit(s_full0 + 8 * (j & 1));
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(kv_full0, 0, abort_flag);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        scores(0);
+      }
+      uint32_t accumulate = 0;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) {
+          ok = mbar_wait(kv_full0 + 8 * ((j + 1) % KV_STAGES), ((j + 1) / KV_STAGES) & 1, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          scores(j + 1);
+        }
+        ok = mbar_wait(p_full, j & 1, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int s = j % KV_STAGES;
+        const uint32_t v_addr = smem_u32(kv_s + s * STAGE_BYTES) + K_BYTES;
+        const uint32_t mask = group_mask[s];
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          if (!(mask & (1u << kk))) continue;  // keys never loaded: their P is zero, their V is stale
+          umma(tmem_base + O_COL, desc_k_major(p_addr + (kk / 4) * HALF_BYTES + (kk % 4) * 32),
+               desc_mn_major(v_addr + kk * GROUP_BYTES, HALF_BYTES), instr_o, accumulate);
+          accumulate = 1;
+        }
+        umma_commit(kv_empty0 + 8 * s);
+        umma_commit(o_done);
+      }
+    }
+  } else {
+    // ---- softmax and epilogue: one thread per row ---------------------------------------------------
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const bool live = row < rows;
+    const int pos = pos0 + row / GROUP;
+    const int row_hi = live ? pos : -1;
+    const int row_lo = live ? (window > 0 ? max(0, pos - window + 1) : 0) : 0;
+    const uint32_t lane_field = (uint32_t)(quarter * 32) << 16;
+    const float sl2 = scale * LOG2E;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int key0 = (tile0 + j) * BN;
+      ok = mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t s_addr = tmem_base + lane_field + S_COL + (j & 1) * BN;
+      // Which keys of the tile this row sees; a tile that every row sees whole needs no masks.
+      const int lo = max(row_lo - key0, 0), hi = min(row_hi - key0, BN - 1);  // visible columns [lo, hi]
+      // Pass 1: the row's maximum.
+      float tile_max = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t v[32];
+        tmem_load32(s_addr + c, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = c + i;
+          if (col >= lo && col <= hi) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
+        }
+      }
+      const float m_new = fmaxf(m, tile_max);
+      const float offset = m_new == -INFINITY ? 0.f : m_new * sl2;
+      const float alpha = (m == -INFINITY || m_new == m) ? 1.f : exp2f(m * sl2 - offset);
+      m = m_new;
+      // The previous tile's P V must be done before O is rescaled or P is overwritten.
+      if (j > 0) {
+        ok = mbar_wait(o_done, (j - 1) & 1, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t v[32];
+            tmem_load32(tmem_base + lane_field + O_COL + c, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_store32(tmem_base + lane_field + O_COL + c, v);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+      }
+      l *= alpha;
+      // Pass 2: P = exp2(s * scale * log2e - offset), rounded to bfloat16, into swizzled shared memory.
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t v[32];
+        tmem_load32(s_addr + c, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = c + i + e;
+            p[e] = (col >= lo && col <= hi) ? exp2f(__uint_as_float(v[i + e]) * sl2 - offset) : 0.f;
+            sum += p[e];
+          }
+          packed[i / 2] = pack_bf16(p[0], p[1]);
+        }
+        // Columns c .. c+31 are chunks (c % 64) / 8 .. + 3 of half c / 64; chunk x of row r lives at x ^ (r % 8).
+        unsigned char* row_base = p_s + (c / 64) * HALF_BYTES + row * 128;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const int chunk = ((c % 64) / 8 + x) ^ (row & 7);
+          *reinterpret_cast<uint4*>(row_base + chunk * 16) =
+              make_uint4(packed[4 * x], packed[4 * x + 1], packed[4 * x + 2], packed[4 * x + 3]);
+        }
+      }
+      l += sum;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core (async proxy)
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(p_full);
+    }
+    // Epilogue: O / l, gate, store.
+    if (ok) ok = mbar_wait(o_done, (n_tiles - 1) & 1, abort_flag);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const size_t token = (size_t)(q_begin + tok0 + row / GROUP);
+      const int head = kvh * GROUP + row % GROUP;
+      bf16* dst = out + (token * nq + head) * D;
+      const bf16* gp = gate ? gate + token * gate_stride + (size_t)head * D : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t v[32];
+        tmem_load32(tmem_base + lane_field + O_COL + c, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (!live) continue;
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
+            float a = __uint_as_float(v[i + e]) * inv, b = __uint_as_float(v[i + e + 1]) * inv;
+            if (gp) {
+              a *= 1.f / (1.f + expf(-__bfloat162float(gp[c + i + e])));
+              b *= 1.f / (1.f + expf(-__bfloat162float(gp[c + i + e + 1])));
+            }
+            w[e / 2] = pack_bf16(a, b);
+          }
+          *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicOr(err, OMNIA_ERR_TIMEOUT);
+}
+
+// ---- host side -------------------------------------------------------------------------------
+
+namespace {
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+  static EncodeTiled fn = nullptr;
+  if (fn == nullptr) {
+    void* symbol = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(symbol);
+  }
+  return fn;
+}
+
+}  // namespace
+
+extern "C" int omnia_attention_tcgen05_info(int* head_dim, int* group, int* tokens_per_block) {
+  *head_dim = HEAD_DIM;
+  *group = GROUP;
+  *tokens_per_block = TOKENS;
+  return 0;
+}
+
+// q: [tokens, nq, D]; pages: [num_pages, 2, nkv, page_size, D]; page_size a multiple of 16.
+extern "C" int omnia_attention_prefill_tcgen05(const void* q, int tokens, const void* pages, const int* block_table,
+                                               const int* cu_seqlens, const int* seq_lens, const int* work,
+                                               int blocks, const void* gate, int gate_stride, void* out,
+                                               int max_pages, int num_pages, int nq, int nkv, int page_size,
+                                               int window, float scale, int* err, cudaStream_t stream) {
+  if (blocks == 0) return 0;
+  if (nq != nkv * GROUP || page_size % 16 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)pages & 15))
+    return (int)cudaErrorInvalidValue;
+  EncodeTiled encode = encode_tiled();
+  if (encode == nullptr) return (int)cudaErrorNotSupported;
+  CUtensorMap map_q, map_kv;
+  {
+    const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)nq, (cuuint64_t)tokens};
+    const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)nq * D * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)GROUP, (cuuint32_t)TOKENS};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    if (encode(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return (int)cudaErrorInvalidValue;
+  }
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)num_pages * 2 * nkv * page_size};
+    const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    const cuuint32_t box[2] = {64, 16};
+    const cuuint32_t elem[2] = {1, 1};
+    if (encode(&map_kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return (int)cudaErrorInvalidValue;
+  }
+  constexpr size_t smem = Q_BYTES + P_BYTES + KV_STAGES * STAGE_BYTES + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  attention_prefill_tcgen05_kernel<<<dim3(blocks, nkv), THREADS, smem, stream>>>(
+      map_q, map_kv, block_table, cu_seqlens, seq_lens, work, (const bf16*)gate, gate_stride, (bf16*)out,
+      max_pages, num_pages, nq, nkv, page_size, window, scale, err);
+  return OMNIA_LAUNCH_RESULT();
+}

@@ -176,17 +176,27 @@ def tiled_attention_supported(dtype: torch.dtype, nq: int, nkv: int, d: int) -> 
 
 
 def _prefill_work(step: StepContext, tokens_per_block: int, device: torch.device) -> torch.Tensor:
-    """(request, first token) of every block of `tokens_per_block` query tokens; built once
-    per step and shared by all layers."""
+    """(request, first token) of every block of `tokens_per_block` query tokens, the blocks
+    that see the most keys first (they run longest); built once per step and shared by all
+    layers."""
     if step.workspace is None:
         step.workspace = {}
     key = ("prefill_work", tokens_per_block)
     work = step.workspace.get(key)
     if work is None:
         items = [(s, t0) for s, n in enumerate(step.q_lens) for t0 in range(0, n, tokens_per_block)]
+        if step.seq_lens_host:
+            items.sort(key=lambda item: -(step.seq_lens_host[item[0]] - step.q_lens[item[0]] + item[1]))
         work = torch.tensor(items, dtype=torch.int32).pin_memory().to(device, non_blocking=True)
         step.workspace[key] = work
     return work
+
+
+def tcgen05_attention_supported(dtype: torch.dtype, nq: int, nkv: int, d: int, page_size: int) -> bool:
+    """The tcgen05 prefill kernel takes bfloat16, head sizes 64 and 128, pages of a multiple
+    of 16 tokens and up to 16 query heads per key/value head."""
+    return (dtype == torch.bfloat16 and d in (64, 128) and page_size % 16 == 0 and nq % nkv == 0
+            and nq // nkv <= 16)
 
 
 def paged_attention(q: torch.Tensor, kv: KVView, step: StepContext, scale: float,
@@ -196,8 +206,9 @@ def paged_attention(q: torch.Tensor, kv: KVView, step: StepContext, scale: float
     columns start at `gate_col`) is given.  -> [tokens, nq * d]
 
     bfloat16 with a supported head size runs on the tensor-core kernels: the split-key
-    decode kernel when every request brings one token, the tiled prefill kernel
-    otherwise. Other cases (the 32-bit path among them) run on the generic kernel."""
+    decode kernel when every request brings one token; otherwise the tcgen05 prefill kernel
+    (head sizes 64 and 128, pages of a multiple of 16) or the mma.sync prefill kernel. Other
+    cases (the 32-bit path among them) run on the generic kernel."""
     tokens, nq, d = q.shape
     nkv = kv.pages.shape[2]
     out = torch.empty(tokens, nq * d, dtype=q.dtype, device=q.device)
@@ -232,6 +243,15 @@ def paged_attention(q: torch.Tensor, kv: KVView, step: StepContext, scale: float
                   gate_stride,
                   _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size, kv.window or 0, scale, err, _stream()),
                "attention_decode")
+        return out
+    if USE_TCGEN05 and tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):
+        work = _prefill_work(step, 128 // (nq // nkv), q.device)
+        fn = _function("attention_tcgen05", "omnia_attention_prefill_tcgen05",
+                       [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p], defines)
+        _check(fn(_ptr(q), tokens, _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.seq_lens),
+                  _ptr(work), work.shape[0], gate_ptr, gate_stride, _ptr(out), max_pages, num_pages, nq, nkv,
+                  kv.page_size, kv.window or 0, scale, err, _stream()), "attention_prefill_tcgen05")
         return out
     tokens_per_block = 64 // (nq // nkv)
     work = _prefill_work(step, tokens_per_block, q.device)
