@@ -3,8 +3,9 @@
 //   -DHEAD_DIM=64|128   -DGROUP=g (query heads per key/value head, g <= 16)
 //
 // A block owns up to 128 rows, each row a (token, query head of the group) pair of ONE
-// key/value head and one request, and walks the visible keys in tiles of 128:
-//   S = Q K^T   tcgen05.mma (M 128, N 128) over the head size, accumulator in tensor memory
+// key/value head and one request, and walks the visible keys in tiles of 64 (two blocks share an SM,
+// so one block's softmax overlaps the other's matrix products):
+//   S = Q K^T   tcgen05.mma (M 128, N 64) over the head size, accumulator in tensor memory
 //   softmax     four warps, one thread per row: tcgen05.ld the scores, mask, running maximum and
 //               sum in float32, exp2, P rounded to bfloat16 into shared memory (128-byte swizzle)
 //   O += P V    tcgen05.mma (M 128, N head size) over the tile's keys, accumulator in tensor memory;
@@ -40,20 +41,21 @@ constexpr int D = HEAD_DIM;
 static_assert(D == 64 || D == 128, "the tcgen05 attention kernel takes head sizes 64 and 128");
 static_assert(GROUP >= 1 && GROUP <= 16, "group size must be 1..16");
 constexpr int DH = D / 64;                 // 64-wide halves of a head
-constexpr int BM = 128, BN = 128;
+constexpr int BM = 128, BN = 64;      // rows per block, keys per tile
 constexpr int TOKENS = BM / GROUP;         // tokens per block
 constexpr int ROWS = TOKENS * GROUP;       // rows in use (<= 128)
 constexpr int KV_STAGES = 2;
 constexpr int THREADS = 192;
 constexpr uint32_t HALF_BYTES = 128 * 128;           // 128 rows of 128 bytes
 constexpr uint32_t Q_BYTES = DH * HALF_BYTES;
-constexpr uint32_t P_BYTES = 2 * HALF_BYTES;         // 128 keys = two 64-key halves
-constexpr uint32_t K_BYTES = DH * HALF_BYTES, V_BYTES = DH * HALF_BYTES;
+constexpr uint32_t P_BYTES = HALF_BYTES;             // 128 rows x 64 keys
+constexpr uint32_t TILE_HALF = BN * 128;             // 64 keys of 128 bytes
+constexpr uint32_t K_BYTES = DH * TILE_HALF, V_BYTES = DH * TILE_HALF;
 constexpr uint32_t STAGE_BYTES = K_BYTES + V_BYTES;
 constexpr uint32_t GROUP_BYTES = 16 * 128;           // one TMA box: 16 keys x 64 dims
-constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t S_COL = 0, O_COL = 256;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr uint32_t TMEM_COLS = 256;                  // two blocks share an SM's 512 columns
+constexpr uint32_t S_COL = 0, O_COL = 128;
+constexpr uint32_t WAIT_LIMIT = 1u << 20;
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -70,20 +72,26 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"  // sleeps up to the hint (ns)
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(2000u)
       : "memory");
   return ok != 0;
 }
+// Bounded wait; false when the block is giving up (its own limit, or another role's).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
     if (mbar_try(bar, parity)) return true;
-    if (*abort_flag) return false;
+    if ((i & 63) == 63 && *abort_flag) return false;
   }
   *abort_flag = 1;
   return false;
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile(
@@ -152,11 +160,26 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+#ifdef ATTN_TIMING
+// Debug build only: nanosecond stamps of block (0, 0), read back with omnia_attention_timing.
+__device__ unsigned long long g_timing[8192];
+__device__ __forceinline__ void stamp(int slot) {
+  if (blockIdx.x == 0 && blockIdx.y == 0 && slot < 8192) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_timing[slot] = t;
+  }
+}
+#define STAMP(role, j, what) stamp(((j) * 4 + (what)) * 4 + (role))
+#else
+#define STAMP(role, j, what)
+#endif
+
 }  // namespace
 
 // grid (blocks of the work list, nkv); 192 threads. work[b] = (request, first token of the block
 // among the request's tokens of this step).
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                                  const int* __restrict__ block_table, const int* __restrict__ cu_seqlens,
                                  const int* __restrict__ seq_lens, const int* __restrict__ work,
@@ -164,13 +187,18 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  int max_pages, int num_pages, int nq, int nkv, int page_size, int window,
                                  float scale, int* err) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  unsigned char* q_s = base;
+  // The swizzled tiles need a base on 1024 bytes; the dynamic area starts on one (nothing static
+  // precedes it). Two blocks per SM leave no room for padding, so this is checked, not forced.
+  if (smem_u32(smem_raw) & 1023u) {
+    if (threadIdx.x == 0) atomicOr(err, OMNIA_ERR_TIMEOUT);
+    return;
+  }
+  unsigned char* q_s = smem_raw;
   unsigned char* p_s = q_s + Q_BYTES;
   unsigned char* kv_s = p_s + P_BYTES;  // KV_STAGES x (K, V)
   uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + KV_STAGES * STAGE_BYTES);
-  // bars: 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5,6 s_full | 7 p_full | 8 o_done
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 9);
+  // bars: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11 p_full | 12 o_done
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   volatile uint32_t* group_mask = reinterpret_cast<volatile uint32_t*>(tmem_holder + 2);  // [KV_STAGES]
 
@@ -186,13 +214,15 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int tile0 = first / BN, n_tiles = last / BN - tile0 + 1;
 
   const uint32_t bar0 = smem_u32(bars);
-  const uint32_t q_full = bar0, kv_full0 = bar0 + 8, kv_empty0 = bar0 + 24, s_full0 = bar0 + 40,
-                 p_full = bar0 + 56, o_done = bar0 + 64;
+  const uint32_t q_full = bar0, k_full0 = bar0 + 8, k_empty0 = bar0 + 24, v_full0 = bar0 + 40,
+                 v_empty0 = bar0 + 56, s_full0 = bar0 + 72, p_full = bar0 + 88, o_done = bar0 + 96;
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(kv_full0 + 8 * s, 1);
-      mbar_init(kv_empty0 + 8 * s, 1);
+      mbar_init(k_full0 + 8 * s, 1);
+      mbar_init(k_empty0 + 8 * s, 1);
+      mbar_init(v_full0 + 8 * s, 1);
+      mbar_init(v_empty0 + 8 * s, 1);
       mbar_init(s_full0 + 8 * s, 1);
     }
     mbar_init(p_full, 128);
@@ -217,46 +247,73 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       for (int h = 0; h < DH; ++h)
         tma_load_3d(smem_u32(q_s) + h * HALF_BYTES, &map_q, q_full, h * 64, kvh * GROUP, q_begin + tok0);
     }
+    // K and V tiles go through rings of their own, in the order the tensor core wants them:
+    // K0, K1, V0, K2, V1, ... A K slot is free again as soon as its scores are computed, so
+    // the next keys are on their way long before the MMA warp asks for them.
+    // Lane = group * DH + half: each of the tile's boxes (16 keys x 64 dims) is issued by its own lane.
     const int* table = block_table + (size_t)seq * max_pages;
+    if (lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kv) : "memory");
+    const int g = lane / DH, h = lane % DH;
+    const bool active = lane < (BN / 16) * DH;
+    // The page of this lane's group in tile t (-2: the group lies outside what the block reads).
+    // Page numbers are fetched a whole tile before they are used, so the table's latency is hidden.
+    auto lookup = [&](int t) {
+      const int pos = (tile0 + t) * BN + g * 16;
+      return (active && t < n_tiles && pos <= last && pos + 15 >= first) ? table[pos / page_size] : -2;
+    };
     bool ok = true;
-    int issued = 0;
-    for (int j = 0; j < n_tiles && ok; ++j) {
+    int k_issued = 0, v_issued = 0;
+    auto load_tile = [&](int j, int which, int page) {  // which: 0 keys, 1 values
       const int s = j % KV_STAGES;
-      if (lane == 0) ok = mbar_wait(kv_empty0 + 8 * s, ((j / KV_STAGES) & 1) ^ 1, abort_flag);
+      const uint32_t full = (which ? v_full0 : k_full0) + 8 * s, empty = (which ? v_empty0 : k_empty0) + 8 * s;
+      if (lane == 0) ok = mbar_wait(empty, ((j / KV_STAGES) & 1) ^ 1, abort_flag);
       ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-      // Lanes 0..7 own the tile's eight groups of 16 keys.
-      const int pos = (tile0 + j) * BN + lane * 16;
-      bool load = lane < 8 && pos <= last && pos + 15 >= first;
-      int page = -1;
-      if (load) {
-        page = table[pos / page_size];
-        if (page < 0 || page >= num_pages) {
-          // A page behind the window may have been given back; one the block really reads may not.
-          if (pos >= first) atomicOr(err, OMNIA_ERR_PAGE);
-          load = false;
-        }
+      if (!ok) return;
+      if (lane == 0) STAMP(0, j, which * 2);
+      const int pos = (tile0 + j) * BN + g * 16;
+      bool load = page != -2;
+      if (load && (page < 0 || page >= num_pages)) {
+        // A page behind the window may have been given back; one the block really reads may not.
+        if (pos >= first) atomicOr(err, OMNIA_ERR_PAGE);
+        load = false;
       }
-      const uint32_t mask = __ballot_sync(0xffffffffu, load) & 0xffu;
+      const uint32_t loaded = __ballot_sync(0xffffffffu, load);
       if (lane == 0) {
-        group_mask[s] = mask;
-        mbar_expect_tx(kv_full0 + 8 * s, __popc(mask) * 2 * DH * GROUP_BYTES);
+        if (which) {
+          uint32_t mask = 0;
+#pragma unroll
+          for (int x = 0; x < BN / 16; ++x) mask |= ((loaded >> (x * DH)) & 1u) << x;
+          group_mask[s] = mask;
+        }
+        mbar_expect_tx(full, __popc(loaded) * GROUP_BYTES);
       }
       __syncwarp();
       if (load) {
-        const int y = (((page * 2) * nkv + kvh) * page_size) + pos % page_size;   // the key rows
-        const int yv = y + nkv * page_size;                                       // the value rows
-        const uint32_t k_dst = smem_u32(kv_s + s * STAGE_BYTES) + lane * GROUP_BYTES;
-        for (int h = 0; h < DH; ++h) {
-          tma_load_2d(k_dst + h * HALF_BYTES, &map_kv, kv_full0 + 8 * s, h * 64, y);
-          tma_load_2d(k_dst + K_BYTES + h * HALF_BYTES, &map_kv, kv_full0 + 8 * s, h * 64, yv);
-        }
+        const int y = (((page * 2 + which) * nkv + kvh) * page_size) + pos % page_size;
+        const uint32_t dst = smem_u32(kv_s + s * STAGE_BYTES) + which * K_BYTES + h * TILE_HALF + g * GROUP_BYTES;
+        tma_load_2d(dst, &map_kv, full, h * 64, y);
       }
-      issued = j + 1;
+      if (lane == 0) STAMP(0, j, which * 2 + 1);
+      if (which) v_issued = j + 1; else k_issued = j + 1;
+    };
+    // K and V tiles go through rings of their own, in the order the tensor core wants them:
+    // K0, K1, V0, K2, V1, ... A K slot is free again as soon as its scores are computed, so
+    // the next keys are on their way long before the MMA warp asks for them.
+    int page_cur = lookup(0), page_next = lookup(1);
+    load_tile(0, 0, page_cur);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int page_after = lookup(j + 2);
+      if (j + 1 < n_tiles) load_tile(j + 1, 0, page_next);
+      if (ok) load_tile(j, 1, page_cur);
+      page_cur = page_next;
+      page_next = page_after;
     }
     if (lane == 0 && *abort_flag) {
-      for (int j = max(0, issued - KV_STAGES); j < issued; ++j)
-        for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(kv_full0 + 8 * (j % KV_STAGES), (j / KV_STAGES) & 1); ++i) {
+      for (int j = max(0, k_issued - KV_STAGES); j < k_issued; ++j)
+        for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(k_full0 + 8 * (j % KV_STAGES), (j / KV_STAGES) & 1); ++i) {
+        }
+      for (int j = max(0, v_issued - KV_STAGES); j < v_issued; ++j)
+        for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(v_full0 + 8 * (j % KV_STAGES), (j / KV_STAGES) & 1); ++i) {
         }
       for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(q_full, 0); ++i) {
       }
@@ -265,17 +322,23 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     // ---- MMA issuer ------------------------------------------------------------------------------
     if (lane == 0) {
       constexpr uint32_t instr_s = idesc(BM, BN, false), instr_o = idesc(BM, D, true);
-      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
-      auto scores = [&](int j) {  // S[j & 1] = Q K_j^T
-        const uint32_t k_addr = smem_u32(kv_s + (j % KV_STAGES) * STAGE_BYTES);
+      // Descriptors differ only in their address field (the low 14 bits, in units of 16 bytes).
+      const uint64_t q_desc = desc_k_major(smem_u32(q_s)), p_desc = desc_k_major(smem_u32(p_s));
+      uint64_t k_desc[KV_STAGES], v_desc[KV_STAGES];
+      for (int s = 0; s < KV_STAGES; ++s) {
+        k_desc[s] = desc_k_major(smem_u32(kv_s + s * STAGE_BYTES));
+        v_desc[s] = desc_mn_major(smem_u32(kv_s + s * STAGE_BYTES) + K_BYTES, TILE_HALF);
+      }
+      auto scores = [&](int j) {  // S[j & 1] = Q K_j^T, then the K slot is free
+        const int s = j % KV_STAGES;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * HALF_BYTES + (kk % 4) * 32;
-          umma(tmem_base + S_COL + (j & 1) * BN, desc_k_major(q_addr + off), desc_k_major(k_addr + off), instr_s, kk != 0);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma(tmem_base + S_COL + (j & 1) * BN, q_desc + (((kk / 4) * HALF_BYTES + (kk % 4) * 32) >> 4),
+               k_desc[s] + (((kk / 4) * TILE_HALF + (kk % 4) * 32) >> 4), instr_s, kk != 0);
         umma_commit(s_full0 + 8 * (j & 1));
+        umma_commit(k_empty0 + 8 * s);
       };
-      bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(kv_full0, 0, abort_flag);
+      bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(k_full0, 0, abort_flag);
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         scores(0);
@@ -283,26 +346,27 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       uint32_t accumulate = 0;
       for (int j = 0; j < n_tiles && ok; ++j) {
         if (j + 1 < n_tiles) {
-          ok = mbar_wait(kv_full0 + 8 * ((j + 1) % KV_STAGES), ((j + 1) / KV_STAGES) & 1, abort_flag);
+          ok = mbar_wait(k_full0 + 8 * ((j + 1) % KV_STAGES), ((j + 1) / KV_STAGES) & 1, abort_flag);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          STAMP(1, j, 0);
           scores(j + 1);
         }
-        ok = mbar_wait(p_full, j & 1, abort_flag);
+        const int s = j % KV_STAGES;
+        ok = mbar_wait(v_full0 + 8 * s, (j / KV_STAGES) & 1, abort_flag) && mbar_wait(p_full, j & 1, abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int s = j % KV_STAGES;
-        const uint32_t v_addr = smem_u32(kv_s + s * STAGE_BYTES) + K_BYTES;
+        STAMP(1, j, 1);
         const uint32_t mask = group_mask[s];
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           if (!(mask & (1u << kk))) continue;  // keys never loaded: their P is zero, their V is stale
-          umma(tmem_base + O_COL, desc_k_major(p_addr + (kk / 4) * HALF_BYTES + (kk % 4) * 32),
-               desc_mn_major(v_addr + kk * GROUP_BYTES, HALF_BYTES), instr_o, accumulate);
+          umma(tmem_base + O_COL, p_desc + ((kk * 32) >> 4), v_desc[s] + ((kk * GROUP_BYTES) >> 4), instr_o, accumulate);
           accumulate = 1;
         }
-        umma_commit(kv_empty0 + 8 * s);
+        umma_commit(v_empty0 + 8 * s);
         umma_commit(o_done);
+        STAMP(1, j, 2);
       }
     }
   } else {
@@ -322,26 +386,67 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       ok = mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (row == 0) STAMP(2, j, 0);
       const uint32_t s_addr = tmem_base + lane_field + S_COL + (j & 1) * BN;
-      // Which keys of the tile this row sees; a tile that every row sees whole needs no masks.
+      // Which keys of the tile this row sees; a tile that the whole warp sees whole needs no masks.
       const int lo = max(row_lo - key0, 0), hi = min(row_hi - key0, BN - 1);  // visible columns [lo, hi]
+      const bool whole = __all_sync(0xffffffffu, lo == 0 && hi == BN - 1);
       // Pass 1: the row's maximum.
       float tile_max = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t v[32];
+      for (int c = 0; c < BN; c += 64) {
+        uint32_t v[64];
         tmem_load32(s_addr + c, v);
+        tmem_load32(s_addr + c + 32, v + 32);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (whole) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = c + i;
-          if (col >= lo && col <= hi) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
+          for (int i = 0; i < 64; ++i) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const int col = c + i;
+            if (col >= lo && col <= hi) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
+          }
         }
       }
+      if (row == 0) STAMP(2, j, 1);
       const float m_new = fmaxf(m, tile_max);
       const float offset = m_new == -INFINITY ? 0.f : m_new * sl2;
-      const float alpha = (m == -INFINITY || m_new == m) ? 1.f : exp2f(m * sl2 - offset);
+      const float alpha = (m == -INFINITY || m_new == m) ? 1.f : fast_exp2(m * sl2 - offset);
       m = m_new;
+      // Pass 2: P = exp2(s * scale * log2e - offset), rounded to bfloat16, kept in registers: the
+      // arithmetic overlaps the previous tile's P V, which still reads the shared P tile.
+      static_assert(BN == 64, "the softmax below handles one 64-column pass per tile");
+      float sum = 0.f;
+      uint32_t packed[32];
+      {
+        uint32_t v[64];
+        tmem_load32(s_addr, v);
+        tmem_load32(s_addr + 32, v + 32);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (whole) {
+#pragma unroll
+          for (int i = 0; i < 64; i += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), sl2, -offset));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), sl2, -offset));
+            sum += p0 + p1;
+            packed[i / 2] = pack_bf16(p0, p1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; i += 2) {
+            float p[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int col = i + e;
+              p[e] = (col >= lo && col <= hi) ? fast_exp2(fmaf(__uint_as_float(v[i + e]), sl2, -offset)) : 0.f;
+            }
+            sum += p[0] + p[1];
+            packed[i / 2] = pack_bf16(p[0], p[1]);
+          }
+        }
+      }
       // The previous tile's P V must be done before O is rescaled or P is overwritten.
       if (j > 0) {
         ok = mbar_wait(o_done, (j - 1) & 1, abort_flag);
@@ -360,32 +465,14 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
+      if (row == 0) STAMP(2, j, 2);
       l *= alpha;
-      // Pass 2: P = exp2(s * scale * log2e - offset), rounded to bfloat16, into swizzled shared memory.
-      float sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t v[32];
-        tmem_load32(s_addr + c, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        uint32_t packed[16];
+      {
+        // The tile's 64 columns are the eight 16-byte chunks of the row; chunk x of row r lives at x ^ (r % 8).
+        unsigned char* row_base = p_s + row * 128;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = c + i + e;
-            p[e] = (col >= lo && col <= hi) ? exp2f(__uint_as_float(v[i + e]) * sl2 - offset) : 0.f;
-            sum += p[e];
-          }
-          packed[i / 2] = pack_bf16(p[0], p[1]);
-        }
-        // Columns c .. c+31 are chunks (c % 64) / 8 .. + 3 of half c / 64; chunk x of row r lives at x ^ (r % 8).
-        unsigned char* row_base = p_s + (c / 64) * HALF_BYTES + row * 128;
-#pragma unroll
-        for (int x = 0; x < 4; ++x) {
-          const int chunk = ((c % 64) / 8 + x) ^ (row & 7);
-          *reinterpret_cast<uint4*>(row_base + chunk * 16) =
+        for (int x = 0; x < 8; ++x) {
+          *reinterpret_cast<uint4*>(row_base + ((x ^ (row & 7)) * 16)) =
               make_uint4(packed[4 * x], packed[4 * x + 1], packed[4 * x + 2], packed[4 * x + 3]);
         }
       }
@@ -393,6 +480,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core (async proxy)
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(p_full);
+      if (row == 0) STAMP(2, j, 3);
     }
     // Epilogue: O / l, gate, store.
     if (ok) ok = mbar_wait(o_done, (n_tiles - 1) & 1, abort_flag);
@@ -457,6 +545,12 @@ EncodeTiled encode_tiled() {
 
 }  // namespace
 
+#ifdef ATTN_TIMING
+extern "C" int omnia_attention_timing(unsigned long long* host, int count) {
+  return (int)cudaMemcpyFromSymbol(host, g_timing, sizeof(unsigned long long) * count);
+}
+#endif
+
 extern "C" int omnia_attention_tcgen05_info(int* head_dim, int* group, int* tokens_per_block) {
   *head_dim = HEAD_DIM;
   *group = GROUP;
@@ -496,7 +590,7 @@ extern "C" int omnia_attention_prefill_tcgen05(const void* q, int tokens, const 
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return (int)cudaErrorInvalidValue;
   }
-  constexpr size_t smem = Q_BYTES + P_BYTES + KV_STAGES * STAGE_BYTES + 1024 + 256;
+  constexpr size_t smem = Q_BYTES + P_BYTES + KV_STAGES * STAGE_BYTES + 256;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel,

@@ -35,7 +35,7 @@ constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;   // 128 bytes of bfloat16: one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;  // producer warp, MMA warp, four epilogue warps
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr uint32_t WAIT_LIMIT = 1u << 20;
 
 enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_SOFTCAP = 2 };
 
@@ -54,10 +54,10 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"  // sleeps up to the hint (ns)
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(2000u)
       : "memory");
   return ok != 0;
 }
@@ -65,7 +65,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
     if (mbar_try(bar, parity)) return true;
-    if (*abort_flag) return false;
+    if ((i & 63) == 63 && *abort_flag) return false;
   }
   *abort_flag = 1;
   return false;
@@ -119,7 +119,7 @@ __device__ __forceinline__ void tmem_load32(uint32_t addr, uint32_t* v) {
 }
 
 template <int BLOCK_N, int STAGES, int EPI>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     void* __restrict__ out, int m, int n, int k, int pair_offset, float multiplier,
                     float cap, int m_tiles, int n_tiles, int* err) {
