@@ -225,6 +225,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pa
                          const bf16* __restrict__ gate, int gate_stride, bf16* __restrict__ out,
                          int max_pages, int num_pages, int nq, int nkv, int page_size, int window,
                          float scale, int* err) {
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [BM][ROW]
   bf16* kv = qs + BM * ROW;                       // 2 stages x (K [BN][ROW], V [BN][ROW])
@@ -302,6 +303,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pa
     __syncthreads();
   }
   cp_async_wait<0>();
+  pdl_launch_dependents();  // the cache is read: the next kernel may begin its preamble
 
   // Normalise, gate, store.
 #pragma unroll
@@ -405,6 +407,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
                         bf16* __restrict__ out, int chunk_keys, int max_chunks, int max_pages,
                         int num_pages, int nq, int nkv, int page_size, int window, float scale,
                         int* err) {
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* kv = reinterpret_cast<bf16*>(smem_raw);  // DECODE_STAGES x (K [32][ROW], V [32][ROW])
   const int lane = threadIdx.x;
@@ -502,6 +505,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     __syncwarp();
   }
   cp_async_wait<0>();
+  pdl_launch_dependents();  // the cache is read: the next kernel may begin its preamble
 
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -572,7 +576,7 @@ extern "C" int omnia_attention_prefill_tc(const void* q, const void* pages, cons
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  attention_prefill_kernel<<<dim3(blocks, nkv), 128, smem, stream>>>(
+  launch_pdl(attention_prefill_kernel, dim3(blocks, nkv), 128, smem, stream, 
       (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, work, (const bf16*)gate,
       gate_stride, (bf16*)out, max_pages, num_pages, nq, nkv, page_size, window, scale, err);
   return OMNIA_LAUNCH_RESULT();
@@ -596,7 +600,7 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  attention_decode_kernel<<<dim3(max_chunks, nkv, requests), 32, smem, stream>>>(
+  launch_pdl(attention_decode_kernel, dim3(max_chunks, nkv, requests), 32, smem, stream, 
       (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
       tickets, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
       num_pages, nq, nkv, page_size, window, scale, err);
@@ -677,7 +681,7 @@ extern "C" int omnia_attention_decode_tc_static(const void* q, const void* pages
     return (int)e;
   }
   const size_t smem = (size_t)(DECODE_STAGES * 2 * DECODE_BN) * ROW * sizeof(bf16);
-  attention_decode_kernel<<<dim3(max_chunks, nkv, requests), 32, smem, stream>>>(
+  launch_pdl(attention_decode_kernel, dim3(max_chunks, nkv, requests), 32, smem, stream, 
       (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
       ticket_area, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
       num_pages, nq, nkv, page_size, window, scale, err);

@@ -63,6 +63,30 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[32];
 }
 
+// Programmatic dependent launch. A kernel launched through launch_pdl may begin while the kernel
+// before it in the stream is still running; it must call pdl_wait() before it touches anything an
+// earlier kernel wrote (reading weights before that is fine and hides their latency), and calls
+// pdl_launch_dependents() to let the kernel after it start its own preamble early. In a kernel
+// launched the ordinary way both calls do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 #define OMNIA_LAUNCH_RESULT() ((int)cudaGetLastError())
 
 #define OMNIA_DISPATCH_DTYPE(code, ...)                    \

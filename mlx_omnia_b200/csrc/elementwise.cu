@@ -9,6 +9,8 @@ template <typename T>
 __global__ void embed_rmsnorm_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                      float* __restrict__ x, int hidden, int vocab, float eps,
                                      int normed, int* err) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[33];
   const int t = blockIdx.x;
   int id = ids[t];
@@ -32,7 +34,7 @@ extern "C" int omnia_embed_rmsnorm(const int* ids, const void* table, float* x, 
                                    int hidden, int vocab, float eps, int normed, int dtype,
                                    int* err, cudaStream_t stream) {
   if (tokens == 0) return 0;
-  OMNIA_DISPATCH_DTYPE(dtype, (embed_rmsnorm_kernel<T><<<tokens, 256, 0, stream>>>(
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(embed_rmsnorm_kernel<T>, tokens, 256, 0, stream, 
                                   ids, (const T*)table, x, hidden, vocab, eps, normed, err)));
   return OMNIA_LAUNCH_RESULT();
 }
@@ -42,6 +44,8 @@ extern "C" int omnia_embed_rmsnorm(const int* ids, const void* table, float* x, 
 template <typename T>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                T* __restrict__ h, int hidden, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[33];
   const float* row = x + (size_t)blockIdx.x * hidden;
   T* out = h + (size_t)blockIdx.x * hidden;
@@ -59,7 +63,7 @@ extern "C" int omnia_rmsnorm(const float* x, const float* w, void* h, int rows, 
                              float eps, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
   OMNIA_DISPATCH_DTYPE(dtype,
-                       (rmsnorm_kernel<T><<<rows, 256, 0, stream>>>(x, w, (T*)h, hidden, eps)));
+                       (launch_pdl(rmsnorm_kernel<T>, rows, 256, 0, stream, x, w, (T*)h, hidden, eps)));
   return OMNIA_LAUNCH_RESULT();
 }
 
@@ -75,6 +79,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
                                    const float* __restrict__ wb, float eps_b, int norm_branch,
                                    const float* __restrict__ wo, float eps_o, int norm_out,
                                    T* __restrict__ h, int hidden) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float row[];
   __shared__ float scratch[33];
   float* xr = x + (size_t)blockIdx.x * hidden;
@@ -146,6 +152,8 @@ __global__ void add_rmsnorm_reg_kernel(float* __restrict__ x, const T* __restric
                                        const float* __restrict__ wb, float eps_b, int norm_branch,
                                        const float* __restrict__ wo, float eps_o, int norm_out,
                                        T* __restrict__ h, int hidden) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[33];
   float* xr = x + (size_t)blockIdx.x * hidden;
   const T* br = branch + (size_t)blockIdx.x * hidden;
@@ -206,10 +214,10 @@ extern "C" int omnia_add_rmsnorm(float* x, const void* branch, const float* wb, 
     const int iters = (hidden + threads * 4 - 1) / (threads * 4);
     OMNIA_DISPATCH_DTYPE(dtype, {
       if (iters <= 2)
-        add_rmsnorm_reg_kernel<T, 2><<<rows, threads, 0, stream>>>(
+        launch_pdl(add_rmsnorm_reg_kernel<T, 2>, rows, threads, 0, stream, 
             x, (const T*)branch, wb, eps_b, norm_branch, wo, eps_o, norm_out, (T*)h, hidden);
       else
-        add_rmsnorm_reg_kernel<T, 4><<<rows, threads, 0, stream>>>(
+        launch_pdl(add_rmsnorm_reg_kernel<T, 4>, rows, threads, 0, stream, 
             x, (const T*)branch, wb, eps_b, norm_branch, wo, eps_o, norm_out, (T*)h, hidden);
     });
     return OMNIA_LAUNCH_RESULT();
@@ -220,7 +228,7 @@ extern "C" int omnia_add_rmsnorm(float* x, const void* branch, const float* wb, 
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)smem);
-    add_rmsnorm_kernel<T><<<rows, 256, smem, stream>>>(x, (const T*)branch, wb, eps_b,
+    launch_pdl(add_rmsnorm_kernel<T>, rows, 256, smem, stream, x, (const T*)branch, wb, eps_b,
                                                        norm_branch, wo, eps_o, norm_out, (T*)h,
                                                        hidden);
   });
@@ -242,6 +250,8 @@ __global__ void qk_norm_rope_store_kernel(const T* __restrict__ proj, int row_st
                                           const long long* __restrict__ slot_mapping,
                                           T* __restrict__ q_out, T* __restrict__ pages,
                                           int page_size, long long num_slots, int* err) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hs = blockIdx.y * (blockDim.x >> 5) + warp;
@@ -301,7 +311,7 @@ extern "C" int omnia_qk_norm_rope_store(const void* proj, int row_stride, int q_
   if (d > 256 || (d & 1) || rot > d || (rot & 1)) return (int)cudaErrorInvalidValue;
   const int heads = nq + 2 * nkv;
   dim3 grid(tokens, (heads + 3) / 4);
-  OMNIA_DISPATCH_DTYPE(dtype, (qk_norm_rope_store_kernel<T><<<grid, 128, 0, stream>>>(
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(qk_norm_rope_store_kernel<T>, grid, 128, 0, stream, 
                                   (const T*)proj, row_stride, q_col, k_col, v_col, nq, nkv, d, eps,
                                   inv_freq, rot, positions, slot_mapping, (T*)q_out, (T*)pages,
                                   page_size, num_slots, err)));
@@ -313,6 +323,8 @@ extern "C" int omnia_qk_norm_rope_store(const void* proj, int row_stride, int q_
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, long long total,
                               int inner) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += stride) {
@@ -329,7 +341,7 @@ extern "C" int omnia_swiglu(const void* gu, void* act, int rows, int inner, int 
   const long long total = (long long)rows * inner;
   if (total == 0) return 0;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-  OMNIA_DISPATCH_DTYPE(dtype, (swiglu_kernel<T><<<blocks, 256, 0, stream>>>(
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(swiglu_kernel<T>, blocks, 256, 0, stream, 
                                   (const T*)gu, (T*)act, total, inner)));
   return OMNIA_LAUNCH_RESULT();
 }
@@ -339,6 +351,8 @@ extern "C" int omnia_swiglu(const void* gu, void* act, int rows, int inner, int 
 template <typename T>
 __global__ void softcap_kernel(const T* __restrict__ z, float* __restrict__ out, long long total,
                                float multiplier, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += stride) {
@@ -351,7 +365,7 @@ extern "C" int omnia_softcap(const void* z, float* out, long long total, float m
                              float cap, int dtype, cudaStream_t stream) {
   if (total == 0) return 0;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-  OMNIA_DISPATCH_DTYPE(dtype, (softcap_kernel<T><<<blocks, 256, 0, stream>>>((const T*)z, out,
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(softcap_kernel<T>, blocks, 256, 0, stream, (const T*)z, out,
                                                                             total, multiplier, cap)));
   return OMNIA_LAUNCH_RESULT();
 }
@@ -361,6 +375,8 @@ extern "C" int omnia_softcap(const void* z, float* out, long long total, float m
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restrict__ rows,
                                    T* __restrict__ out, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
   const T* s = src + (size_t)rows[blockIdx.x] * width;
   T* o = out + (size_t)blockIdx.x * width;
   for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = s[i];
@@ -369,7 +385,7 @@ __global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restr
 extern "C" int omnia_gather_rows(const void* src, const int* rows, void* out, int count, int width,
                                  int dtype, cudaStream_t stream) {
   if (count == 0) return 0;
-  OMNIA_DISPATCH_DTYPE(dtype, (gather_rows_kernel<T><<<count, 256, 0, stream>>>(
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(gather_rows_kernel<T>, count, 256, 0, stream, 
                                   (const T*)src, rows, (T*)out, width)));
   return OMNIA_LAUNCH_RESULT();
 }

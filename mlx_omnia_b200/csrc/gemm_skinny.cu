@@ -81,6 +81,19 @@ gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, void*
   const int per_warp = (blocks + WARPS - 1) / WARPS;
   const int b_begin = warp * per_warp, b_end = min(blocks, b_begin + per_warp);
   const uint4 zero = make_uint4(0, 0, 0, 0);
+  // The weights do not depend on the kernel before this one: pull this warp's slice of them into
+  // L2 while that kernel is still finishing, then wait for the activations it produces.
+  {
+    const int slice_begin = b_begin * 64, slice_end = min(b_end * 64, k * 2);  // bytes within a row
+#pragma unroll
+    for (int r = 0; r < RG; ++r)
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        if (wlive[r][h])
+          for (int off = slice_begin + t * 128; off < slice_end; off += 512)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(wrow[r][h]) + off));
+  }
+  pdl_wait();
   for (int b0 = b_begin; b0 < b_end; b0 += UNROLL) {
     uint4 wv[UNROLL][RG][2], av[UNROLL][NT];
 #pragma unroll
@@ -105,6 +118,8 @@ gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, void*
           mma_bf16(acc[r][j], wv[u][r][0].z, wv[u][r][1].z, wv[u][r][0].w, wv[u][r][1].w, av[u][j].z, av[u][j].w);
         }
   }
+  // The weights are read: the next kernel may start its own preamble while the sums are reduced.
+  pdl_launch_dependents();
   // Partial sums: C fragment (row g / g + 8 of the group, activation rows 2t, 2t + 1).
 #pragma unroll
   for (int r = 0; r < RG; ++r)
@@ -151,13 +166,13 @@ int launch(const bf16* a, const bf16* w, void* out, int m, int n, int k, int pai
            float multiplier, float cap, cudaStream_t stream) {
   if (EPI == EPI_SWIGLU) {
     const int blocks = (pair_offset + 15) / 16;
-    gemm_skinny_kernel<NT, 2, EPI><<<blocks, WARPS * 32, 0, stream>>>(a, w, out, m, n, k, pair_offset,
+    launch_pdl(gemm_skinny_kernel<NT, 2, EPI>, blocks, WARPS * 32, 0, stream, a, w, out, m, n, k, pair_offset,
                                                                      multiplier, cap);
   } else if (n >= 32 * 148) {
-    gemm_skinny_kernel<NT, 2, EPI><<<(n + 31) / 32, WARPS * 32, 0, stream>>>(a, w, out, m, n, k, 0,
+    launch_pdl(gemm_skinny_kernel<NT, 2, EPI>, (n + 31) / 32, WARPS * 32, 0, stream, a, w, out, m, n, k, 0,
                                                                             multiplier, cap);
   } else {
-    gemm_skinny_kernel<NT, 1, EPI><<<(n + 15) / 16, WARPS * 32, 0, stream>>>(a, w, out, m, n, k, 0,
+    launch_pdl(gemm_skinny_kernel<NT, 1, EPI>, (n + 15) / 16, WARPS * 32, 0, stream, a, w, out, m, n, k, 0,
                                                                             multiplier, cap);
   }
   return OMNIA_LAUNCH_RESULT();

@@ -83,6 +83,8 @@ sample_kernel(float* __restrict__ logits, long long stride, int vocab,
               const float* __restrict__ penalty, const int* __restrict__ history, int history_len,
               const long long* __restrict__ seeds, const long long* __restrict__ draws,
               int* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float fscratch[33];
   __shared__ ArgMax ascratch[33];
   const int row = blockIdx.x;
@@ -187,6 +189,8 @@ sample_kernel(float* __restrict__ logits, long long stride, int vocab,
 __global__ void __launch_bounds__(256)
 argmax_partial_kernel(const float* __restrict__ logits, long long stride, int vocab,
                       float* __restrict__ part_v, int* __restrict__ part_i) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ ArgMax ascratch[33];
   const int row = blockIdx.y, part = blockIdx.x;
   const float* z = logits + (size_t)row * stride;
@@ -204,6 +208,8 @@ argmax_partial_kernel(const float* __restrict__ logits, long long stride, int vo
 __global__ void __launch_bounds__(32)
 argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
                     int* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x, lane = threadIdx.x;
   ArgMax a{part_v[row * ARGMAX_PARTS + lane], part_i[row * ARGMAX_PARTS + lane]};
 #pragma unroll
@@ -220,9 +226,9 @@ argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ pa
 extern "C" int omnia_argmax(const float* logits, long long stride, int rows, int vocab,
                             float* part_v, int* part_i, int* out, cudaStream_t stream) {
   if (rows == 0) return 0;
-  argmax_partial_kernel<<<dim3(ARGMAX_PARTS, rows), 256, 0, stream>>>(logits, stride, vocab, part_v,
+  launch_pdl(argmax_partial_kernel, dim3(ARGMAX_PARTS, rows), 256, 0, stream, logits, stride, vocab, part_v,
                                                                      part_i);
-  argmax_final_kernel<<<rows, 32, 0, stream>>>(part_v, part_i, out);
+  launch_pdl(argmax_final_kernel, rows, 32, 0, stream, part_v, part_i, out);
   return OMNIA_LAUNCH_RESULT();
 }
 
@@ -233,7 +239,7 @@ extern "C" int omnia_sample(float* logits, long long stride, int rows, int vocab
                             int* out, cudaStream_t stream) {
   if (rows == 0) return 0;
   if (history_len > SAMPLE_THREADS) return (int)cudaErrorInvalidValue;
-  sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, stride, vocab, temperature, top_k,
+  launch_pdl(sample_kernel, rows, SAMPLE_THREADS, 0, stream, logits, stride, vocab, temperature, top_k,
                                                      top_p, min_p, penalty, history, history_len,
                                                      seeds, draws, out);
   return OMNIA_LAUNCH_RESULT();
