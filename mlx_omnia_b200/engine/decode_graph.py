@@ -49,6 +49,7 @@ class _Captured:
     logits: torch.Tensor
     batch: int
     width: int
+    launches: int = 0  # this package's kernels inside the graph (counted at capture)
     copied: torch.cuda.Event | None = None  # the last host-to-device copy of the metadata
 
 
@@ -122,9 +123,10 @@ class DecodeGraphs:
         torch.cuda.current_stream(device).wait_stream(side)
         torch.cuda.synchronize(device)
         graph = torch.cuda.CUDAGraph()
+        before = ops.launches
         with torch.cuda.graph(graph):
             logits = runner.model.forward(step, layers)
-        return _Captured(graph, step, host, host_tensor, dev, fields, logits, batch, width)
+        return _Captured(graph, step, host, host_tensor, dev, fields, logits, batch, width, ops.launches - before)
 
     def _fill(self, host: np.ndarray, fields, batch: int, width: int, entries, starts) -> None:
         cache = self.runner.cache
@@ -188,6 +190,7 @@ class DecodeGraphs:
         captured.copied.record()
         captured.graph.replay()
         self.replays += 1
+        ops.launches += captured.launches  # the replay launches what the capture recorded
         wanted = [i for i, e in enumerate(entries) if e.want]
         if len(wanted) == len(entries):
             logits = captured.logits[: len(entries)]

@@ -52,7 +52,8 @@ def _stream() -> int:
 
 
 launches = 0
-"""How many of this package's own kernels have been launched by this process."""
+"""How many launches of this package's own kernels this process has issued (a call that
+launches two kernels counts once; replayed CUDA graphs add what their capture recorded)."""
 
 
 def _check(code: int, what: str) -> None:
