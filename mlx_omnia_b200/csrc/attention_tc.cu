@@ -395,7 +395,7 @@ __device__ __forceinline__ void combine_head(const float* __restrict__ part_o,
 // ---------------------------------------------------------------------------------------
 // Decode: grid (chunks, nkv, requests); 32 threads. Request s is the single-token
 // request seq_ids[s] (or s when seq_ids is null). Partials:
-//   part_o  [tokens, nq, max_chunks, D] float32 (unnormalised), part_ml [tokens, nq, max_chunks, 2]
+//   part_o  [requests, nq, max_chunks, D] float32 (unnormalised), part_ml [requests, nq, max_chunks, 2]
 //   tickets [requests, nkv] int32, zero before the first launch; the merging block zeroes its
 //   ticket again, so the array is ready for the next launch.
 __global__ void __launch_bounds__(32)
@@ -517,7 +517,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
   for (int r = 0; r < 2; ++r) {
     const int row = (lane >> 2) + 8 * r;
     if (row >= GROUP) continue;
-    const size_t slot = ((token * nq + kvh * GROUP + row) * max_chunks + chunk);
+    const size_t slot = (((size_t)blockIdx.z * nq + kvh * GROUP + row) * max_chunks + chunk);
     float* dst = part_o + slot * D;
 #pragma unroll
     for (int j = 0; j < NT_O; ++j) {
@@ -545,7 +545,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
 #pragma unroll 1
   for (int r = 0; r < GROUP; ++r) {
     const int head = kvh * GROUP + r;
-    combine_head(part_o, part_ml, (token * nq + head) * max_chunks, c0, c1,
+    combine_head(part_o, part_ml, ((size_t)blockIdx.z * nq + head) * max_chunks, c0, c1,
                  gate ? gate + token * gate_stride + (size_t)head * D : nullptr,
                  out + (token * nq + head) * D);
   }

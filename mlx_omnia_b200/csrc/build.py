@@ -100,6 +100,11 @@ def compile_library(name: str, defines: dict[str, object] | None = None, extra: 
         partial.unlink(missing_ok=True)
         raise KernelBuildError(f"nvcc failed for {source.name}:\n{' '.join(command)}\n{output}")
     os.replace(partial, target)
+    # Libraries of the same name and macros built from older sources are of no use any more.
+    stem = target.name.rsplit("_", 1)[0]
+    for stale in target.parent.glob(stem + "_*.so"):
+        if stale != target and stale.name.rsplit("_", 1)[0] == stem:
+            stale.unlink(missing_ok=True)
     if verbose:
         print(f"[mlx_omnia_b200]   built {target.name} in {time.time() - started:.1f} s", file=sys.stderr, flush=True)
     return target

@@ -185,12 +185,26 @@ def _prefill_work(step: StepContext, tokens_per_block: int, device: torch.device
     key = ("prefill_work", tokens_per_block)
     work = step.workspace.get(key)
     if work is None:
-        items = [(s, t0) for s, n in enumerate(step.q_lens) for t0 in range(0, n, tokens_per_block)]
+        items = [(s, t0) for s, n in enumerate(step.q_lens) if n > 1 for t0 in range(0, n, tokens_per_block)]
         if step.seq_lens_host:
             items.sort(key=lambda item: -(step.seq_lens_host[item[0]] - step.q_lens[item[0]] + item[1]))
         work = torch.tensor(items, dtype=torch.int32).pin_memory().to(device, non_blocking=True)
         step.workspace[key] = work
     return work
+
+
+def _single_token_requests(step: StepContext, device: torch.device) -> tuple[torch.Tensor | None, int]:
+    """Indices of the requests that bring one token to a mixed step (they take the decode
+    kernel), and the longest of them."""
+    if step.workspace is None:
+        step.workspace = {}
+    held = step.workspace.get("single_token_requests")
+    if held is None:
+        ids = [s for s, n in enumerate(step.q_lens) if n == 1]
+        longest = max((step.seq_lens_host[s] for s in ids), default=0)
+        tensor = torch.tensor(ids, dtype=torch.int32).pin_memory().to(device, non_blocking=True) if ids else None
+        held = step.workspace["single_token_requests"] = (tensor, longest)
+    return held
 
 
 def tcgen05_attention_supported(dtype: torch.dtype, nq: int, nkv: int, d: int, page_size: int) -> bool:
@@ -226,25 +240,29 @@ def paged_attention(q: torch.Tensor, kv: KVView, step: StepContext, scale: float
                   kv.page_size, kv.window or 0, scale, _code(q.dtype), err, _stream()), "paged_attention")
         return out
     defines = {"HEAD_DIM": d, "GROUP": nq // nkv}
-    if step.decode_only:
-        max_chunks = -(-step.max_seq_len // DECODE_CHUNK)
+    # Requests that bring a single token take the split-key decode kernel, in a decode-only step
+    # (all of them, no index list: the shape a captured graph replays) and in a mixed step alike.
+    single, longest = (None, step.max_seq_len) if step.decode_only else _single_token_requests(step, q.device)
+    if step.decode_only or single is not None:
+        count = step.num_seqs if step.decode_only else single.shape[0]
+        max_chunks = -(-longest // DECODE_CHUNK)
         held = step.workspace if isinstance(step.workspace, dict) else {}
         part_o, part_ml = held.get("attention_part_o"), held.get("attention_part_ml")
         tickets = held.get("attention_tickets")
-        if part_o is None or part_o.numel() < tokens * nq * max_chunks * d:
-            part_o = scratch(q.device, "attention_part_o", tokens * nq * max_chunks * d)
-            part_ml = scratch(q.device, "attention_part_ml", tokens * nq * max_chunks * 2)
-            tickets = scratch(q.device, "attention_tickets", tokens * nkv, torch.int32, zeroed=True)
+        if part_o is None or part_o.numel() < count * nq * max_chunks * d:
+            part_o = scratch(q.device, "attention_part_o", count * nq * max_chunks * d)
+            part_ml = scratch(q.device, "attention_part_ml", count * nq * max_chunks * 2)
+            tickets = scratch(q.device, "attention_tickets", count * nkv, torch.int32, zeroed=True)
         fn = _function("attention_tc", "omnia_attention_decode_tc",
                        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                         c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_float, c_void_p, c_void_p], defines)
-        _check(fn(_ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.seq_lens), None,
-                  step.num_seqs, _ptr(part_o), _ptr(part_ml), _ptr(tickets), DECODE_CHUNK, max_chunks, gate_ptr,
-                  gate_stride,
-                  _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size, kv.window or 0, scale, err, _stream()),
-               "attention_decode")
-        return out
+        _check(fn(_ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.seq_lens),
+                  _ptr(single), count, _ptr(part_o), _ptr(part_ml), _ptr(tickets), DECODE_CHUNK, max_chunks, gate_ptr,
+                  gate_stride, _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size, kv.window or 0, scale, err,
+                  _stream()), "attention_decode")
+        if step.decode_only or all(n == 1 for n in step.q_lens):
+            return out
     if USE_TCGEN05 and tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):
         work = _prefill_work(step, 128 // (nq // nkv), q.device)
         fn = _function("attention_tcgen05", "omnia_attention_prefill_tcgen05",
