@@ -1,8 +1,9 @@
-// out[m, n] = sum_k a[m, k] * w[n, k] for a handful of rows m (decode steps): the weight
+// out[m, n] = sum_k a[m, k] * w[n, k] for up to 64 rows m (decode steps): the weight
 // matrix is streamed from HBM exactly once, straight into tensor-core fragments.
 //
 // A warp owns 16 (or 32) weight rows and one slice of k. The m16n8k16 MMA takes the weight
-// rows as its 16-row operand and up to 8 activation rows as its 8-column operand. A dot
+// rows as its 16-row operand and 8 activation rows as its 8-column operand (up to eight such
+// tiles of activations per pass over the weights). A dot
 // product does not care about the order of k, so every thread loads 16 contiguous bytes
 // (8 values of k) of its weight row and the same 8 values of k of its activation row, and
 // feeds them to two MMAs; no shared memory and no shuffles are needed to form fragments.
@@ -18,7 +19,6 @@ namespace {
 
 typedef __nv_bfloat16 bf16;
 constexpr int WARPS = 8;
-constexpr int UNROLL = 4;
 
 enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_SOFTCAP = 2 };
 
@@ -39,13 +39,15 @@ __device__ __forceinline__ void mma_bf16(float* c, unsigned a0, unsigned a1, uns
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// NT: activation tiles of 8 rows (1 or 2). RG: weight row groups of 16 per warp (1 or 2).
+// NT: activation tiles of 8 rows (1, 2, 4 or 8). RG: weight row groups of 16 per warp (1 or 2).
 // With EPI_SWIGLU, RG is 2 and the second group lies `pair_offset` rows after the first.
-template <int NT, int RG, int EPI>
+// UNROLL: k-blocks whose loads are issued together (fewer when many activation tiles need registers).
+template <int NT, int RG, int EPI, int UNROLL = (NT <= 2 ? 4 : 2)>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, void* __restrict__ out,
                    int m, int n, int k, int pair_offset, float multiplier, float cap) {
-  __shared__ float partial[WARPS][RG * 16][NT * 8 + 1];
+  extern __shared__ float partial_raw[];
+  float (*partial)[RG * 16][NT * 8 + 1] = reinterpret_cast<float (*)[RG * 16][NT * 8 + 1]>(partial_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int rows_per_block = EPI == EPI_SWIGLU ? 16 : RG * 16;
@@ -161,21 +163,39 @@ gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, void*
   }
 }
 
+template <int NT, int RG, int EPI>
+int launch_variant(int blocks, const bf16* a, const bf16* w, void* out, int m, int n, int k, int pair_offset,
+                   float multiplier, float cap, cudaStream_t stream) {
+  constexpr size_t smem = sizeof(float) * WARPS * RG * 16 * (NT * 8 + 1);
+  static bool configured = false;
+  if (smem > 48 * 1024 && !configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NT, RG, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  launch_pdl(gemm_skinny_kernel<NT, RG, EPI>, blocks, WARPS * 32, smem, stream, a, w, out, m, n, k, pair_offset,
+             multiplier, cap);
+  return OMNIA_LAUNCH_RESULT();
+}
+
 template <int NT, int EPI>
 int launch(const bf16* a, const bf16* w, void* out, int m, int n, int k, int pair_offset,
            float multiplier, float cap, cudaStream_t stream) {
-  if (EPI == EPI_SWIGLU) {
-    const int blocks = (pair_offset + 15) / 16;
-    launch_pdl(gemm_skinny_kernel<NT, 2, EPI>, blocks, WARPS * 32, 0, stream, a, w, out, m, n, k, pair_offset,
-                                                                     multiplier, cap);
-  } else if (n >= 32 * 148) {
-    launch_pdl(gemm_skinny_kernel<NT, 2, EPI>, (n + 31) / 32, WARPS * 32, 0, stream, a, w, out, m, n, k, 0,
-                                                                            multiplier, cap);
-  } else {
-    launch_pdl(gemm_skinny_kernel<NT, 1, EPI>, (n + 15) / 16, WARPS * 32, 0, stream, a, w, out, m, n, k, 0,
-                                                                            multiplier, cap);
-  }
-  return OMNIA_LAUNCH_RESULT();
+  if (EPI == EPI_SWIGLU)
+    return launch_variant<NT, 2, EPI>((pair_offset + 15) / 16, a, w, out, m, n, k, pair_offset, multiplier, cap, stream);
+  if (NT <= 2 && n >= 32 * 148)
+    return launch_variant<NT, 2, EPI>((n + 31) / 32, a, w, out, m, n, k, 0, multiplier, cap, stream);
+  return launch_variant<NT, 1, EPI>((n + 15) / 16, a, w, out, m, n, k, 0, multiplier, cap, stream);
+}
+
+template <int EPI>
+int launch_rows(const bf16* a, const bf16* w, void* out, int m, int n, int k, int pair_offset, float multiplier,
+                float cap, cudaStream_t stream) {
+  if (m <= 8) return launch<1, EPI>(a, w, out, m, n, k, pair_offset, multiplier, cap, stream);
+  if (m <= 16) return launch<2, EPI>(a, w, out, m, n, k, pair_offset, multiplier, cap, stream);
+  if (m <= 32) return launch<4, EPI>(a, w, out, m, n, k, pair_offset, multiplier, cap, stream);
+  return launch<8, EPI>(a, w, out, m, n, k, pair_offset, multiplier, cap, stream);
 }
 
 }  // namespace
@@ -185,18 +205,14 @@ int launch(const bf16* a, const bf16* w, void* out, int m, int n, int k, int pai
 extern "C" int omnia_gemm_skinny(const void* a, const void* w, void* out, int m, int n, int k,
                                  int epilogue, float multiplier, float cap, cudaStream_t stream) {
   if (m == 0 || n == 0) return 0;
-  if (m > 16 || k % 8 != 0 || k <= 0) return (int)cudaErrorInvalidValue;
+  if (m > 64 || k % 8 != 0 || k <= 0) return (int)cudaErrorInvalidValue;
   const bf16* ap = (const bf16*)a;
   const bf16* wp = (const bf16*)w;
   if (epilogue == EPI_SWIGLU) {
     if (n % 2) return (int)cudaErrorInvalidValue;
-    return m <= 8 ? launch<1, EPI_SWIGLU>(ap, wp, out, m, n, k, n / 2, 1.f, 0.f, stream)
-                  : launch<2, EPI_SWIGLU>(ap, wp, out, m, n, k, n / 2, 1.f, 0.f, stream);
+    return launch_rows<EPI_SWIGLU>(ap, wp, out, m, n, k, n / 2, 1.f, 0.f, stream);
   }
-  if (epilogue == EPI_SOFTCAP)
-    return m <= 8 ? launch<1, EPI_SOFTCAP>(ap, wp, out, m, n, k, 0, multiplier, cap, stream)
-                  : launch<2, EPI_SOFTCAP>(ap, wp, out, m, n, k, 0, multiplier, cap, stream);
+  if (epilogue == EPI_SOFTCAP) return launch_rows<EPI_SOFTCAP>(ap, wp, out, m, n, k, 0, multiplier, cap, stream);
   if (epilogue != EPI_STORE) return (int)cudaErrorInvalidValue;
-  return m <= 8 ? launch<1, EPI_STORE>(ap, wp, out, m, n, k, 0, 1.f, 0.f, stream)
-                : launch<2, EPI_STORE>(ap, wp, out, m, n, k, 0, 1.f, 0.f, stream);
+  return launch_rows<EPI_STORE>(ap, wp, out, m, n, k, 0, 1.f, 0.f, stream);
 }

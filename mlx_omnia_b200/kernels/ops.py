@@ -328,14 +328,21 @@ def _gemm_skinny(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilo
     return out
 
 
+TENSOR_CORE_ROWS = 129
+"""From this many rows on, bfloat16 products run on this package's tcgen05 kernel. Between the
+skinny kernel's rows and these, a 128-row tile would be mostly padding and too few tiles would
+keep the SMs busy, so the vendor library's product stands there (measured: 11-17 us against
+17-35 us for the configs[2] shapes at 64 rows)."""
+
 USE_TCGEN05 = True
-"""bfloat16 products with more than SKINNY_ROWS rows run on this package's tcgen05 kernel;
-False hands them to the vendor library instead (kept for measuring one against the other)."""
+"""False hands every product above SKINNY_ROWS to the vendor library (kept for measuring one
+against the other)."""
 
 
 def _tensor_core(a: torch.Tensor, weight: torch.Tensor) -> bool:
     return (USE_TCGEN05 and a.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and a.is_cuda
-            and a.shape[0] > SKINNY_ROWS and a.shape[1] % 8 == 0 and a.is_contiguous() and weight.is_contiguous())
+            and a.shape[0] >= TENSOR_CORE_ROWS and a.shape[1] % 8 == 0 and a.is_contiguous()
+            and weight.is_contiguous())
 
 
 def _gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, multiplier: float = 1.0,

@@ -210,7 +210,7 @@ def test_linear_is_true_float32(ops):
     close(ops.linear(ab, wb), (ab.double() @ wb.double().t()).float(), torch.bfloat16, scale=3)
 
 
-@pytest.mark.parametrize("m", [1, 3, 8, 11, 16])
+@pytest.mark.parametrize("m", [1, 3, 8, 11, 16, 23, 32, 47, 64])
 @pytest.mark.parametrize("n,k", [(2048, 2048), (6144, 2048), (2048, 6144), (1000, 96), (777, 160), (50, 8), (5000, 520)])
 def test_skinny_products(ops, m, n, k):
     """The weight-streaming kernel and its fused epilogues against float64 products of the
@@ -218,16 +218,23 @@ def test_skinny_products(ops, m, n, k):
     a = rand(m, k, dtype=torch.bfloat16, seed=m)
     w = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=n + k)
     exact = a.double() @ w.double().t()
-    close(ops.linear(a, w), exact, torch.bfloat16)
     z = exact.float().bfloat16().double()
-    close(ops.linear_softcap(a, w, 3.0, 7.0), 7.0 * torch.tanh(z * 3.0 / 7.0), torch.bfloat16)
-    close(ops.linear_softcap(a, w, 0.5, None), z * 0.5, torch.bfloat16)
+
+    def skinny(epilogue, out, multiplier=1.0, cap=0.0):  # the kernel itself, whatever `linear` would pick
+        return ops._gemm_skinny(a, w, out, epilogue, multiplier, cap)
+
+    close(skinny(0, torch.empty(m, n, dtype=torch.bfloat16, device="cuda")), exact, torch.bfloat16)
+    close(skinny(2, torch.empty(m, n, dtype=torch.float32, device="cuda"), 3.0, 7.0), 7.0 * torch.tanh(z * 3.0 / 7.0),
+          torch.bfloat16)
+    close(skinny(2, torch.empty(m, n, dtype=torch.float32, device="cuda"), 0.5, 0.0), z * 0.5, torch.bfloat16)
     if n % 2 == 0:
         g, u = z[:, : n // 2], z[:, n // 2:]
-        close(ops.linear_swiglu(a, w), g * torch.sigmoid(g) * u, torch.bfloat16)
+        close(skinny(1, torch.empty(m, n // 2, dtype=torch.bfloat16, device="cuda")), g * torch.sigmoid(g) * u,
+              torch.bfloat16)
+    close(ops.linear(a, w), exact, torch.bfloat16)
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 128, 128), (17, 1000, 96), (200, 300, 136), (300, 778, 160),
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 128, 128), (129, 1000, 96), (200, 300, 136), (300, 778, 160),
                                    (2048, 2048, 2048), (1000, 6144, 2048), (260, 2048, 6144), (130, 12288, 512)])
 def test_tcgen05_products(ops, m, n, k):
     """The tcgen05/TMA kernel and its epilogues against float64 products of the same bfloat16
