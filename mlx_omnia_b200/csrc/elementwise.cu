@@ -301,6 +301,70 @@ __global__ void qk_norm_rope_store_kernel(const T* __restrict__ proj, int row_st
   for (int i = 2 * rhalf + lane; i < d; i += 32) dst[i] = from_f32<T>(v[i] * scale);
 }
 
+// The same step for head sizes that are multiples of 32 with full (or no) rotation: lane l owns
+// VW = d / 32 contiguous dims, read and written as one vector; the rotation partner of a dim in
+// the first half lives 16 lanes away.
+template <typename T, int VW>
+struct alignas(sizeof(T) * VW) HeadPack {
+  T v[VW];
+};
+
+template <typename T, int VW>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_store_vec_kernel(const T* __restrict__ proj, int row_stride, int q_col, int k_col, int v_col, int nq,
+                              int nkv, float eps, const float* __restrict__ inv_freq,
+                              const int* __restrict__ positions, const long long* __restrict__ slot_mapping,
+                              T* __restrict__ q_out, T* __restrict__ pages, int page_size, long long num_slots,
+                              int* err) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int d = 32 * VW;
+  __shared__ float cos_s[d / 2], sin_s[d / 2];
+  const int t = blockIdx.x;  // one block per token: the token's angles are computed once for all heads
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (inv_freq != nullptr) {
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < d / 2; i += blockDim.x) sincosf(pos * inv_freq[i], &sin_s[i], &cos_s[i]);
+  }
+  __syncthreads();
+  const long long slot = slot_mapping != nullptr ? slot_mapping[t] : -1;
+  if (nkv > 0 && slot >= num_slots && threadIdx.x == 0) atomicOr(err, OMNIA_ERR_SLOT);
+  for (int hs = warp; hs < nq + 2 * nkv; hs += blockDim.x >> 5) {
+    const int kind = hs < nq ? 0 : (hs < nq + nkv ? 1 : 2);
+    const int head = kind == 0 ? hs : (kind == 1 ? hs - nq : hs - nq - nkv);
+    const T* src = proj + (size_t)t * row_stride + (kind == 0 ? q_col : kind == 1 ? k_col : v_col) + (size_t)head * d;
+    T* dst;
+    if (kind == 0) {
+      dst = q_out + ((size_t)t * nq + head) * d;
+    } else {
+      if (slot < 0 || slot >= num_slots) continue;
+      const long long page = slot / page_size, off = slot % page_size;
+      dst = pages + (((page * 2 + (kind == 2)) * nkv + head) * page_size + off) * d;
+    }
+    HeadPack<T, VW> pack = *reinterpret_cast<const HeadPack<T, VW>*>(src + lane * VW);
+    if (kind != 2) {
+      float v[VW], ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < VW; ++i) {
+        v[i] = to_f32(pack.v[i]);
+        ss += v[i] * v[i];
+      }
+      const float scale = eps >= 0.f ? rsqrtf(warp_sum(ss) / (float)d + eps) : 1.f;
+#pragma unroll
+      for (int i = 0; i < VW; ++i) {
+        float mine = v[i] * scale;
+        if (inv_freq != nullptr) {
+          const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+          const float c = cos_s[(lane & 15) * VW + i], sn = sin_s[(lane & 15) * VW + i];
+          mine = lane < 16 ? mine * c - other * sn : other * sn + mine * c;
+        }
+        pack.v[i] = from_f32<T>(mine);
+      }
+    }
+    *reinterpret_cast<HeadPack<T, VW>*>(dst + lane * VW) = pack;
+  }
+}
+
 extern "C" int omnia_qk_norm_rope_store(const void* proj, int row_stride, int q_col, int k_col,
                                         int v_col, int nq, int nkv, int d, float eps,
                                         const float* inv_freq, int rot, const int* positions,
@@ -311,6 +375,24 @@ extern "C" int omnia_qk_norm_rope_store(const void* proj, int row_stride, int q_
   if (d > 256 || (d & 1) || rot > d || (rot & 1)) return (int)cudaErrorInvalidValue;
   const int heads = nq + 2 * nkv;
   dim3 grid(tokens, (heads + 3) / 4);
+  // Head sizes 64, 128, 256 with full or no rotation, and operands aligned for vector access.
+  const bool vector_ok = (rot == d || inv_freq == nullptr) && (d == 64 || d == 128 || d == 256) &&
+                         row_stride % 8 == 0 && q_col % 8 == 0 && k_col % 8 == 0 && v_col % 8 == 0 &&
+                         ((uintptr_t)proj & 15) == 0 && ((uintptr_t)q_out & 15) == 0 && ((uintptr_t)pages & 15) == 0;
+  if (vector_ok) {
+    OMNIA_DISPATCH_DTYPE(dtype, {
+      if (d == 64)
+        launch_pdl(qk_norm_rope_store_vec_kernel<T, 2>, tokens, 256, 0, stream, (const T*)proj, row_stride, q_col, k_col,
+                   v_col, nq, nkv, eps, inv_freq, positions, slot_mapping, (T*)q_out, (T*)pages, page_size, num_slots, err);
+      else if (d == 128)
+        launch_pdl(qk_norm_rope_store_vec_kernel<T, 4>, tokens, 256, 0, stream, (const T*)proj, row_stride, q_col, k_col,
+                   v_col, nq, nkv, eps, inv_freq, positions, slot_mapping, (T*)q_out, (T*)pages, page_size, num_slots, err);
+      else
+        launch_pdl(qk_norm_rope_store_vec_kernel<T, 8>, tokens, 256, 0, stream, (const T*)proj, row_stride, q_col, k_col,
+                   v_col, nq, nkv, eps, inv_freq, positions, slot_mapping, (T*)q_out, (T*)pages, page_size, num_slots, err);
+    });
+    return OMNIA_LAUNCH_RESULT();
+  }
   OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(qk_norm_rope_store_kernel<T>, grid, 128, 0, stream, 
                                   (const T*)proj, row_stride, q_col, k_col, v_col, nq, nkv, d, eps,
                                   inv_freq, rot, positions, slot_mapping, (T*)q_out, (T*)pages,
