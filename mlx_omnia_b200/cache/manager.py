@@ -33,6 +33,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from mlx_omnia_b200.parts.base import KVSpec, StateSpec
@@ -91,6 +92,12 @@ class RequestCache:
     tables: list[list[int]] = field(default_factory=list)  # per group: physical page per logical page (-1 freed)
     slot: int = -1
     fresh: bool = True  # no step has run for it yet
+    # int32 copies of `tables` (capacity grown by doubling; entries beyond len(tables[g]) are -1),
+    # so that a step lays its block tables out with array copies instead of Python loops
+    arrays: list[np.ndarray] = field(default_factory=list)
+
+    def table_array(self, group: int) -> np.ndarray:
+        return self.arrays[group][: len(self.tables[group])]
 
 
 class CacheManager:
@@ -153,7 +160,8 @@ class CacheManager:
             raise CacheError(f"request {request_id!r} is already open")
         if self.slots.free == 0:
             raise CacheError("no free request slot")
-        request = RequestCache(request_id, tables=[[] for _ in self.groups], slot=self.slots.take())
+        request = RequestCache(request_id, tables=[[] for _ in self.groups], slot=self.slots.take(),
+                               arrays=[np.full(16, -1, dtype=np.int32) for _ in self.groups])
         self.requests[request_id] = request
         return request
 
@@ -166,9 +174,14 @@ class CacheManager:
         for n, group in zip(need, self.groups):
             if n > group.pool.free:
                 raise CacheError(f"group {group.spec} needs {n} pages, {group.pool.free} free")
-        for n, group, table in zip(need, self.groups, request.tables):
+        for g, (n, group, table) in enumerate(zip(need, self.groups, request.tables)):
+            if len(table) + n > len(request.arrays[g]):
+                grown = np.full(max(2 * len(request.arrays[g]), len(table) + n), -1, dtype=np.int32)
+                grown[: len(table)] = request.arrays[g][: len(table)]
+                request.arrays[g] = grown
             for _ in range(n):
-                table.append(group.pool.take())
+                request.arrays[g][len(table)] = page = group.pool.take()
+                table.append(page)
         request.tokens += new_tokens
 
     def slot_of(self, request: RequestCache, group: int, position: int) -> int:
@@ -182,16 +195,17 @@ class CacheManager:
         `tokens` positions written, the next query sits at position >= tokens and sees
         keys >= tokens - window + 1. Returns how many pages were freed."""
         freed = 0
-        for group, table in zip(self.groups, request.tables):
+        for g, (group, table) in enumerate(zip(self.groups, request.tables)):
             window = group.spec.window
             if window is None:
                 continue
             dead_below = request.tokens - window + 1  # positions < this are never read again
-            for index in range(min(len(table), max(dead_below, 0) // self.page_size)):
-                if table[index] >= 0:
-                    group.pool.give(table[index])
-                    table[index] = -1
-                    freed += 1
+            for index in range(min(len(table), max(dead_below, 0) // self.page_size) - 1, -1, -1):
+                if table[index] < 0:
+                    break  # everything below was given back earlier
+                group.pool.give(table[index])
+                table[index] = request.arrays[g][index] = -1
+                freed += 1
         return freed
 
     def close(self, request_id: str) -> None:

@@ -18,7 +18,6 @@
 namespace {
 
 typedef __nv_bfloat16 bf16;
-constexpr int WARPS = 8;
 
 enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_SOFTCAP = 2 };
 
@@ -42,7 +41,8 @@ __device__ __forceinline__ void mma_bf16(float* c, unsigned a0, unsigned a1, uns
 // NT: activation tiles of 8 rows (1, 2, 4 or 8). RG: weight row groups of 16 per warp (1 or 2).
 // With EPI_SWIGLU, RG is 2 and the second group lies `pair_offset` rows after the first.
 // UNROLL: k-blocks whose loads are issued together (fewer when many activation tiles need registers).
-template <int NT, int RG, int EPI, int UNROLL = (NT <= 2 ? 4 : 2)>
+// WARPS: slices of k per block (8, or 16 for matrices with so few rows that the grid is one wave).
+template <int NT, int RG, int EPI, int WARPS, int UNROLL = (NT <= 2 ? 4 : 2)>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, void* __restrict__ out,
                    int m, int n, int k, int pair_offset, float multiplier, float cap) {
@@ -163,20 +163,29 @@ gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, void*
   }
 }
 
-template <int NT, int RG, int EPI>
-int launch_variant(int blocks, const bf16* a, const bf16* w, void* out, int m, int n, int k, int pair_offset,
-                   float multiplier, float cap, cudaStream_t stream) {
+template <int NT, int RG, int EPI, int WARPS>
+int launch_warps(int blocks, const bf16* a, const bf16* w, void* out, int m, int n, int k, int pair_offset,
+                 float multiplier, float cap, cudaStream_t stream) {
   constexpr size_t smem = sizeof(float) * WARPS * RG * 16 * (NT * 8 + 1);
   static bool configured = false;
   if (smem > 48 * 1024 && !configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NT, RG, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NT, RG, EPI, WARPS>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  launch_pdl(gemm_skinny_kernel<NT, RG, EPI>, blocks, WARPS * 32, smem, stream, a, w, out, m, n, k, pair_offset,
+  launch_pdl(gemm_skinny_kernel<NT, RG, EPI, WARPS>, blocks, WARPS * 32, smem, stream, a, w, out, m, n, k, pair_offset,
              multiplier, cap);
   return OMNIA_LAUNCH_RESULT();
+}
+
+template <int NT, int RG, int EPI>
+int launch_variant(int blocks, const bf16* a, const bf16* w, void* out, int m, int n, int k, int pair_offset,
+                   float multiplier, float cap, cudaStream_t stream) {
+  // A grid of at most one wave leaves every block a long slice of k: sixteen warps halve it.
+  if (NT <= 2 && blocks <= 148)
+    return launch_warps<NT, RG, EPI, 16>(blocks, a, w, out, m, n, k, pair_offset, multiplier, cap, stream);
+  return launch_warps<NT, RG, EPI, 8>(blocks, a, w, out, m, n, k, pair_offset, multiplier, cap, stream);
 }
 
 template <int NT, int EPI>

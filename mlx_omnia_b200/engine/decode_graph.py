@@ -154,9 +154,9 @@ class DecodeGraphs:
             table[:] = -1
             slots = np.full(batch, -1, dtype=np.int64)
             for i, (e, start) in enumerate(zip(entries, starts)):
-                pages = e.request.tables[g]
+                pages = e.request.table_array(g)
                 table[i, : len(pages)] = pages
-                slots[i] = pages[start // page] * page + start % page
+                slots[i] = int(pages[start // page]) * page + start % page
             offset, length = fields[f"slots{g}"]
             host[offset: offset + length].view(np.int64)[:] = slots
 

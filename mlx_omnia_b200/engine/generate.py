@@ -93,7 +93,7 @@ class Generator:
             return []
         entries = []
         for planned in plan.entries:
-            tokens = planned.request.tokens[planned.start: planned.start + planned.count]
+            tokens = planned.request.token_slice(planned.start, planned.count)
             entries.append(StepEntry(planned.request.cache, tokens, [planned.count - 1] if planned.samples else []))
         try:
             logits = self.engine.runner.run(entries, copy=False)
@@ -104,9 +104,11 @@ class Generator:
         sampling = [p.request for p in plan.entries if p.samples]
         sampled: dict[str, int] = {}
         if sampling:
+            histories = [r.token_slice(max(0, len(r.prompt) + len(r.generated) - r.sampling.penalty_context),
+                                       r.sampling.penalty_context) if r.sampling.repetition_penalty != 1.0 else []
+                         for r in sampling]
             chosen = sample_rows(logits, [r.sampling for r in sampling], [self._seeds[r.request_id] for r in sampling],
-                                 [len(r.generated) for r in sampling],
-                                 [r.tokens[-r.sampling.penalty_context:] for r in sampling])
+                                 [len(r.generated) for r in sampling], histories)
             sampled = dict(zip((r.request_id for r in sampling), chosen.tolist()))
         outputs = self.scheduler.commit(plan, sampled)
         for output in outputs:

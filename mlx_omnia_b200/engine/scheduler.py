@@ -40,7 +40,7 @@ from mlx_omnia_b200.cache.manager import CacheManager, RequestCache
 from mlx_omnia_b200.sampling.options import SamplingParams
 
 
-@dataclass
+@dataclass(eq=False)
 class Request:
     request_id: str
     prompt: list[int]
@@ -58,6 +58,15 @@ class Request:
     @property
     def tokens(self) -> list[int]:
         return self.prompt + self.generated
+
+    def token_slice(self, start: int, count: int) -> list[int]:
+        """tokens[start: start + count] without building the whole list."""
+        split = len(self.prompt)
+        if start >= split:
+            return self.generated[start - split: start - split + count]
+        if start + count <= split:
+            return self.prompt[start: start + count]
+        return self.prompt[start:] + self.generated[: start + count - split]
 
     @property
     def pending(self) -> int:
@@ -172,14 +181,14 @@ class Scheduler:
 
         # (1) decoding requests, oldest first; preempt the newest while pages are short.
         decoding = sorted((r for r in self.running if r.pending == 1 and r.generated), key=lambda r: r.order)
-        planned: list[Request] = []
+        planned: set[int] = set()  # ids of requests that have an entry in this plan
         for request in decoding:
             if request.status != "running" or budget < 1:
                 continue
             while self._affordable(request, 1, reserved) < 1:
                 victim = max(self.running, key=lambda r: r.order)
-                if victim in planned:  # give back what the plan promised it
-                    planned.remove(victim)
+                if id(victim) in planned:  # give back what the plan promised it
+                    planned.discard(id(victim))
                     entries[:] = [e for e in entries if e.request is not victim]
                     reserved = [0] * len(self.cache.groups)
                     for e in entries:
@@ -193,11 +202,12 @@ class Scheduler:
                 continue
             entries.append(PlannedEntry(request, request.computed, 1, True))
             self._reserve(request, 1, reserved)
-            planned.append(request)
+            planned.add(id(request))
             budget -= 1
 
         # (2) running requests that still have a prompt (or a recomputation) to read.
-        for request in sorted((r for r in self.running if r not in planned and r.pending > 0), key=lambda r: r.order):
+        for request in sorted((r for r in self.running if id(r) not in planned and r.pending > 0),
+                              key=lambda r: r.order):
             if budget < 1:
                 break
             count = self._affordable(request, min(request.pending, budget), reserved)
@@ -210,7 +220,7 @@ class Scheduler:
         # (3) admissions, strictly first come first served.
         while self.waiting and budget >= 1 and len(self.running) < self.max_running and self.cache.slots.free > 0:
             request = self.waiting[0]
-            if request in preempted:
+            if any(request is p for p in preempted):
                 break  # it lost its pages in this very plan
             count = self._affordable(request, min(request.pending, budget), reserved)
             if count < 1:

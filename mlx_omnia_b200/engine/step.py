@@ -85,10 +85,10 @@ class StepRunner:
             table = np.full((len(entries), max(width, 1)), -1, dtype=np.int32)
             slots = np.empty(total, dtype=np.int64)
             for i, e in enumerate(entries):
-                t = np.asarray(e.request.tables[g], dtype=np.int64)
+                t = e.request.table_array(g)
                 table[i, : len(t)] = t
                 pos = positions[cu[i]: cu[i + 1]].astype(np.int64)
-                slots[cu[i]: cu[i + 1]] = t[pos // page] * page + pos % page
+                slots[cu[i]: cu[i + 1]] = t[pos // page].astype(np.int64) * page + pos % page
             groups[g] = (self._device(table), self._device(slots))
         return StepContext(
             num_tokens=total, num_seqs=len(entries),
@@ -105,9 +105,10 @@ class StepRunner:
         page = self.cache.page_size
         request.tokens -= count
         keep = -(-request.tokens // page)
-        for group, table in zip(self.cache.groups, request.tables):
+        for g, (group, table) in enumerate(zip(self.cache.groups, request.tables)):
             while len(table) > keep:
                 group.pool.give(table.pop())
+                request.arrays[g][len(table)] = -1
 
     def layer_contexts(self, step: StepContext) -> list[LayerContext]:
         cache = self.cache
