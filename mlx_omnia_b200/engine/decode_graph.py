@@ -161,9 +161,10 @@ class DecodeGraphs:
             host[offset: offset + length].view(np.int64)[:] = slots
 
     # -- one step ----------------------------------------------------------------------
-    def run(self, entries, copy: bool = True) -> torch.Tensor:
+    def run(self, entries, copy: bool = True, device_tokens: torch.Tensor | None = None) -> torch.Tensor:
         """Run a step whose entries all bring one token. -> logits [wanted, vocab].
-        With `copy` False the result is the graph's own buffer, valid until the next step."""
+        With `copy` False the result is the graph's own buffer, valid until the next step.
+        `device_tokens` (int32 [entries], on the device) replace the entries' token ids."""
         runner, cache = self.runner, self.runner.cache
         starts = [e.request.tokens for e in entries]
         grown = []
@@ -185,6 +186,8 @@ class DecodeGraphs:
             captured.copied.synchronize()  # the pinned buffer is free to be written again
         self._fill(captured.host, captured.fields, batch, width, entries, starts)
         captured.device.copy_(captured.host_tensor, non_blocking=True)
+        if device_tokens is not None:
+            captured.step.token_ids[: len(entries)].copy_(device_tokens[: len(entries)])
         if captured.copied is None:
             captured.copied = torch.cuda.Event()
         captured.copied.record()

@@ -21,7 +21,7 @@ from pathlib import Path
 import torch
 
 from mlx_omnia_b200.engine.engine import DTYPES, Engine, EngineArgs
-from mlx_omnia_b200.engine.scheduler import Request, Scheduler, StepOutput
+from mlx_omnia_b200.engine.scheduler import PlannedEntry, Request, Scheduler, StepOutput, StepPlan
 from mlx_omnia_b200.engine.step import StepEntry
 from mlx_omnia_b200.kernels import ops
 from mlx_omnia_b200.sampling.batch import sample_rows
@@ -58,6 +58,16 @@ class TokenIdTokenizer:
         return "".join(f"{i} " for i in ids)
 
 
+@dataclass
+class _Launched:
+    """A step that is running on the GPU: its plan, the requests it samples for and their
+    chosen tokens (still on the device)."""
+
+    plan: StepPlan
+    sampling: list[Request]
+    chosen: torch.Tensor | None
+
+
 class Generator:
     """Continuous batching over one `Engine`."""
 
@@ -66,6 +76,8 @@ class Generator:
         self.scheduler = Scheduler(engine.cache, max_tokens_per_step=max_tokens_per_step, max_running=max_running)
         self._ids = itertools.count()
         self._seeds: dict[str, int] = {}
+        self._in_flight: _Launched | None = None
+        self.pipelined = True  # launch the next decode step before reading this one's tokens
 
     def add(self, prompt: Sequence[int], options: GenerationOptions, request_id: str | None = None) -> Request:
         prompt = [int(t) for t in prompt]
@@ -86,40 +98,97 @@ class Generator:
         self.scheduler.abort(request_id)
         self._seeds.pop(request_id, None)
 
-    def step(self) -> list[StepOutput]:
-        """Plan, run and commit one step; returns what each sampling request produced."""
-        plan = self.scheduler.plan()
-        if not plan.entries:
-            return []
+    def drain(self) -> list[StepOutput]:
+        """Commit the step that is still in flight, if any."""
+        launched, self._in_flight = self._in_flight, None
+        return self._finalize(launched) if launched is not None else []
+
+    # -- one step -----------------------------------------------------------------------------
+    # A decode step's tokens are chosen on the GPU and can feed the next step from there, so the
+    # host need not wait for them before it launches that step: while the GPU runs step n + 1 the
+    # host reads step n's tokens (one step late, as the reference does: src/mlx_omnia/engine/
+    # batching.py:598-604), commits them and prepares step n + 2. A request that turns out to
+    # have ended on a stop token has then computed one token too many, which is dropped.
+
+    def _launch(self, plan: StepPlan, device_tokens: torch.Tensor | None = None) -> "_Launched":
         entries = []
         for planned in plan.entries:
-            tokens = planned.request.token_slice(planned.start, planned.count)
+            tokens = [0] * planned.count if device_tokens is not None else \
+                planned.request.token_slice(planned.start, planned.count)
             entries.append(StepEntry(planned.request.cache, tokens, [planned.count - 1] if planned.samples else []))
         try:
-            logits = self.engine.runner.run(entries, copy=False)
+            logits = self.engine.runner.run(entries, copy=False, device_tokens=device_tokens)
         except Exception:
             for planned in plan.entries:  # a failed step fails its requests and frees what they hold
                 self.scheduler._finish(planned.request, "abort")
             raise
         sampling = [p.request for p in plan.entries if p.samples]
-        sampled: dict[str, int] = {}
+        chosen = None
         if sampling:
+            ahead = 1 if device_tokens is not None else 0  # draws already spent by the step not yet committed
             histories = [r.token_slice(max(0, len(r.prompt) + len(r.generated) - r.sampling.penalty_context),
                                        r.sampling.penalty_context) if r.sampling.repetition_penalty != 1.0 else []
                          for r in sampling]
             chosen = sample_rows(logits, [r.sampling for r in sampling], [self._seeds[r.request_id] for r in sampling],
-                                 [len(r.generated) for r in sampling], histories)
-            sampled = dict(zip((r.request_id for r in sampling), chosen.tolist()))
-        outputs = self.scheduler.commit(plan, sampled)
+                                 [len(r.generated) + ahead for r in sampling], histories)
+        return _Launched(plan, sampling, chosen)
+
+    def _finalize(self, launched: "_Launched") -> list[StepOutput]:
+        """Read the launched step's tokens (this waits for it) and commit them."""
+        plan = launched.plan
+        tokens = launched.chosen.tolist() if launched.chosen is not None else []
+        sampled = dict(zip((r.request_id for r in launched.sampling), tokens))
+        # A request that ended (a stop token, an abort) after this step was launched is left out.
+        live = [e for e in plan.entries if e.request.status == "running"]
+        outputs = self.scheduler.commit(StepPlan(live, plan.preempted), sampled)
         for output in outputs:
             if output.finished:
                 self._seeds.pop(output.request.request_id, None)
         return outputs
 
+    def _next_decode_plan(self, launched: "_Launched") -> StepPlan | None:
+        """The plan of the step after `launched`, if it can be made before `launched`'s tokens
+        are known: every entry decodes, nobody waits for admission, no request needs its own
+        last token on the host (repetition penalty), and the pages are there."""
+        if self.engine.runner.graphs is None or self.scheduler.waiting or not self.pipelined:
+            return None
+        entries = launched.plan.entries
+        if len(entries) != len(self.scheduler.running) or not all(e.count == 1 and e.samples for e in entries):
+            return None
+        following = []
+        reserved = [0] * len(self.engine.cache.groups)
+        for e in entries:
+            r = e.request
+            if r.status != "running" or r.sampling.repetition_penalty != 1.0:
+                return None
+            if len(r.generated) + 2 > r.max_tokens:  # it ends with the launched step's token: plan normally
+                return None
+            if self.scheduler._affordable(r, 1, reserved) < 1:  # (the launched step's page is already taken)
+                return None
+            self.scheduler._reserve(r, 1, reserved)
+            following.append(PlannedEntry(r, e.start + 1, 1, True))
+        return StepPlan(following, [])
+
+    def step(self) -> list[StepOutput]:
+        """Run one step (or, in steady decoding, launch the next one and) return what the oldest
+        step in flight produced for each sampling request."""
+        if self._in_flight is None:
+            plan = self.scheduler.plan()
+            if not plan.entries:
+                return []
+            self._in_flight = self._launch(plan)
+        launched = self._in_flight
+        following = self._next_decode_plan(launched)
+        if following is not None:
+            self._in_flight = self._launch(following, device_tokens=launched.chosen)
+        else:
+            self._in_flight = None
+        return self._finalize(launched)
+
     def run(self) -> None:
         """Step until every request has finished."""
-        while not self.scheduler.idle:
-            if not self.step() and not self.scheduler.running and self.scheduler.waiting:
+        while not self.scheduler.idle or self._in_flight is not None:
+            if not self.step() and self._in_flight is None and not self.scheduler.running and self.scheduler.waiting:
                 raise RuntimeError("the scheduler can admit nothing: the cache pool is too small")
 
     def generate(self, prompts: Sequence[Sequence[int]], options: GenerationOptions) -> list[list[int]]:

@@ -124,18 +124,22 @@ class StepRunner:
         return contexts
 
     # -- the step ----------------------------------------------------------------------
-    def run(self, entries: list[StepEntry], copy: bool = True) -> torch.Tensor:
+    def run(self, entries: list[StepEntry], copy: bool = True, device_tokens: torch.Tensor | None = None) -> torch.Tensor:
         """One step. Steps in which every request brings a single token are replayed
         from a captured CUDA graph when graphs are on; `copy=False` then returns the
-        graph's own logits buffer, which the next step overwrites."""
+        graph's own logits buffer, which the next step overwrites. `device_tokens`
+        (int32 on the device, one per entry; graph steps only) are the step's tokens when
+        the host does not know them yet."""
         fresh_slots = [e.request.slot for e in entries if e.request.fresh]
         if fresh_slots and self.cache.state:
             index = torch.as_tensor(fresh_slots, device=self.runtime.device)
             for state in self.cache.state.values():
                 state.index_fill_(0, index, 0)
         if self.graphs is not None and entries and all(len(e.tokens) == 1 and e.want in ([], [0]) for e in entries):
-            logits = self.graphs.run(entries, copy)
+            logits = self.graphs.run(entries, copy, device_tokens)
         else:
+            if device_tokens is not None:
+                raise ValueError("tokens that live on the device can only feed a captured single-token step")
             step = self.build_context(entries)
             logits = self.model.forward(step, self.layer_contexts(step))
         for entry in entries:

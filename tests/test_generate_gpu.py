@@ -117,3 +117,31 @@ def test_captured_decode_steps_equal_eager_ones(name, dtype):
         picks.append(results[1][at + live.index(0)])
         at += len(live)
     assert plain_impl.relative_diff(torch.stack(picks), expect) < (1e-4 if dtype == "float32" else 3e-2)
+
+
+def test_pipelined_decoding_gives_the_same_tokens(tmp_path):
+    """Launching step n + 1 from the tokens still on the device, before step n's tokens are read,
+    changes nothing: greedy and seeded sampling give the ids of the step-by-step loop, stop tokens
+    end a request at the same place, and nothing is left in the cache."""
+    from mlx_omnia_b200.engine.engine import Engine, EngineArgs
+    from mlx_omnia_b200.engine.generate import Generator
+
+    raw, weights = tiny_configs.config("B"), tiny_configs.tensors("B")
+    prompts = [tiny_configs.prompt(n, 1000, 300 + n) for n in (5, 19, 33)]
+    plain_ids = plain_impl.greedy_generate(raw, weights, prompts[0], 24)
+    for options in (GenerationOptions(max_tokens=24, stop=()),
+                    GenerationOptions(max_tokens=24, stop=(plain_ids[9],)),
+                    GenerationOptions(max_tokens=17, sampler=sampler(temperature(0.9), top_k(30), seed=5), stop=())):
+        results = []
+        for pipelined in (False, True):
+            engine = Engine.from_tensors(raw, weights, EngineArgs(dtype="float32", page_size=8, cache_tokens=512,
+                                                                  max_requests=4))
+            generator = Generator(engine)
+            generator.pipelined = pipelined
+            results.append(generator.generate(prompts, options))
+            assert not engine.cache.requests and generator._in_flight is None
+            assert all(g.pool.free == g.pool.count for g in engine.cache.groups)
+        assert results[0] == results[1]
+        if options.sampler.greedy:
+            cut = plain_ids.index(plain_ids[9]) if options.stop else 24
+            assert results[1][0] == plain_ids[:cut]
