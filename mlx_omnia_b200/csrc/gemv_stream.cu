@@ -1,0 +1,372 @@
+// out[m, n] = sum_k a[m, k] * w[n, k] for up to 16 rows m (decode steps), the weight matrix
+// streamed from HBM exactly once through a ring in shared memory.
+//
+// One block per SM owns a contiguous run of 16-row tiles of the matrix. A producer warp copies
+// the tiles into the ring with TMA, boxes of 8 rows x 256 columns (4 KB), 1024 columns of a tile
+// (32 KB) per stage, four stages, signalled by mbarriers. Measured on B200 while tuning this:
+// a stage costs about half a microsecond to hand over whatever its size, so stages of 16 KB
+// reach 4.3 TB/s and stages of 32 KB 6.8 TB/s with the same bytes in flight; rows copied one by
+// one (1 KB bulk copies) reach 2.6 TB/s. The weights never depend on the kernel before this
+// one, so the producer starts at once (the launch is a programmatic dependent launch) and only
+// the eight consumer warps wait for the activations. Each consumer warp takes 128 columns of
+// every stage, builds m16n8k16 fragments from 16-byte reads (a dot product does not care about
+// the order of k, so eight consecutive k of a weight row meet the same eight k of an activation
+// row and no shuffle is needed), and the warps' partial sums of a tile are added through shared
+// memory in a fixed order: results do not depend on timing. Activations are fetched from L2 one
+// stage ahead into registers.
+//
+// Epilogues: plain store; SwiGLU (a tile is eight gate rows over the eight up rows of the same
+// columns, and the block stores silu(gate) * up); soft cap (float32 logits).
+// bfloat16 operands, float32 accumulation; k a multiple of 8; a, w 16-byte aligned.
+//
+// Every wait on a barrier is bounded: when the bound is hit the block raises OMNIA_ERR_TIMEOUT
+// in the error word, its warps leave their loops, the producer waits (bounded again) for the
+// copies it still has in flight, and the block returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define OMNIA_ERR_TIMEOUT 8
+
+#ifndef GEMV_STAGES
+#define GEMV_STAGES 4
+#endif
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int CONSUMER_WARPS = 8;
+constexpr int CONSUMERS = CONSUMER_WARPS * 32;
+constexpr int THREADS = CONSUMERS + 32;
+constexpr int TILE_ROWS = 16;
+#ifndef GEMV_WARP_COLS
+#define GEMV_WARP_COLS 128
+#endif
+constexpr int WARP_COLS = GEMV_WARP_COLS;                  // columns of a stage per consumer warp (a multiple of 32)
+constexpr int KBLOCKS = WARP_COLS / 32;                    // 32-column steps of a warp per stage
+constexpr int STAGE_COLS = CONSUMER_WARPS * WARP_COLS;     // 1024
+constexpr int BOX_ROWS = 8, BOX_COLS = 256;                // one TMA copy; lands dense, [8][256]
+constexpr int BOX_BYTES = BOX_ROWS * BOX_COLS * 2;
+constexpr int BOXES_ACROSS = STAGE_COLS / BOX_COLS;        // boxes side by side in a stage
+constexpr int STAGE_BOXES = 2 * BOXES_ACROSS;              // upper eight rows, then lower eight rows
+constexpr int STAGE_BYTES = STAGE_BOXES * BOX_BYTES;
+static_assert(STAGE_COLS % BOX_COLS == 0 && STAGE_BOXES <= 32, "a stage is at most 32 boxes");
+constexpr int STAGES = GEMV_STAGES;
+constexpr uint32_t WAIT_LIMIT = 1u << 20;
+
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_SOFTCAP = 2 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"  // sleeps up to the hint (ns)
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(2000u)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait; false when the block is giving up (its own limit, or another warp's).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try(bar, parity)) return true;
+    if ((i & 63) == 63 && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void mma_bf16(float* c, unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS) : "memory"); }
+
+// The matrix row that row r (0..15) of tile `tile` holds, or -1 when it lies outside the matrix.
+template <int EPI>
+__device__ __forceinline__ int tile_row(int tile, int r, int n, int inner) {
+  if (EPI == EPI_SWIGLU) {
+    const int col = tile * 8 + (r & 7);
+    return col < inner ? (r < 8 ? col : inner + col) : -1;
+  }
+  const int row = tile * TILE_ROWS + r;
+  return row < n ? row : -1;
+}
+
+// NT: activation tiles of 8 rows (1 for m <= 8, 2 for m <= 16).
+template <int NT, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemv_stream_kernel(const bf16* __restrict__ a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
+                   int m, int n, int k, int inner, int tiles, float multiplier, float cap, int* __restrict__ err) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* ring = smem;
+  float (*partial)[CONSUMER_WARPS][TILE_ROWS][NT * 8 + 1] =
+      reinterpret_cast<float (*)[CONSUMER_WARPS][TILE_ROWS][NT * 8 + 1]>(smem + STAGES * STAGE_BYTES);
+  __shared__ __align__(8) unsigned long long bars[2 * STAGES];
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, CONSUMER_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_launch_dependents();  // the next kernel's blocks may start as soon as an SM has room for them
+
+  // This block's tiles: a contiguous run, sizes differing by at most one between blocks.
+  const int base = tiles / gridDim.x, extra = tiles % gridDim.x;
+  const int my_tiles = base + ((int)blockIdx.x < extra ? 1 : 0);
+  const int tile0 = blockIdx.x * base + min((int)blockIdx.x, extra);
+  const int chunks = (k + STAGE_COLS - 1) / STAGE_COLS;
+  const int units = my_tiles * chunks;
+
+  if (warp == CONSUMER_WARPS) {
+    // ---- producer: needs nothing from the kernel before, so it does not wait for it ----
+    int issued = 0;
+    for (int u = 0; u < units; ++u) {
+      const int s = u % STAGES;
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(empty0 + 8 * s, ((u / STAGES) & 1) ^ 1, abort_flag);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      const int tile = tile0 + u / chunks, c = u % chunks;
+      // Lane i copies box i of the stage: half i / BOXES_ACROSS (rows g, then rows g + 8) and
+      // 256 columns. A box that starts outside the matrix is not copied (its rows and columns
+      // are masked by the consumers); one that straddles an edge is filled with zeros there.
+      const int half = lane / BOXES_ACROSS, x = c * STAGE_COLS + (lane % BOXES_ACROSS) * BOX_COLS;
+      const int y = lane < STAGE_BOXES ? tile_row<EPI>(tile, half * 8, n, inner) : -1;
+      const bool copies = y >= 0 && x < k;
+      const unsigned live = __ballot_sync(0xffffffffu, copies);
+      if (lane == 0) mbar_expect_tx(full0 + 8 * s, (uint32_t)__popc(live) * BOX_BYTES);
+      __syncwarp();
+      if (copies) tma_load_2d(smem_u32(ring + s * STAGE_BYTES + lane * BOX_BYTES), &map_w, full0 + 8 * s, x, y);
+      issued = u + 1;
+    }
+    if (issued < units && lane == 0) {
+      // Giving up: the copies already issued must land before the block's shared memory is released.
+      for (int u = max(0, issued - STAGES); u < issued; ++u)
+        for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(full0 + 8 * (u % STAGES), (u / STAGES) & 1); ++i) {
+        }
+    }
+  } else {
+    // ---- consumers ----
+    const int g = lane >> 2, t = lane & 3;
+    const bf16* arow[NT];
+    bool alive[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      alive[j] = 8 * j + g < m;
+      arow[j] = a + (size_t)(alive[j] ? 8 * j + g : 0) * k;
+    }
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    pdl_wait();  // the activations come from the kernel before
+    // The activations of a stage are fetched while the stage before it is worked on: they come
+    // from L2 (the rings leave little room for an L1 cache), which is far.
+    auto fetch = [&](int c, uint4 (&dst)[KBLOCKS][NT]) {
+      const int col0 = c * STAGE_COLS + warp * WARP_COLS + 8 * t;
+#pragma unroll
+      for (int h = 0; h < KBLOCKS; ++h)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+          dst[h][j] = alive[j] && col0 + 32 * h < k ? __ldg(reinterpret_cast<const uint4*>(arow[j] + col0 + 32 * h)) : zero;
+    };
+    uint4 av[KBLOCKS][NT], av_next[KBLOCKS][NT];
+    if (units > 0) fetch(0, av_next);
+    bool ok = true;
+    int s = 0, phase = 0, c = 0, tile_local = 0;
+    for (int u = 0; u < units && ok; ++u) {
+      const int tile = tile0 + tile_local;
+      const int col0 = c * STAGE_COLS + warp * WARP_COLS + 8 * t;  // this thread's first column of the stage
+#pragma unroll
+      for (int h = 0; h < KBLOCKS; ++h)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) av[h][j] = av_next[h][j];
+      if (u + 1 < units) fetch(c + 1 == chunks ? 0 : c + 1, av_next);
+      const bool lo_live = tile_row<EPI>(tile, g, n, inner) >= 0, hi_live = tile_row<EPI>(tile, g + 8, n, inner) >= 0;
+      ok = mbar_wait(full0 + 8 * s, phase, abort_flag);
+      if (!ok) break;
+      // Column warp * WARP_COLS + 32 h + 8 t of the stage: box (that / 256), then 512-byte rows.
+      const int in_stage = warp * WARP_COLS + 8 * t;
+      const uint32_t stage = smem_u32(ring + s * STAGE_BYTES) + (in_stage / BOX_COLS) * BOX_BYTES +
+                             g * (BOX_COLS * 2) + (in_stage % BOX_COLS) * 2;
+#pragma unroll
+      for (int h = 0; h < KBLOCKS; ++h) {
+        const bool live = col0 + 32 * h < k;
+        static_assert(BOX_COLS % WARP_COLS == 0, "a warp's columns of a stage lie in one box");
+        const uint32_t at = stage + 64 * h;
+        uint4 lo = lds128(at), hi = lds128(at + BOXES_ACROSS * BOX_BYTES);
+        if (!live || !lo_live) lo = zero;
+        if (!live || !hi_live) hi = zero;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          mma_bf16(acc[j], lo.x, hi.x, lo.y, hi.y, av[h][j].x, av[h][j].y);
+          mma_bf16(acc[j], lo.z, hi.z, lo.w, hi.w, av[h][j].z, av[h][j].w);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * s);  // the stage may be filled again
+      if (++s == STAGES) s = 0, phase ^= 1;
+      if (++c != chunks) continue;
+      c = 0;
+
+      // The tile is complete: add the warps' partial sums in a fixed order and store.
+      const int buf = tile_local & 1;
+      ++tile_local;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        partial[buf][warp][g][j * 8 + 2 * t] = acc[j][0];
+        partial[buf][warp][g][j * 8 + 2 * t + 1] = acc[j][1];
+        partial[buf][warp][g + 8][j * 8 + 2 * t] = acc[j][2];
+        partial[buf][warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
+        acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+      }
+      consumer_sync();
+      const int out_rows = EPI == EPI_SWIGLU ? 8 : TILE_ROWS;
+      for (int idx = threadIdx.x; idx < out_rows * NT * 8; idx += CONSUMERS) {
+        const int token = idx / out_rows, r = idx % out_rows;
+        if (token >= m) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int s2 = 0; s2 < CONSUMER_WARPS; ++s2) v += partial[buf][s2][r][token];
+        if (EPI == EPI_SWIGLU) {
+          float up = 0.f;
+#pragma unroll
+          for (int s2 = 0; s2 < CONSUMER_WARPS; ++s2) up += partial[buf][s2][8 + r][token];
+          const int col = tile * 8 + r;
+          if (col >= inner) continue;
+          // The two halves are rounded to bfloat16 first, as a separate product would round them.
+          const float gate = __bfloat162float(__float2bfloat16_rn(v));
+          up = __bfloat162float(__float2bfloat16_rn(up));
+          reinterpret_cast<bf16*>(out)[(size_t)token * inner + col] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+        } else {
+          const int col = tile * TILE_ROWS + r;
+          if (col >= n) continue;
+          if (EPI == EPI_SOFTCAP) {
+            const float z = __bfloat162float(__float2bfloat16_rn(v)) * multiplier;
+            reinterpret_cast<float*>(out)[(size_t)token * n + col] = cap > 0.f ? cap * tanhf(z / cap) : z;
+          } else {
+            reinterpret_cast<bf16*>(out)[(size_t)token * n + col] = __float2bfloat16_rn(v);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicOr(err, OMNIA_ERR_TIMEOUT);
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+  static EncodeTiled fn = nullptr;
+  if (fn == nullptr) {
+    void* symbol = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(symbol);
+  }
+  return fn;
+}
+
+// The [rows, k] bfloat16 row-major matrix as a 2-D tensor map with dense boxes of 8 rows x 256 columns;
+// what a box covers beyond the matrix is filled with zeros.
+bool make_map(CUtensorMap* map, const void* base, int rows, int k) {
+  EncodeTiled encode = encode_tiled();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)k * sizeof(bf16)};
+  const cuuint32_t box[2] = {(cuuint32_t)BOX_COLS, (cuuint32_t)BOX_ROWS};
+  const cuuint32_t elem[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int NT, int EPI>
+int launch(const bf16* a, const bf16* w, void* out, int m, int n, int k, int inner, float multiplier, float cap,
+           int* err, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)STAGES * STAGE_BYTES + sizeof(float) * 2 * CONSUMER_WARPS * TILE_ROWS * (NT * 8 + 1);
+  static int sms = 0;
+  if (sms == 0) {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemv_stream_kernel<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      sms = 0;
+      return (int)e;
+    }
+  }
+  CUtensorMap map_w;
+  if (!make_map(&map_w, w, n, k)) return (int)cudaErrorInvalidValue;
+  const int tiles = EPI == EPI_SWIGLU ? (inner + 7) / 8 : (n + TILE_ROWS - 1) / TILE_ROWS;
+  launch_pdl(gemv_stream_kernel<NT, EPI>, min(tiles, sms), THREADS, smem, stream, a, map_w, out, m, n, k, inner, tiles,
+             multiplier, cap, err);
+  return OMNIA_LAUNCH_RESULT();
+}
+
+template <int EPI>
+int launch_rows(const bf16* a, const bf16* w, void* out, int m, int n, int k, int inner, float multiplier, float cap,
+                int* err, cudaStream_t stream) {
+  if (m <= 8) return launch<1, EPI>(a, w, out, m, n, k, inner, multiplier, cap, err, stream);
+  return launch<2, EPI>(a, w, out, m, n, k, inner, multiplier, cap, err, stream);
+}
+
+}  // namespace
+
+// epilogue: 0 store bfloat16 [m, n]; 1 SwiGLU, w = [gate rows | up rows] with n = 2 * inner,
+// out bfloat16 [m, inner]; 2 soft cap, out float32 [m, n]. err: the device error word.
+extern "C" int omnia_gemv_stream(const void* a, const void* w, void* out, int m, int n, int k, int epilogue,
+                                 float multiplier, float cap, int* err, cudaStream_t stream) {
+  if (m == 0 || n == 0) return 0;
+  if (m > 16 || k % 8 != 0 || k <= 0) return (int)cudaErrorInvalidValue;
+  if (((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) != 0) return (int)cudaErrorInvalidValue;
+  const bf16* ap = (const bf16*)a;
+  const bf16* wp = (const bf16*)w;
+  if (epilogue == EPI_SWIGLU) {
+    if (n % 2) return (int)cudaErrorInvalidValue;
+    return launch_rows<EPI_SWIGLU>(ap, wp, out, m, n, k, n / 2, 1.f, 0.f, err, stream);
+  }
+  if (epilogue == EPI_SOFTCAP) return launch_rows<EPI_SOFTCAP>(ap, wp, out, m, n, k, 0, multiplier, cap, err, stream);
+  if (epilogue != EPI_STORE) return (int)cudaErrorInvalidValue;
+  return launch_rows<EPI_STORE>(ap, wp, out, m, n, k, 0, 1.f, 0.f, err, stream);
+}

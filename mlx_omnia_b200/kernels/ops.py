@@ -319,6 +319,28 @@ def _skinny(a: torch.Tensor, weight: torch.Tensor) -> bool:
             and a.shape[1] % 8 == 0 and a.is_cuda)
 
 
+USE_GEMV_STREAM = True
+"""Products of up to 16 rows run on the kernel that streams the matrix through a shared-memory
+ring (gemv_stream.cu); off, they run on the register-fed kernel (gemm_skinny.cu)."""
+
+
+def _gemv_stream(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, multiplier: float = 1.0,
+                 cap: float = 0.0) -> torch.Tensor:
+    fn = _function("gemv_stream", "omnia_gemv_stream",
+                   [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p])
+    _check(fn(_ptr(a), _ptr(weight), _ptr(out), a.shape[0], weight.shape[0], a.shape[1], epilogue, multiplier, cap,
+              _ptr(error_word(a.device)), _stream()), "gemv_stream")
+    return out
+
+
+def _small_product(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, multiplier: float = 1.0,
+                   cap: float = 0.0) -> torch.Tensor:
+    """A product of few rows, on whichever of the two weight-streaming kernels takes it."""
+    if USE_GEMV_STREAM and a.shape[0] <= 16 and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
+        return _gemv_stream(a, weight, out, epilogue, multiplier, cap)
+    return _gemm_skinny(a, weight, out, epilogue, multiplier, cap)
+
+
 def _gemm_skinny(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, multiplier: float = 1.0,
                  cap: float = 0.0) -> torch.Tensor:
     fn = _function("gemm_skinny", "omnia_gemm_skinny",
@@ -368,7 +390,7 @@ def linear(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     on the 32-bit path it runs without any reduced-precision mode."""
     if _skinny(a, weight):
         out = torch.empty(a.shape[0], weight.shape[0], dtype=a.dtype, device=a.device)
-        return _gemm_skinny(a, weight, out, 0)
+        return _small_product(a, weight, out, 0)
     if _tensor_core(a, weight):
         out = torch.empty(a.shape[0], weight.shape[0], dtype=a.dtype, device=a.device)
         return _gemm_tcgen05(a, weight, out, 0)
@@ -379,7 +401,7 @@ def linear_swiglu(a: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
     """silu(a @ gate^T) * (a @ up^T) with gate_up = [gate rows | up rows] -> [rows, inner]."""
     if _skinny(a, gate_up):
         out = torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device)
-        return _gemm_skinny(a, gate_up, out, 1)
+        return _small_product(a, gate_up, out, 1)
     if _tensor_core(a, gate_up):
         out = torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device)
         return _gemm_tcgen05(a, gate_up, out, 1)
@@ -390,7 +412,7 @@ def linear_softcap(a: torch.Tensor, weight: torch.Tensor, multiplier: float, cap
     """float32 logits = cap * tanh((a @ weight^T) * multiplier / cap) -> [rows, n]."""
     if _skinny(a, weight):
         out = torch.empty(a.shape[0], weight.shape[0], dtype=torch.float32, device=a.device)
-        return _gemm_skinny(a, weight, out, 2, multiplier, cap or 0.0)
+        return _small_product(a, weight, out, 2, multiplier, cap or 0.0)
     if _tensor_core(a, weight):
         out = torch.empty(a.shape[0], weight.shape[0], dtype=torch.float32, device=a.device)
         return _gemm_tcgen05(a, weight, out, 2, multiplier, cap or 0.0)

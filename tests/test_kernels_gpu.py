@@ -212,16 +212,21 @@ def test_linear_is_true_float32(ops):
 
 @pytest.mark.parametrize("m", [1, 3, 8, 11, 16, 23, 32, 47, 64])
 @pytest.mark.parametrize("n,k", [(2048, 2048), (6144, 2048), (2048, 6144), (1000, 96), (777, 160), (50, 8), (5000, 520)])
-def test_skinny_products(ops, m, n, k):
-    """The weight-streaming kernel and its fused epilogues against float64 products of the
-    same bfloat16 operands, at sizes with ragged edges in every dimension."""
+@pytest.mark.parametrize("kernel", ["registers", "ring"])
+def test_skinny_products(ops, kernel, m, n, k):
+    """The two weight-streaming kernels (fed through registers, up to 64 rows; fed through a
+    shared-memory ring, up to 16 rows) and their fused epilogues against float64 products of
+    the same bfloat16 operands, at sizes with ragged edges in every dimension."""
+    if kernel == "ring" and m > 16:
+        pytest.skip("the ring-fed kernel takes up to 16 rows")
     a = rand(m, k, dtype=torch.bfloat16, seed=m)
     w = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=n + k)
     exact = a.double() @ w.double().t()
     z = exact.float().bfloat16().double()
 
     def skinny(epilogue, out, multiplier=1.0, cap=0.0):  # the kernel itself, whatever `linear` would pick
-        return ops._gemm_skinny(a, w, out, epilogue, multiplier, cap)
+        product = ops._gemv_stream if kernel == "ring" else ops._gemm_skinny
+        return product(a, w, out, epilogue, multiplier, cap)
 
     close(skinny(0, torch.empty(m, n, dtype=torch.bfloat16, device="cuda")), exact, torch.bfloat16)
     close(skinny(2, torch.empty(m, n, dtype=torch.float32, device="cuda"), 3.0, 7.0), 7.0 * torch.tanh(z * 3.0 / 7.0),
@@ -232,6 +237,7 @@ def test_skinny_products(ops, m, n, k):
         close(skinny(1, torch.empty(m, n // 2, dtype=torch.bfloat16, device="cuda")), g * torch.sigmoid(g) * u,
               torch.bfloat16)
     close(ops.linear(a, w), exact, torch.bfloat16)
+    ops.raise_on_error(a.device)
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 128, 128), (129, 1000, 96), (200, 300, 136), (300, 778, 160),
