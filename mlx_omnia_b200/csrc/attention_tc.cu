@@ -10,8 +10,8 @@
 //             the visible keys in tiles of 64, double-buffered with cp.async; it writes
 //             the final output (optionally times sigmoid(gate)).
 //   decode:   one warp per block owns the g rows of one single-token request and one
-//             fixed chunk of DECODE_CHUNK keys (chunks are aligned to absolute key
-//             positions, so the partition never depends on the batch); it writes an
+//             chunk of keys (chunks are aligned to absolute key positions; the caller picks
+//             their size from the number of requests and the longest one); it writes an
 //             unnormalised partial (max, sum, accumulator) to scratch memory and takes a
 //             ticket; the block that draws the last ticket of a (request, head group)
 //             merges that group's chunks in ascending order (nobody waits for anybody).

@@ -68,6 +68,11 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // earlier kernel wrote (reading weights before that is fine and hides their latency), and calls
 // pdl_launch_dependents() to let the kernel after it start its own preamble early. In a kernel
 // launched the ordinary way both calls do nothing.
+// Rule of this package: a kernel calls pdl_launch_dependents() only after its own pdl_wait(), so
+// at most two kernels ever overlap. (Were it called first, a third kernel's block could start on
+// an SM where the first kernel still runs, and later find in L1, through a cached load, lines
+// that the first kernel's blocks fetched from memory which has since been freed, handed out
+// again and rewritten. That was seen as a rare wrong token.)
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

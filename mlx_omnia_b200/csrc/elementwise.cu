@@ -9,8 +9,8 @@ template <typename T>
 __global__ void embed_rmsnorm_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                      float* __restrict__ x, int hidden, int vocab, float eps,
                                      int normed, int* err) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   __shared__ float scratch[33];
   const int t = blockIdx.x;
   int id = ids[t];
@@ -44,8 +44,8 @@ extern "C" int omnia_embed_rmsnorm(const int* ids, const void* table, float* x, 
 template <typename T>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                T* __restrict__ h, int hidden, float eps) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   __shared__ float scratch[33];
   const float* row = x + (size_t)blockIdx.x * hidden;
   T* out = h + (size_t)blockIdx.x * hidden;
@@ -79,8 +79,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
                                    const float* __restrict__ wb, float eps_b, int norm_branch,
                                    const float* __restrict__ wo, float eps_o, int norm_out,
                                    T* __restrict__ h, int hidden) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   extern __shared__ float row[];
   __shared__ float scratch[33];
   float* xr = x + (size_t)blockIdx.x * hidden;
@@ -152,8 +152,8 @@ __global__ void add_rmsnorm_reg_kernel(float* __restrict__ x, const T* __restric
                                        const float* __restrict__ wb, float eps_b, int norm_branch,
                                        const float* __restrict__ wo, float eps_o, int norm_out,
                                        T* __restrict__ h, int hidden) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   __shared__ float scratch[33];
   float* xr = x + (size_t)blockIdx.x * hidden;
   const T* br = branch + (size_t)blockIdx.x * hidden;
@@ -250,8 +250,8 @@ __global__ void qk_norm_rope_store_kernel(const T* __restrict__ proj, int row_st
                                           const long long* __restrict__ slot_mapping,
                                           T* __restrict__ q_out, T* __restrict__ pages,
                                           int page_size, long long num_slots, int* err) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hs = blockIdx.y * (blockDim.x >> 5) + warp;
@@ -316,8 +316,8 @@ qk_norm_rope_store_vec_kernel(const T* __restrict__ proj, int row_stride, int q_
                               const int* __restrict__ positions, const long long* __restrict__ slot_mapping,
                               T* __restrict__ q_out, T* __restrict__ pages, int page_size, long long num_slots,
                               int* err) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   constexpr int d = 32 * VW;
   __shared__ float cos_s[d / 2], sin_s[d / 2];
   const int t = blockIdx.x;  // one block per token: the token's angles are computed once for all heads
@@ -405,8 +405,8 @@ extern "C" int omnia_qk_norm_rope_store(const void* proj, int row_stride, int q_
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, long long total,
                               int inner) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += stride) {
@@ -433,8 +433,8 @@ extern "C" int omnia_swiglu(const void* gu, void* act, int rows, int inner, int 
 template <typename T>
 __global__ void softcap_kernel(const T* __restrict__ z, float* __restrict__ out, long long total,
                                float multiplier, float cap) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += stride) {
@@ -457,8 +457,8 @@ extern "C" int omnia_softcap(const void* z, float* out, long long total, float m
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restrict__ rows,
                                    T* __restrict__ out, int width) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   const T* s = src + (size_t)rows[blockIdx.x] * width;
   T* o = out + (size_t)blockIdx.x * width;
   for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = s[i];

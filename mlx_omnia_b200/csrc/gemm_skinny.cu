@@ -108,7 +108,7 @@ gemm_skinny_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, void*
         for (int h = 0; h < 2; ++h) wv[u][r][h] = live && wlive[r][h] ? load_stream(wrow[r][h] + kk) : zero;
 #pragma unroll
       for (int j = 0; j < NT; ++j)
-        av[u][j] = live && alive[j] ? __ldg(reinterpret_cast<const uint4*>(arow[j] + kk)) : zero;
+        av[u][j] = live && alive[j] ? __ldcg(reinterpret_cast<const uint4*>(arow[j] + kk)) : zero;
     }
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u)

@@ -53,6 +53,10 @@ constexpr int STAGE_BOXES = 2 * BOXES_ACROSS;              // upper eight rows, 
 constexpr int STAGE_BYTES = STAGE_BOXES * BOX_BYTES;
 static_assert(STAGE_COLS % BOX_COLS == 0 && STAGE_BOXES <= 32, "a stage is at most 32 boxes");
 constexpr int STAGES = GEMV_STAGES;
+#ifndef GEMV_GROUP_TILES
+#define GEMV_GROUP_TILES 4
+#endif
+constexpr int GROUP_TILES = GEMV_GROUP_TILES;              // tiles that share one fetch of the activations
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
 
 enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_SOFTCAP = 2 };
@@ -126,8 +130,8 @@ gemv_stream_kernel(const bf16* __restrict__ a, const __grid_constant__ CUtensorM
                    int m, int n, int k, int inner, int tiles, float multiplier, float cap, int* __restrict__ err) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* ring = smem;
-  float (*partial)[CONSUMER_WARPS][TILE_ROWS][NT * 8 + 1] =
-      reinterpret_cast<float (*)[CONSUMER_WARPS][TILE_ROWS][NT * 8 + 1]>(smem + STAGES * STAGE_BYTES);
+  float (*partial)[GROUP_TILES * TILE_ROWS][NT * 8 + 1] =
+      reinterpret_cast<float (*)[GROUP_TILES * TILE_ROWS][NT * 8 + 1]>(smem + STAGES * STAGE_BYTES);
   __shared__ __align__(8) unsigned long long bars[2 * STAGES];
   __shared__ int abort_word;
   volatile int* abort_flag = &abort_word;
@@ -143,42 +147,53 @@ gemv_stream_kernel(const bf16* __restrict__ a, const __grid_constant__ CUtensorM
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  pdl_launch_dependents();  // the next kernel's blocks may start as soon as an SM has room for them
 
-  // This block's tiles: a contiguous run, sizes differing by at most one between blocks.
+  // This block's tiles: a contiguous run, sizes differing by at most one between blocks. They
+  // are worked on in groups of GROUP_TILES: for every 1024 columns, the stages of all tiles of
+  // the group follow one another, so a warp fetches its activations of those columns once per
+  // group (from L2, which is far: fetched per stage they bounded a stage's time from below).
   const int base = tiles / gridDim.x, extra = tiles % gridDim.x;
   const int my_tiles = base + ((int)blockIdx.x < extra ? 1 : 0);
   const int tile0 = blockIdx.x * base + min((int)blockIdx.x, extra);
   const int chunks = (k + STAGE_COLS - 1) / STAGE_COLS;
-  const int units = my_tiles * chunks;
 
   if (warp == CONSUMER_WARPS) {
     // ---- producer: needs nothing from the kernel before, so it does not wait for it ----
-    int issued = 0;
-    for (int u = 0; u < units; ++u) {
-      const int s = u % STAGES;
-      bool ok = true;
-      if (lane == 0) ok = mbar_wait(empty0 + 8 * s, ((u / STAGES) & 1) ^ 1, abort_flag);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-      const int tile = tile0 + u / chunks, c = u % chunks;
-      // Lane i copies box i of the stage: half i / BOXES_ACROSS (rows g, then rows g + 8) and
-      // 256 columns. A box that starts outside the matrix is not copied (its rows and columns
-      // are masked by the consumers); one that straddles an edge is filled with zeros there.
-      const int half = lane / BOXES_ACROSS, x = c * STAGE_COLS + (lane % BOXES_ACROSS) * BOX_COLS;
-      const int y = lane < STAGE_BOXES ? tile_row<EPI>(tile, half * 8, n, inner) : -1;
-      const bool copies = y >= 0 && x < k;
-      const unsigned live = __ballot_sync(0xffffffffu, copies);
-      if (lane == 0) mbar_expect_tx(full0 + 8 * s, (uint32_t)__popc(live) * BOX_BYTES);
-      __syncwarp();
-      if (copies) tma_load_2d(smem_u32(ring + s * STAGE_BYTES + lane * BOX_BYTES), &map_w, full0 + 8 * s, x, y);
-      issued = u + 1;
-    }
-    if (issued < units && lane == 0) {
-      // Giving up: the copies already issued must land before the block's shared memory is released.
-      for (int u = max(0, issued - STAGES); u < issued; ++u)
-        for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(full0 + 8 * (u % STAGES), (u / STAGES) & 1); ++i) {
+    int s = 0, phase = 1, in_flight = 0;
+    bool ok = true;
+    for (int first = 0; first < my_tiles && ok; first += GROUP_TILES) {
+      const int count = min(GROUP_TILES, my_tiles - first);
+      for (int c = 0; c < chunks && ok; ++c)
+        for (int i = 0; i < count; ++i) {
+          if (lane == 0) ok = mbar_wait(empty0 + 8 * s, phase, abort_flag);
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
+          const int tile = tile0 + first + i;
+          // Lane i copies box i of the stage: half i / BOXES_ACROSS (rows g, then rows g + 8) and
+          // 256 columns. A box that starts outside the matrix is not copied (its rows and columns
+          // are masked by the consumers); one that straddles an edge is filled with zeros there.
+          const int half = lane / BOXES_ACROSS, x = c * STAGE_COLS + (lane % BOXES_ACROSS) * BOX_COLS;
+          const int y = lane < STAGE_BOXES ? tile_row<EPI>(tile, half * 8, n, inner) : -1;
+          const bool copies = y >= 0 && x < k;
+          const unsigned live = __ballot_sync(0xffffffffu, copies);
+          if (lane == 0) mbar_expect_tx(full0 + 8 * s, (uint32_t)__popc(live) * BOX_BYTES);
+          __syncwarp();
+          if (copies) tma_load_2d(smem_u32(ring + s * STAGE_BYTES + lane * BOX_BYTES), &map_w, full0 + 8 * s, x, y);
+          in_flight = min(in_flight + 1, STAGES);
+          if (++s == STAGES) s = 0, phase ^= 1;
         }
+    }
+    pdl_launch_dependents();
+    if (!ok && lane == 0) {
+      // Giving up: the copies already issued must land before the block's shared memory is released.
+      // The last `in_flight` stages before s were filled in phase `phase ^ 1` of their barriers, or
+      // in phase `phase` when the ring wrapped between them and s.
+      for (int back = 1; back <= in_flight; ++back) {
+        const int st = (s - back + STAGES) % STAGES;
+        const int filled_phase = (st < s ? phase : phase ^ 1) ^ 1;
+        for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(full0 + 8 * st, filled_phase); ++i) {
+        }
+      }
     }
   } else {
     // ---- consumers ----
@@ -191,82 +206,93 @@ gemv_stream_kernel(const bf16* __restrict__ a, const __grid_constant__ CUtensorM
       arow[j] = a + (size_t)(alive[j] ? 8 * j + g : 0) * k;
     }
     const uint4 zero = make_uint4(0, 0, 0, 0);
-    float acc[NT][4];
-#pragma unroll
-    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    const int in_stage = warp * WARP_COLS + 8 * t;  // this thread's first column within a stage
     pdl_wait();  // the activations come from the kernel before
-    // The activations of a stage are fetched while the stage before it is worked on: they come
-    // from L2 (the rings leave little room for an L1 cache), which is far.
+    // From here on every earlier kernel is complete, so the next kernel's blocks may move in beside
+    // this one (never more than two kernels overlap). Activations are read through L2 (__ldcg): a
+    // block that started while an earlier kernel was still running must not find lines in L1 that
+    // that kernel's blocks on the same SM left there.
+    pdl_launch_dependents();
     auto fetch = [&](int c, uint4 (&dst)[KBLOCKS][NT]) {
-      const int col0 = c * STAGE_COLS + warp * WARP_COLS + 8 * t;
+      const int col0 = c * STAGE_COLS + in_stage;
 #pragma unroll
       for (int h = 0; h < KBLOCKS; ++h)
 #pragma unroll
         for (int j = 0; j < NT; ++j)
-          dst[h][j] = alive[j] && col0 + 32 * h < k ? __ldg(reinterpret_cast<const uint4*>(arow[j] + col0 + 32 * h)) : zero;
+          dst[h][j] = alive[j] && col0 + 32 * h < k ? __ldcg(reinterpret_cast<const uint4*>(arow[j] + col0 + 32 * h)) : zero;
     };
     uint4 av[KBLOCKS][NT], av_next[KBLOCKS][NT];
-    if (units > 0) fetch(0, av_next);
+    if (my_tiles > 0) fetch(0, av_next);
     bool ok = true;
-    int s = 0, phase = 0, c = 0, tile_local = 0;
-    for (int u = 0; u < units && ok; ++u) {
-      const int tile = tile0 + tile_local;
-      const int col0 = c * STAGE_COLS + warp * WARP_COLS + 8 * t;  // this thread's first column of the stage
+    int s = 0, phase = 0;
+    for (int first = 0; first < my_tiles && ok; first += GROUP_TILES) {
+      const int count = min(GROUP_TILES, my_tiles - first);
+      float acc[GROUP_TILES][NT][4];
 #pragma unroll
-      for (int h = 0; h < KBLOCKS; ++h)
+      for (int i = 0; i < GROUP_TILES; ++i)
 #pragma unroll
-        for (int j = 0; j < NT; ++j) av[h][j] = av_next[h][j];
-      if (u + 1 < units) fetch(c + 1 == chunks ? 0 : c + 1, av_next);
-      const bool lo_live = tile_row<EPI>(tile, g, n, inner) >= 0, hi_live = tile_row<EPI>(tile, g + 8, n, inner) >= 0;
-      ok = mbar_wait(full0 + 8 * s, phase, abort_flag);
-      if (!ok) break;
-      // Column warp * WARP_COLS + 32 h + 8 t of the stage: box (that / 256), then 512-byte rows.
-      const int in_stage = warp * WARP_COLS + 8 * t;
-      const uint32_t stage = smem_u32(ring + s * STAGE_BYTES) + (in_stage / BOX_COLS) * BOX_BYTES +
-                             g * (BOX_COLS * 2) + (in_stage % BOX_COLS) * 2;
+        for (int j = 0; j < NT; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+      for (int c = 0; c < chunks && ok; ++c) {
 #pragma unroll
-      for (int h = 0; h < KBLOCKS; ++h) {
-        const bool live = col0 + 32 * h < k;
-        static_assert(BOX_COLS % WARP_COLS == 0, "a warp's columns of a stage lie in one box");
-        const uint32_t at = stage + 64 * h;
-        uint4 lo = lds128(at), hi = lds128(at + BOXES_ACROSS * BOX_BYTES);
-        if (!live || !lo_live) lo = zero;
-        if (!live || !hi_live) hi = zero;
+        for (int h = 0; h < KBLOCKS; ++h)
 #pragma unroll
-        for (int j = 0; j < NT; ++j) {
-          mma_bf16(acc[j], lo.x, hi.x, lo.y, hi.y, av[h][j].x, av[h][j].y);
-          mma_bf16(acc[j], lo.z, hi.z, lo.w, hi.w, av[h][j].z, av[h][j].w);
+          for (int j = 0; j < NT; ++j) av[h][j] = av_next[h][j];
+        // The next columns' activations (the first columns again when another group follows).
+        if (c + 1 < chunks || first + GROUP_TILES < my_tiles) fetch(c + 1 < chunks ? c + 1 : 0, av_next);
+        const int col0 = c * STAGE_COLS + in_stage;
+#pragma unroll
+        for (int i = 0; i < GROUP_TILES; ++i) {
+          if (i >= count) break;
+          const int tile = tile0 + first + i;
+          const bool lo_live = tile_row<EPI>(tile, g, n, inner) >= 0, hi_live = tile_row<EPI>(tile, g + 8, n, inner) >= 0;
+          ok = mbar_wait(full0 + 8 * s, phase, abort_flag);
+          if (!ok) break;
+          // Column in_stage + 32 h of the stage: box (that / 256), then rows of 512 bytes.
+          static_assert(BOX_COLS % WARP_COLS == 0, "a warp's columns of a stage lie in one box");
+          const uint32_t stage = smem_u32(ring + s * STAGE_BYTES) + (in_stage / BOX_COLS) * BOX_BYTES +
+                                 g * (BOX_COLS * 2) + (in_stage % BOX_COLS) * 2;
+#pragma unroll
+          for (int h = 0; h < KBLOCKS; ++h) {
+            const bool live = col0 + 32 * h < k;
+            uint4 lo = lds128(stage + 64 * h), hi = lds128(stage + 64 * h + BOXES_ACROSS * BOX_BYTES);
+            if (!live || !lo_live) lo = zero;
+            if (!live || !hi_live) hi = zero;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+              mma_bf16(acc[i][j], lo.x, hi.x, lo.y, hi.y, av[h][j].x, av[h][j].y);
+              mma_bf16(acc[i][j], lo.z, hi.z, lo.w, hi.w, av[h][j].z, av[h][j].w);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(empty0 + 8 * s);  // the stage may be filled again
+          if (++s == STAGES) s = 0, phase ^= 1;
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty0 + 8 * s);  // the stage may be filled again
-      if (++s == STAGES) s = 0, phase ^= 1;
-      if (++c != chunks) continue;
-      c = 0;
+      if (!ok) break;
 
-      // The tile is complete: add the warps' partial sums in a fixed order and store.
-      const int buf = tile_local & 1;
-      ++tile_local;
+      // The group is complete: add the warps' partial sums in a fixed order and store.
 #pragma unroll
-      for (int j = 0; j < NT; ++j) {
-        partial[buf][warp][g][j * 8 + 2 * t] = acc[j][0];
-        partial[buf][warp][g][j * 8 + 2 * t + 1] = acc[j][1];
-        partial[buf][warp][g + 8][j * 8 + 2 * t] = acc[j][2];
-        partial[buf][warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
-        acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-      }
+      for (int i = 0; i < GROUP_TILES; ++i)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          partial[warp][i * TILE_ROWS + g][j * 8 + 2 * t] = acc[i][j][0];
+          partial[warp][i * TILE_ROWS + g][j * 8 + 2 * t + 1] = acc[i][j][1];
+          partial[warp][i * TILE_ROWS + g + 8][j * 8 + 2 * t] = acc[i][j][2];
+          partial[warp][i * TILE_ROWS + g + 8][j * 8 + 2 * t + 1] = acc[i][j][3];
+        }
       consumer_sync();
       const int out_rows = EPI == EPI_SWIGLU ? 8 : TILE_ROWS;
-      for (int idx = threadIdx.x; idx < out_rows * NT * 8; idx += CONSUMERS) {
-        const int token = idx / out_rows, r = idx % out_rows;
+      for (int idx = threadIdx.x; idx < count * out_rows * NT * 8; idx += CONSUMERS) {
+        const int token = idx / (count * out_rows), rest = idx % (count * out_rows);
+        const int i = rest / out_rows, r = rest % out_rows, tile = tile0 + first + i;
         if (token >= m) continue;
         float v = 0.f;
 #pragma unroll
-        for (int s2 = 0; s2 < CONSUMER_WARPS; ++s2) v += partial[buf][s2][r][token];
+        for (int s2 = 0; s2 < CONSUMER_WARPS; ++s2) v += partial[s2][i * TILE_ROWS + r][token];
         if (EPI == EPI_SWIGLU) {
           float up = 0.f;
 #pragma unroll
-          for (int s2 = 0; s2 < CONSUMER_WARPS; ++s2) up += partial[buf][s2][8 + r][token];
+          for (int s2 = 0; s2 < CONSUMER_WARPS; ++s2) up += partial[s2][i * TILE_ROWS + 8 + r][token];
           const int col = tile * 8 + r;
           if (col >= inner) continue;
           // The two halves are rounded to bfloat16 first, as a separate product would round them.
@@ -284,6 +310,7 @@ gemv_stream_kernel(const bf16* __restrict__ a, const __grid_constant__ CUtensorM
           }
         }
       }
+      consumer_sync();  // the partial sums are read before the next group overwrites them
     }
   }
   __syncthreads();
@@ -323,7 +350,8 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int k) {
 template <int NT, int EPI>
 int launch(const bf16* a, const bf16* w, void* out, int m, int n, int k, int inner, float multiplier, float cap,
            int* err, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)STAGES * STAGE_BYTES + sizeof(float) * 2 * CONSUMER_WARPS * TILE_ROWS * (NT * 8 + 1);
+  constexpr size_t smem =
+      (size_t)STAGES * STAGE_BYTES + sizeof(float) * CONSUMER_WARPS * GROUP_TILES * TILE_ROWS * (NT * 8 + 1);
   static int sms = 0;
   if (sms == 0) {
     int device = 0;

@@ -83,8 +83,8 @@ sample_kernel(float* __restrict__ logits, long long stride, int vocab,
               const float* __restrict__ penalty, const int* __restrict__ history, int history_len,
               const long long* __restrict__ seeds, const long long* __restrict__ draws,
               int* __restrict__ out) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   __shared__ float fscratch[33];
   __shared__ ArgMax ascratch[33];
   const int row = blockIdx.x;
@@ -189,8 +189,8 @@ sample_kernel(float* __restrict__ logits, long long stride, int vocab,
 __global__ void __launch_bounds__(256)
 argmax_partial_kernel(const float* __restrict__ logits, long long stride, int vocab,
                       float* __restrict__ part_v, int* __restrict__ part_i) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   __shared__ ArgMax ascratch[33];
   const int row = blockIdx.y, part = blockIdx.x;
   const float* z = logits + (size_t)row * stride;
@@ -208,8 +208,8 @@ argmax_partial_kernel(const float* __restrict__ logits, long long stride, int vo
 __global__ void __launch_bounds__(32)
 argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
                     int* __restrict__ out) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.x, lane = threadIdx.x;
   ArgMax a{part_v[row * ARGMAX_PARTS + lane], part_i[row * ARGMAX_PARTS + lane]};
 #pragma unroll

@@ -96,17 +96,8 @@ class DecodeGraphs:
             slots = view(f"slots{g}").view(torch.int64)
             groups[g] = (view(f"table{g}").view(batch, width), slots)
         context_bound = width * runner.cache.page_size
-        max_chunks = -(-context_bound // ops.DECODE_CHUNK)
-        heads = max((getattr(b.mixer, "heads", 1) * getattr(b.mixer, "head_dim", 1) for b in runner.model.blocks),
-                    default=1)
-        workspace = {
-            "attention_part_o": torch.empty(batch * heads * max_chunks, dtype=torch.float32, device=device),
-            "attention_part_ml": torch.empty(batch * max((getattr(b.mixer, "heads", 1) for b in runner.model.blocks),
-                                                         default=1) * max_chunks * 2,
-                                             dtype=torch.float32, device=device),
-            "attention_tickets": torch.zeros(batch * max((getattr(b.mixer, "kv_heads", 1) for b in runner.model.blocks),
-                                                         default=1), dtype=torch.int32, device=device),
-        }
+        # Kernels that need scratch memory keep it here, for as long as the graph lives.
+        workspace = {"private": True}
         step = StepContext(
             num_tokens=batch, num_seqs=batch, token_ids=view("token_ids"), positions=view("positions"),
             cu_seqlens=view("cu_seqlens"), seq_lens=view("seq_lens"), state_slots=view("state_slots"),

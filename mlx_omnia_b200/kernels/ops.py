@@ -170,6 +170,39 @@ def scratch(device: torch.device, name: str, numel: int, dtype: torch.dtype = to
     return held
 
 
+def _step_buffers(step: StepContext, device: torch.device, wanted: dict) -> list[torch.Tensor]:
+    """Scratch buffers `name -> (elements, dtype, zeroed)` for a kernel of this step. A step whose
+    workspace says `private` (a step captured into a graph, which must keep its buffers for as
+    long as the graph lives) gets buffers of its own, kept in the workspace; any other step
+    shares the process-wide ones. A zeroed buffer is zero when created and its users leave it zero."""
+    held = step.workspace if isinstance(step.workspace, dict) else None
+    private = held is not None and held.get("private", False)
+    buffers = []
+    for name, (numel, dtype, zeroed) in wanted.items():
+        if private:
+            t = held.get(name)
+            if t is None or t.numel() < numel or t.dtype != dtype:
+                t = held[name] = (torch.zeros if zeroed else torch.empty)(max(numel, 1), dtype=dtype, device=device)
+        else:
+            t = scratch(device, name, numel, dtype, zeroed)
+        buffers.append(t)
+    return buffers
+
+
+def decode_chunk(pairs: int, longest: int) -> int:
+    """Keys per block of the decode attention kernel for `pairs` (request, key/value head)
+    pairs whose longest request holds `longest` positions. Every block is one warp that keeps
+    one tile of keys in flight, so a block's time grows with its chunk while the number of
+    blocks decides how many run at once; about 512 blocks (a little over half of what the GPU
+    holds at a time) measured best from batch 1 to 64 at 4096 positions, within chunks of 128
+    to 1024 keys. Both arguments are rounded up to powers of two first, so a step takes the same
+    chunk whether it runs on its own or from a captured graph (which is sized for such bounds)."""
+    def pow2(n: int) -> int:
+        return 1 << max(n - 1, 0).bit_length()
+    wanted = pow2(max(longest, 1)) * pow2(max(pairs, 1)) // 512
+    return min(max(-(-wanted // 64) * 64, DECODE_CHUNK), 1024)
+
+
 def tiled_attention_supported(dtype: torch.dtype, nq: int, nkv: int, d: int) -> bool:
     """The tensor-core kernels take bfloat16, head sizes in steps of 8 up to 256 and up to
     16 query heads per key/value head; everything else runs on the generic kernel."""
@@ -245,20 +278,18 @@ def paged_attention(q: torch.Tensor, kv: KVView, step: StepContext, scale: float
     single, longest = (None, step.max_seq_len) if step.decode_only else _single_token_requests(step, q.device)
     if step.decode_only or single is not None:
         count = step.num_seqs if step.decode_only else single.shape[0]
-        max_chunks = -(-longest // DECODE_CHUNK)
-        held = step.workspace if isinstance(step.workspace, dict) else {}
-        part_o, part_ml = held.get("attention_part_o"), held.get("attention_part_ml")
-        tickets = held.get("attention_tickets")
-        if part_o is None or part_o.numel() < count * nq * max_chunks * d:
-            part_o = scratch(q.device, "attention_part_o", count * nq * max_chunks * d)
-            part_ml = scratch(q.device, "attention_part_ml", count * nq * max_chunks * 2)
-            tickets = scratch(q.device, "attention_tickets", count * nkv, torch.int32, zeroed=True)
+        chunk = decode_chunk(count * nkv, longest)
+        max_chunks = -(-longest // chunk)
+        part_o, part_ml, tickets = _step_buffers(step, q.device, {
+            "attention_part_o": (count * nq * max_chunks * d, torch.float32, False),
+            "attention_part_ml": (count * nq * max_chunks * 2, torch.float32, False),
+            "attention_tickets": (count * nkv, torch.int32, True)})
         fn = _function("attention_tc", "omnia_attention_decode_tc",
                        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                         c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_float, c_void_p, c_void_p], defines)
         _check(fn(_ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.seq_lens),
-                  _ptr(single), count, _ptr(part_o), _ptr(part_ml), _ptr(tickets), DECODE_CHUNK, max_chunks, gate_ptr,
+                  _ptr(single), count, _ptr(part_o), _ptr(part_ml), _ptr(tickets), chunk, max_chunks, gate_ptr,
                   gate_stride, _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size, kv.window or 0, scale, err,
                   _stream()), "attention_decode")
         if step.decode_only or all(n == 1 for n in step.q_lens):

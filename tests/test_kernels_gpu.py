@@ -148,14 +148,16 @@ def test_paged_attention(ops, dtype, nq, nkv, d, page, window):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,d,page,window", [(4, 2, 16, 4, None), (8, 1, 24, 8, 16), (6, 3, 128, 16, None),
                                                    (6, 3, 128, 16, 200), (5, 5, 40, 3, 130), (16, 8, 64, 16, None),
-                                                   (10, 2, 96, 16, None)])
+                                                   (10, 2, 96, 16, None), (16, 1, 128, 32, 300), (4, 4, 64, 64, 70),
+                                                   (8, 4, 128, 16, 64)])
 def test_paged_attention_decode_only(ops, dtype, nq, nkv, d, page, window):
     """Every request brings one token: the split-key kernel, at lengths around its chunk
-    and tile edges."""
+    and tile edges. Unused places of the cache hold NaN."""
     seq_lens = [1, 31, 32, 33, 127, 128, 129, 257, 700]
     q_lens = [1] * len(seq_lens)
     step = step_of(q_lens, seq_lens)
     pages, table = make_kv(seq_lens, nkv, d, page, dtype, 1 + sum(-(-n // page) for n in seq_lens), seed=6)
+    pages.fill_(float("nan"))
     for s, n in enumerate(seq_lens):
         for first in range(0, n, page):
             p = int(table[s, first // page])
