@@ -45,7 +45,8 @@ constexpr int TOKENS_PER_BLOCK = BM / GROUP;
 #ifndef DECODE_PIPELINE
 #define DECODE_PIPELINE 2
 #endif
-constexpr int DECODE_BN = DECODE_TILE_KEYS;   // keys per decode tile (16, 32 or 64)
+constexpr int DECODE_BN = DECODE_TILE_KEYS;   // keys per decode tile
+static_assert(DECODE_TILE_KEYS == 32, "a decode tile is loaded by one warp, lane l looking up key l: 32 keys");
 constexpr int DECODE_STAGES = DECODE_PIPELINE;
 constexpr int DECODE_TABLE = 64;         // block-table entries a decode block stages in shared memory
 constexpr float LOG2E = 1.4426950408889634f;
