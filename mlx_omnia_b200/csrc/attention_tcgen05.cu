@@ -164,7 +164,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // Debug build only: nanosecond stamps of block (0, 0), read back with omnia_attention_timing.
 __device__ unsigned long long g_timing[8192];
 __device__ __forceinline__ void stamp(int slot) {
-  if (blockIdx.x == 0 && blockIdx.y == 0 && slot < 8192) {
+  if (blockIdx.x == 0 && slot < 8192) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     g_timing[slot] = t;
@@ -177,8 +177,8 @@ __device__ __forceinline__ void stamp(int slot) {
 
 }  // namespace
 
-// grid (blocks of the work list, nkv); 192 threads. work[b] = (request, first token of the block
-// among the request's tokens of this step).
+// grid (blocks of the work list); 192 threads. work[b] = (request, first token of the block among
+// the request's tokens of this step, key/value head); the caller lists the longest blocks first.
 __global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                                  const int* __restrict__ block_table, const int* __restrict__ cu_seqlens,
@@ -203,8 +203,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   volatile uint32_t* group_mask = reinterpret_cast<volatile uint32_t*>(tmem_holder + 2);  // [KV_STAGES]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = work[2 * blockIdx.x], tok0 = work[2 * blockIdx.x + 1];
-  const int kvh = blockIdx.y;
+  const int seq = work[3 * blockIdx.x], tok0 = work[3 * blockIdx.x + 1], kvh = work[3 * blockIdx.x + 2];
   const int q_begin = cu_seqlens[seq], q_len = cu_seqlens[seq + 1] - q_begin;
   const int pos0 = seq_lens[seq] - q_len + tok0;      // position of the block's first token
   const int tokens = min(TOKENS, q_len - tok0);
@@ -598,7 +597,7 @@ extern "C" int omnia_attention_prefill_tcgen05(const void* q, int tokens, const 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  attention_prefill_tcgen05_kernel<<<dim3(blocks, nkv), THREADS, smem, stream>>>(
+  attention_prefill_tcgen05_kernel<<<blocks, THREADS, smem, stream>>>(
       map_q, map_kv, block_table, cu_seqlens, seq_lens, work, (const bf16*)gate, gate_stride, (bf16*)out,
       max_pages, num_pages, nq, nkv, page_size, window, scale, err);
   return OMNIA_LAUNCH_RESULT();
