@@ -73,32 +73,63 @@ class StepRunner:
             raise
         q_lens = [len(e.tokens) for e in entries]
         total = sum(q_lens)
-        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
-        positions = np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(starts, q_lens)])
-        cu = np.zeros(len(entries) + 1, dtype=np.int32)
+        n = len(entries)
+        cu = np.zeros(n + 1, dtype=np.int32)
         cu[1:] = np.cumsum(q_lens)
-        seq_lens = np.asarray([e.request.tokens for e in entries], dtype=np.int32)
         rows = [int(cu[i]) + w for i, e in enumerate(entries) for w in e.want]
-        groups = {}
+        widths = [max(max(len(e.request.tables[g]) for e in entries), 1) for g in range(len(cache.groups))]
+        # Everything goes to the device in one copy: the fields are laid out in one pinned buffer of
+        # int32 words (the int64 slot mappings first, so they start on 8 bytes).
+        fields: dict[str, tuple[int, int]] = {}
+        offset = 0
+        for name, length in ([(f"slots{g}", 2 * total) for g in range(len(cache.groups))] +
+                             [("token_ids", total), ("positions", total), ("cu_seqlens", n + 1), ("seq_lens", n),
+                              ("state_slots", n), ("fresh", n), ("logit_rows", len(rows))] +
+                             [(f"table{g}", n * widths[g]) for g in range(len(cache.groups))]):
+            fields[name] = (offset, length)
+            offset += length
+        pinned = self.runtime.device.type == "cuda"
+        host_tensor = torch.empty(max(offset, 1), dtype=torch.int32, pin_memory=pinned)
+        host = host_tensor.numpy()
+
+        def field_of(name: str) -> np.ndarray:
+            at, length = fields[name]
+            return host[at: at + length]
+
+        positions = field_of("positions")
+        for i, (e, s) in enumerate(zip(entries, starts)):
+            field_of("token_ids")[cu[i]: cu[i + 1]] = e.tokens
+            positions[cu[i]: cu[i + 1]] = np.arange(s, s + q_lens[i], dtype=np.int32)
+        field_of("cu_seqlens")[:] = cu
+        seq_lens = field_of("seq_lens")
+        seq_lens[:] = [e.request.tokens for e in entries]
+        field_of("state_slots")[:] = [e.request.slot for e in entries]
+        field_of("fresh")[:] = [int(e.request.fresh) for e in entries]
+        field_of("logit_rows")[:] = rows
         for g in range(len(cache.groups)):
-            width = max(len(e.request.tables[g]) for e in entries)
-            table = np.full((len(entries), max(width, 1)), -1, dtype=np.int32)
-            slots = np.empty(total, dtype=np.int64)
+            table = field_of(f"table{g}").reshape(n, widths[g])
+            table.fill(-1)
+            slots = field_of(f"slots{g}").view(np.int64)
             for i, e in enumerate(entries):
                 t = e.request.table_array(g)
                 table[i, : len(t)] = t
                 pos = positions[cu[i]: cu[i + 1]].astype(np.int64)
                 slots[cu[i]: cu[i + 1]] = t[pos // page].astype(np.int64) * page + pos % page
-            groups[g] = (self._device(table), self._device(slots))
+        device = host_tensor.to(self.runtime.device, non_blocking=True) if pinned else host_tensor
+
+        def on_device(name: str) -> torch.Tensor:
+            at, length = fields[name]
+            return device[at: at + length]
+
+        groups = {g: (on_device(f"table{g}").view(n, widths[g]), on_device(f"slots{g}").view(torch.int64))
+                  for g in range(len(cache.groups))}
         return StepContext(
-            num_tokens=total, num_seqs=len(entries),
-            token_ids=self._device(token_ids), positions=self._device(positions), cu_seqlens=self._device(cu),
-            seq_lens=self._device(seq_lens),
-            state_slots=self._device(np.asarray([e.request.slot for e in entries], dtype=np.int32)),
-            fresh=self._device(np.asarray([int(e.request.fresh) for e in entries], dtype=np.int32)),
-            logit_rows=self._device(np.asarray(rows, dtype=np.int32)),
+            num_tokens=total, num_seqs=n,
+            token_ids=on_device("token_ids"), positions=on_device("positions"), cu_seqlens=on_device("cu_seqlens"),
+            seq_lens=on_device("seq_lens"), state_slots=on_device("state_slots"), fresh=on_device("fresh"),
+            logit_rows=on_device("logit_rows"),
             q_lens=q_lens, seq_lens_host=[int(s) for s in seq_lens], max_q_len=max(q_lens),
-            max_seq_len=int(seq_lens.max()), decode_only=all(n == 1 for n in q_lens), groups=groups)
+            max_seq_len=int(seq_lens.max()), decode_only=all(q == 1 for q in q_lens), groups=groups)
 
     def _shrink(self, request: RequestCache, count: int) -> None:
         """Undo a `grow` of `count` tokens that no kernel has used."""

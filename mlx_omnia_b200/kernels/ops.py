@@ -48,7 +48,9 @@ def _ptr(t: torch.Tensor | None) -> int | None:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The current stream's handle (the raw query: `torch.cuda.current_stream()` builds a Python
+    object and costs 3 us, which a step of 230 launches pays 230 times)."""
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
 
 
 launches = 0
