@@ -191,18 +191,29 @@ def _step_buffers(step: StepContext, device: torch.device, wanted: dict) -> list
     return buffers
 
 
-def decode_chunk(pairs: int, longest: int) -> int:
+def decode_chunk(pairs: int, longest: int, sms: int = 148) -> int:
     """Keys per block of the decode attention kernel for `pairs` (request, key/value head)
     pairs whose longest request holds `longest` positions. Every block is one warp that keeps
-    one tile of keys in flight, so a block's time grows with its chunk while the number of
-    blocks decides how many run at once; about 512 blocks (a little over half of what the GPU
-    holds at a time) measured best from batch 1 to 64 at 4096 positions, within chunks of 128
-    to 1024 keys. Both arguments are rounded up to powers of two first, so a step takes the same
-    chunk whether it runs on its own or from a captured graph (which is sized for such bounds)."""
+    one 32-key tile (16 KB at head size 128) in flight. A block's time is a fixed part (about
+    four tiles' worth: its start, its partial result, the merge) plus its tiles; a tile takes
+    the memory's latency (1.2 us) or, when the blocks on the GPU (about six per SM) together ask
+    for more than the memory delivers in that time, its share of the bandwidth. The chunk (a
+    multiple of 64 keys, 128 to 1024) is the one with the smallest rounds x (4 + tiles) x tile
+    time, the larger on a tie (fewer partials to merge). Measured at 4,096 positions this picks
+    within 5 % of the best chunk from batch 1 to 64. Both arguments are rounded up to powers of
+    two first, so a step takes the same chunk whether it runs on its own or from a captured
+    graph (which is sized for such bounds)."""
     def pow2(n: int) -> int:
         return 1 << max(n - 1, 0).bit_length()
-    wanted = pow2(max(longest, 1)) * pow2(max(pairs, 1)) // 512
-    return min(max(-(-wanted // 64) * 64, DECODE_CHUNK), 1024)
+    pairs, longest, resident = pow2(max(pairs, 1)), pow2(max(longest, 1)), 6 * sms
+    best, best_cost = DECODE_CHUNK, None
+    for chunk in range(DECODE_CHUNK, 1024 + 1, 64):
+        blocks = pairs * -(-longest // chunk)
+        tile_us = max(1.2, min(blocks, resident) * 16384 / 6.65e6)
+        cost = -(-blocks // resident) * (4 + chunk // 32) * tile_us
+        if best_cost is None or cost <= best_cost * (1 + 1e-9):
+            best, best_cost = chunk, cost
+    return best
 
 
 def tiled_attention_supported(dtype: torch.dtype, nq: int, nkv: int, d: int) -> bool:
