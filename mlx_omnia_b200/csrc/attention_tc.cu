@@ -394,12 +394,16 @@ __device__ __forceinline__ void combine_head(const float* __restrict__ part_o,
 }
 
 // ---------------------------------------------------------------------------------------
-// Decode: grid (chunks, nkv, requests); 32 threads. Request s is the single-token
-// request seq_ids[s] (or s when seq_ids is null). Partials:
+// Decode: grid (chunks, nkv, requests); WARPS x 32 threads. Request s is the single-token
+// request seq_ids[s] (or s when seq_ids is null). With one warp the block walks its chunk's tiles
+// through a two-stage ring; with four (small batches, where there are too few chunks to fill the
+// GPU otherwise) the warps take the tiles in turn, one stage each, and their states are merged
+// through shared memory before the block's partial is written. Partials:
 //   part_o  [requests, nq, max_chunks, D] float32 (unnormalised), part_ml [requests, nq, max_chunks, 2]
 //   tickets [requests, nkv] int32, zero before the first launch; the merging block zeroes its
 //   ticket again, so the array is ready for the next launch.
-__global__ void __launch_bounds__(32)
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages,
                         const int* __restrict__ block_table, const int* __restrict__ cu_seqlens,
                         const int* __restrict__ seq_lens, const int* __restrict__ seq_ids,
@@ -409,9 +413,10 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
                         int num_pages, int nq, int nkv, int page_size, int window, float scale,
                         int* err) {
   pdl_wait();
+  constexpr int STAGES = WARPS == 1 ? DECODE_STAGES : 1;  // stages of each warp's own ring
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* kv = reinterpret_cast<bf16*>(smem_raw);  // DECODE_STAGES x (K [32][ROW], V [32][ROW])
-  const int lane = threadIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  bf16* kv = reinterpret_cast<bf16*>(smem_raw) + warp * STAGES * 2 * DECODE_BN * ROW;  // STAGES x (K [32][ROW], V [32][ROW])
   const int seq = seq_ids ? seq_ids[blockIdx.z] : blockIdx.z;
   const int kvh = blockIdx.y, chunk = blockIdx.x;
   const int pos = seq_lens[seq] - 1;
@@ -427,21 +432,23 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
   const int* table_row = block_table + (size_t)seq * max_pages;
   const bool staged = page_hi - page_lo < DECODE_TABLE;
   if (staged)
-    for (int i = lane; i <= page_hi - page_lo; i += 32) table_s[i] = table_row[page_lo + i];
+    for (int i = threadIdx.x; i <= page_hi - page_lo; i += WARPS * 32) table_s[i] = table_row[page_lo + i];
   CacheRef cache{pages, staged ? table_s : table_row, staged ? page_lo : 0, num_pages, nkv, kvh, page_size};
-  __syncwarp();
+  if (WARPS == 1) __syncwarp(); else __syncthreads();
 
-  for (int stage = 0; stage < DECODE_STAGES; ++stage)
+  for (int stage = 0; stage < STAGES; ++stage)
     zero_padding(kv + stage * 2 * DECODE_BN * ROW, 2 * DECODE_BN, lane, 32);
 
-  const int tile0 = lo / DECODE_BN, tiles = hi / DECODE_BN - tile0 + 1;
+  // This warp's tiles: every WARPS-th of the chunk's, starting with its own number.
+  const int tile0 = lo / DECODE_BN + warp, all_tiles = hi / DECODE_BN - lo / DECODE_BN + 1;
+  const int tiles = (all_tiles - warp + WARPS - 1) / WARPS;
   // A tile's loads: lane l looks up the row of key l once; then the warp copies the tile in
   // flat order (consecutive lanes take consecutive 16-byte chunks of a row, so every
   // request covers whole 128-byte lines), fetching each row's address by shuffle.
   auto load_tile = [&](int tile, int stage) {
     bf16* kt = kv + stage * 2 * DECODE_BN * ROW;
     bf16* vt = kt + DECODE_BN * ROW;
-    const int p = (tile0 + tile) * DECODE_BN + lane;
+    const int p = (tile0 + tile * WARPS) * DECODE_BN + lane;
     const bool visible = p >= lo && p <= hi;
     const bf16* mine = visible ? cache_row(cache, p, 0, err) : nullptr;
     const size_t v_offset = (size_t)nkv * page_size * D;
@@ -456,7 +463,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     }
   };
 #pragma unroll
-  for (int s = 0; s < DECODE_STAGES - 1; ++s) {
+  for (int s = 0; s < STAGES - 1; ++s) {
     if (s < tiles) load_tile(s, s);
     cp_async_commit();
   }
@@ -495,13 +502,13 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
   const float sl2 = scale * LOG2E;
 
   for (int tile = 0; tile < tiles; ++tile) {
-    const int ahead = tile + DECODE_STAGES - 1;
-    if (ahead < tiles) load_tile(ahead, ahead % DECODE_STAGES);
+    const int ahead = tile + STAGES - 1;
+    if (ahead < tiles) load_tile(ahead, ahead % STAGES);
     cp_async_commit();
-    cp_async_wait<DECODE_STAGES - 1>();
+    cp_async_wait<STAGES - 1>();
     __syncwarp();
-    const bf16* kt = kv + (tile % DECODE_STAGES) * 2 * DECODE_BN * ROW;
-    attend_tile<DECODE_BN>(qf, kt, kt + DECODE_BN * ROW, (tile0 + tile) * DECODE_BN, row_lo, row_hi,
+    const bf16* kt = kv + (tile % STAGES) * 2 * DECODE_BN * ROW;
+    attend_tile<DECODE_BN>(qf, kt, kt + DECODE_BN * ROW, (tile0 + tile * WARPS) * DECODE_BN, row_lo, row_hi,
                            sl2, m, l, o);
     __syncwarp();
   }
@@ -514,12 +521,16 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
   }
   const int t = lane & 3;
+  // The rows' states go to the block's partial: straight from the registers of a lone warp, or
+  // (several warps) through shared memory, where warp 0 merges them, every lane its own dims.
+  float* merge = reinterpret_cast<float*>(smem_raw);  // [WARPS][GROUP][D + 2]: accumulator, max (log2 units), sum
+  if (WARPS > 1) __syncthreads();                     // every warp is done with its tiles
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int row = (lane >> 2) + 8 * r;
     if (row >= GROUP) continue;
     const size_t slot = (((size_t)blockIdx.z * nq + kvh * GROUP + row) * max_chunks + chunk);
-    float* dst = part_o + slot * D;
+    float* dst = WARPS == 1 ? part_o + slot * D : merge + ((size_t)warp * GROUP + row) * (D + 2);
 #pragma unroll
     for (int j = 0; j < NT_O; ++j) {
       const int dim = 8 * j + 2 * t;
@@ -527,8 +538,41 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
       *reinterpret_cast<float2*>(dst + dim) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
     }
     if (t == 0) {
-      part_ml[slot * 2] = m[r] * sl2;  // the maximum in the exponent's units (log2)
-      part_ml[slot * 2 + 1] = l[r];
+      const float top = m[r] == -INFINITY ? -INFINITY : m[r] * sl2;  // the maximum in the exponent's units (log2)
+      if (WARPS == 1) {
+        part_ml[slot * 2] = top;
+        part_ml[slot * 2 + 1] = l[r];
+      } else {
+        dst[D] = top;
+        dst[D + 1] = l[r];
+      }
+    }
+  }
+  if (WARPS > 1) {
+    __syncthreads();
+    if (warp != 0) return;
+    for (int row = 0; row < GROUP; ++row) {
+      const size_t slot = (((size_t)blockIdx.z * nq + kvh * GROUP + row) * max_chunks + chunk);
+      float top = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) top = fmaxf(top, merge[((size_t)w * GROUP + row) * (D + 2) + D]);
+      float weight[WARPS], sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        const float* src = merge + ((size_t)w * GROUP + row) * (D + 2);
+        weight[w] = src[D] == -INFINITY ? 0.f : exp2f(src[D] - top);
+        sum += src[D + 1] * weight[w];
+      }
+      for (int dim = lane; dim < D; dim += 32) {
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) acc += merge[((size_t)w * GROUP + row) * (D + 2) + dim] * weight[w];
+        part_o[slot * D + dim] = acc;
+      }
+      if (lane == 0) {
+        part_ml[slot * 2] = top;
+        part_ml[slot * 2 + 1] = sum;
+      }
     }
   }
   // Whoever finishes last merges: publish the partial, take a ticket, and if it is the last
@@ -589,22 +633,33 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
                                          float* part_ml, int* tickets, int chunk_keys,
                                          int max_chunks, const void* gate, int gate_stride,
                                          void* out, int max_pages, int num_pages, int nq, int nkv,
-                                         int page_size, int window, float scale, int* err,
+                                         int page_size, int window, float scale, int warps, int* err,
                                          cudaStream_t stream) {
   if (requests == 0) return 0;
-  if (nq != nkv * GROUP || chunk_keys % DECODE_BN != 0 || max_chunks < 1) return (int)cudaErrorInvalidValue;
-  const size_t smem = (size_t)(DECODE_STAGES * 2 * DECODE_BN) * ROW * sizeof(bf16);
+  if (nq != nkv * GROUP || chunk_keys % DECODE_BN != 0 || max_chunks < 1 || (warps != 1 && warps != 4))
+    return (int)cudaErrorInvalidValue;
+  // One warp: a two-stage ring. Four warps: one stage each (a warp has few tiles), and the merge area fits in it.
+  const size_t smem = (size_t)((warps == 1 ? DECODE_STAGES : 4) * 2 * DECODE_BN) * ROW * sizeof(bf16);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)((size_t)(DECODE_STAGES * 2 * DECODE_BN) * ROW * sizeof(bf16)));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)((size_t)(4 * 2 * DECODE_BN) * ROW * sizeof(bf16)));
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  launch_pdl(attention_decode_kernel, dim3(max_chunks, nkv, requests), 32, smem, stream, 
-      (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
-      tickets, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
-      num_pages, nq, nkv, page_size, window, scale, err);
+  if (warps == 1)
+    launch_pdl(attention_decode_kernel<1>, dim3(max_chunks, nkv, requests), 32, smem, stream,
+        (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
+        tickets, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
+        num_pages, nq, nkv, page_size, window, scale, err);
+  else
+    launch_pdl(attention_decode_kernel<4>, dim3(max_chunks, nkv, requests), 128, smem, stream,
+        (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
+        tickets, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
+        num_pages, nq, nkv, page_size, window, scale, err);
   return OMNIA_LAUNCH_RESULT();
 }
 
@@ -665,7 +720,7 @@ extern "C" int omnia_attention_decode_tc_static(const void* q, const void* pages
       return (int)e;
     }
     const size_t smem = (size_t)(DECODE_STAGES * 2 * DECODE_BN) * ROW * sizeof(bf16);
-    e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaFuncSetAttribute(attention_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
       snprintf(static_error, sizeof static_error, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
       return (int)e;
@@ -682,7 +737,7 @@ extern "C" int omnia_attention_decode_tc_static(const void* q, const void* pages
     return (int)e;
   }
   const size_t smem = (size_t)(DECODE_STAGES * 2 * DECODE_BN) * ROW * sizeof(bf16);
-  launch_pdl(attention_decode_kernel, dim3(max_chunks, nkv, requests), 32, smem, stream, 
+  launch_pdl(attention_decode_kernel<1>, dim3(max_chunks, nkv, requests), 32, smem, stream,
       (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
       ticket_area, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
       num_pages, nq, nkv, page_size, window, scale, err);

@@ -191,29 +191,37 @@ def _step_buffers(step: StepContext, device: torch.device, wanted: dict) -> list
     return buffers
 
 
-def decode_chunk(pairs: int, longest: int, sms: int = 148) -> int:
-    """Keys per block of the decode attention kernel for `pairs` (request, key/value head)
-    pairs whose longest request holds `longest` positions. Every block is one warp that keeps
-    one 32-key tile (16 KB at head size 128) in flight. A block's time is a fixed part (about
-    four tiles' worth: its start, its partial result, the merge) plus its tiles; a tile takes
-    the memory's latency (1.2 us) or, when the blocks on the GPU (about six per SM) together ask
-    for more than the memory delivers in that time, its share of the bandwidth. The chunk (a
-    multiple of 64 keys, 128 to 1024) is the one with the smallest rounds x (4 + tiles) x tile
-    time, the larger on a tie (fewer partials to merge). Measured at 4,096 positions this picks
-    within 5 % of the best chunk from batch 1 to 64. Both arguments are rounded up to powers of
-    two first, so a step takes the same chunk whether it runs on its own or from a captured
-    graph (which is sized for such bounds)."""
+def decode_plan(pairs: int, longest: int, sms: int = 148) -> tuple[int, int]:
+    """(keys per block, warps per block) of the decode attention kernel for `pairs` (request,
+    key/value head) pairs whose longest request holds `longest` positions. A warp keeps one
+    32-key tile (16 KB at head size 128) in flight. A block's time is a fixed part (about four
+    tiles' worth: its start, its partial result, the merge) plus its tiles (with four warps: a
+    quarter of them each); a tile takes the memory's latency (1.2 us) or, when the warps on the
+    GPU together ask for more than the memory delivers in that time, its share of the bandwidth;
+    the GPU holds about six one-warp blocks or three four-warp blocks per SM at a time. The plan
+    is the chunk (a multiple of 64 keys, 128 to 1024) and warp count with the smallest rounds x
+    (fixed + tiles per warp) x tile time; on a tie the larger chunk (fewer partials to merge)
+    and the single warp. Measured at 4,096 positions this picks within 5 % of the best chunk
+    from batch 1 to 64. Both arguments are rounded up to powers of two first, so a step takes
+    the same plan whether it runs on its own or from a captured graph (which is sized for such
+    bounds)."""
     def pow2(n: int) -> int:
         return 1 << max(n - 1, 0).bit_length()
-    pairs, longest, resident = pow2(max(pairs, 1)), pow2(max(longest, 1)), 6 * sms
-    best, best_cost = DECODE_CHUNK, None
-    for chunk in range(DECODE_CHUNK, 1024 + 1, 64):
-        blocks = pairs * -(-longest // chunk)
-        tile_us = max(1.2, min(blocks, resident) * 16384 / 6.65e6)
-        cost = -(-blocks // resident) * (4 + chunk // 32) * tile_us
-        if best_cost is None or cost <= best_cost * (1 + 1e-9):
-            best, best_cost = chunk, cost
+    pairs, longest = pow2(max(pairs, 1)), pow2(max(longest, 1))
+    best, best_cost = (DECODE_CHUNK, 1), None
+    for warps, per_sm, fixed in ((4, 3, 4.5), (1, 6, 4.0)):
+        for chunk in range(DECODE_CHUNK, 1024 + 1, 64):
+            blocks = pairs * -(-longest // chunk)
+            tile_us = max(1.2, min(blocks, per_sm * sms) * warps * 16384 / 6.65e6)
+            cost = -(-blocks // (per_sm * sms)) * (fixed + -(-(chunk // 32) // warps)) * tile_us
+            if best_cost is None or cost <= best_cost * (1 + 1e-9):
+                best, best_cost = (chunk, warps), cost
     return best
+
+
+def decode_chunk(pairs: int, longest: int, sms: int = 148) -> int:
+    """The chunk of `decode_plan`."""
+    return decode_plan(pairs, longest, sms)[0]
 
 
 def tiled_attention_supported(dtype: torch.dtype, nq: int, nkv: int, d: int) -> bool:
@@ -321,7 +329,7 @@ def paged_attention(q: torch.Tensor, kv: KVView, step: StepContext, scale: float
     single, longest = (None, step.max_seq_len) if step.decode_only else _single_token_requests(step, q.device)
     if step.decode_only or single is not None:
         count = step.num_seqs if step.decode_only else single.shape[0]
-        chunk = decode_chunk(count * nkv, longest)
+        chunk, warps = decode_plan(count * nkv, longest)
         max_chunks = -(-longest // chunk)
         part_o, part_ml, tickets = _step_buffers(step, q.device, {
             "attention_part_o": (count * nq * max_chunks * d, torch.float32, False),
@@ -330,11 +338,11 @@ def paged_attention(q: torch.Tensor, kv: KVView, step: StepContext, scale: float
         fn = _function("attention_tc", "omnia_attention_decode_tc",
                        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                         c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                        c_float, c_void_p, c_void_p], defines)
+                        c_float, c_int, c_void_p, c_void_p], defines)
         _check(fn(_ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.seq_lens),
                   _ptr(single), count, _ptr(part_o), _ptr(part_ml), _ptr(tickets), chunk, max_chunks, gate_ptr,
-                  gate_stride, _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size, kv.window or 0, scale, err,
-                  _stream()), "attention_decode")
+                  gate_stride, _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size, kv.window or 0, scale, warps,
+                  err, _stream()), "attention_decode")
         if step.decode_only or all(n == 1 for n in step.q_lens):
             return out
     if USE_TCGEN05 and tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):

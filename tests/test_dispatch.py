@@ -13,8 +13,10 @@ def test_decode_chunk_is_a_tile_multiple_within_bounds_and_the_same_for_a_bucket
             assert chunk == ops.decode_chunk(up(pairs), up(longest))
 
 
-def test_decode_chunk_grows_with_the_work():
-    """Few pairs: short chunks, so that enough blocks run; many pairs: long chunks."""
-    assert ops.decode_chunk(8, 4096) == 128
-    assert ops.decode_chunk(64, 4096) > ops.decode_chunk(8, 4096)
-    assert ops.decode_chunk(512, 8192) == 1024
+def test_decode_plan_grows_with_the_work():
+    """Few pairs: short chunks and four warps a block, so that enough warps run; many pairs:
+    long chunks walked by one warp."""
+    chunk, warps = ops.decode_plan(8, 4096)
+    assert chunk <= 256 and warps == 4
+    assert ops.decode_plan(64, 4096) == (512, 1)
+    assert ops.decode_plan(512, 8192) == (1024, 1)
