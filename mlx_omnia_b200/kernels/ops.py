@@ -449,12 +449,40 @@ def _tensor_core(a: torch.Tensor, weight: torch.Tensor) -> bool:
             and weight.is_contiguous())
 
 
+USE_TCGEN05_PAIR = True
+"""Large bfloat16 products run two SMs to a tile (gemm_tcgen05_pair.cu); off, one SM to a tile."""
+
+
+def _pair_pays(rows: int, n: int, k: int, epilogue: int, sms: int = 148) -> bool:
+    """Whether the two-SM kernel is the faster one: it brings in a third less per step of k, but
+    has half as many (twice as large) tiles to hand out and a longer start. Measured at the
+    benchmark's shapes it wins by 4 to 13 % where a pair of SMs gets at least 64 steps of k of
+    a 256 x 256 tile to do (2,048 rows: q/gate/k/v, gate/up, down; 8,192 rows: all), and loses
+    where the work is less (2,048 x 2,048 x 2,048; 512 rows)."""
+    if rows < 256:
+        return False
+    tile_cols = 128 if epilogue == 1 else 256
+    tiles = -(-rows // 256) * -(-(n // 2 if epilogue == 1 else n) // tile_cols)
+    return tiles * -(-k // 64) >= 64 * (sms // 2)
+
+
 def _gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, multiplier: float = 1.0,
                   cap: float = 0.0) -> torch.Tensor:
+    if USE_TCGEN05_PAIR and _pair_pays(a.shape[0], weight.shape[0], a.shape[1], epilogue):
+        return _gemm_tcgen05_pair(a, weight, out, epilogue, multiplier, cap)
     fn = _function("gemm_tcgen05", "omnia_gemm_tcgen05",
                    [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p])
     _check(fn(_ptr(a), _ptr(weight), _ptr(out), a.shape[0], weight.shape[0], a.shape[1], epilogue, multiplier, cap,
               _ptr(error_word(a.device)), _stream()), "gemm_tcgen05")
+    return out
+
+
+def _gemm_tcgen05_pair(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, multiplier: float = 1.0,
+                       cap: float = 0.0) -> torch.Tensor:
+    fn = _function("gemm_tcgen05_pair", "omnia_gemm_tcgen05_pair",
+                   [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p])
+    _check(fn(_ptr(a), _ptr(weight), _ptr(out), a.shape[0], weight.shape[0], a.shape[1], epilogue, multiplier, cap,
+              _ptr(error_word(a.device)), _stream()), "gemm_tcgen05_pair")
     return out
 
 

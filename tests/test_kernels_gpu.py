@@ -243,19 +243,33 @@ def test_skinny_products(ops, kernel, m, n, k):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 128, 128), (129, 1000, 96), (200, 300, 136), (300, 778, 160),
-                                   (2048, 2048, 2048), (1000, 6144, 2048), (260, 2048, 6144), (130, 12288, 512)])
-def test_tcgen05_products(ops, m, n, k):
-    """The tcgen05/TMA kernel and its epilogues against float64 products of the same bfloat16
-    operands: whole tiles, ragged edges in m, n and k, wide and narrow tilings."""
+                                   (2048, 2048, 2048), (1000, 6144, 2048), (260, 2048, 6144), (130, 12288, 512),
+                                   (2048, 6144, 2048), (777, 1000, 520)])
+@pytest.mark.parametrize("kernel", ["one_sm", "two_sm", "dispatch"])
+def test_tcgen05_products(ops, kernel, m, n, k):
+    """The tcgen05/TMA kernels (one SM to a tile; two SMs to a tile, cta_group::2) and their
+    epilogues against float64 products of the same bfloat16 operands: whole tiles, ragged edges
+    in m, n and k, wide and narrow tilings; and whichever of them `linear` picks."""
     a = rand(m, k, dtype=torch.bfloat16, seed=m)
     w = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=n + k)
     exact = a.double() @ w.double().t()
-    close(ops.linear(a, w), exact, torch.bfloat16)
-    ops.raise_on_error(a.device)
     z = exact.float().bfloat16().double()
-    close(ops.linear_softcap(a, w, 3.0, 7.0), 7.0 * torch.tanh(z * 3.0 / 7.0), torch.bfloat16)
     g, u = z[:, : n // 2], z[:, n // 2:]
-    close(ops.linear_swiglu(a, w), g * torch.sigmoid(g) * u, torch.bfloat16)
+    if kernel == "dispatch":
+        plain, capped, gated = ops.linear(a, w), ops.linear_softcap(a, w, 3.0, 7.0), ops.linear_swiglu(a, w)
+    else:
+        product = ops._gemm_tcgen05_pair if kernel == "two_sm" else ops._gemm_tcgen05
+        if kernel == "one_sm":
+            ops.USE_TCGEN05_PAIR = False
+        try:
+            plain = product(a, w, torch.empty(m, n, dtype=torch.bfloat16, device="cuda"), 0)
+            capped = product(a, w, torch.empty(m, n, dtype=torch.float32, device="cuda"), 2, 3.0, 7.0)
+            gated = product(a, w, torch.empty(m, n // 2, dtype=torch.bfloat16, device="cuda"), 1)
+        finally:
+            ops.USE_TCGEN05_PAIR = True
+    close(plain, exact, torch.bfloat16)
+    close(capped, 7.0 * torch.tanh(z * 3.0 / 7.0), torch.bfloat16)
+    close(gated, g * torch.sigmoid(g) * u, torch.bfloat16)
     ops.raise_on_error(a.device)
 
 
