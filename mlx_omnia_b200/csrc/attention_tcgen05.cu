@@ -10,9 +10,9 @@
 //               sum in float32, exp2, P rounded to bfloat16 into shared memory (128-byte swizzle)
 //   O += P V    tcgen05.mma (M 128, N head size) over the tile's keys, accumulator in tensor memory;
 //               when a row's maximum grows its accumulator is rescaled in tensor memory first
-// Warp 0 feeds the ring of K/V stages with TMA, one box of 16 keys x 64 dims per page group (the
-// block table is read there; page sizes must be multiples of 16); warp 1 issues the MMAs; warps
-// 2-5 are the softmax and the epilogue (normalise, optional sigmoid gate, store). The score
+// Warps 0 (K) and 6 (V) feed the rings of K and V stages with TMA, one box of 16 keys x 64 dims per page
+// group (the block table is read there; page sizes must be multiples of 16); warp 1 issues the
+// MMAs; warps 2-5 are the softmax and the epilogue (normalise, optional sigmoid gate, store). The score
 // accumulator is double-buffered, so S of the next tile is computed while this tile's softmax runs.
 // Key groups whose page is not loaded (beyond the request, or given back behind a window) are
 // masked in S and skipped in P V, so stale shared memory never reaches the arithmetic.
@@ -45,7 +45,8 @@ constexpr int BM = 128, BN = 64;      // rows per block, keys per tile
 constexpr int TOKENS = BM / GROUP;         // tokens per block
 constexpr int ROWS = TOKENS * GROUP;       // rows in use (<= 128)
 constexpr int KV_STAGES = 2;
-constexpr int THREADS = 192;
+constexpr int RING_PRODUCERS = 1;  // warps that share the issue of a ring's boxes (1 or 2; two measured no faster)
+constexpr int THREADS = 192 + 32 + (RING_PRODUCERS - 1) * 64;  // warps: 0 K producer, 1 MMA issuer, 2-5 softmax, 6 V producer (7 K, 8 V)
 constexpr uint32_t HALF_BYTES = 128 * 128;           // 128 rows of 128 bytes
 constexpr uint32_t Q_BYTES = DH * HALF_BYTES;
 constexpr uint32_t P_BYTES = HALF_BYTES;             // 128 rows x 64 keys
@@ -200,7 +201,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   // bars: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11 p_full | 12 o_done
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
-  volatile uint32_t* group_mask = reinterpret_cast<volatile uint32_t*>(tmem_holder + 2);  // [KV_STAGES]
+  volatile uint32_t* group_mask = reinterpret_cast<volatile uint32_t*>(tmem_holder + 2);  // [KV_STAGES][RING_PRODUCERS]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq = work[3 * blockIdx.x], tok0 = work[3 * blockIdx.x + 1], kvh = work[3 * blockIdx.x + 2];
@@ -218,9 +219,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(k_full0 + 8 * s, 1);
+      mbar_init(k_full0 + 8 * s, RING_PRODUCERS);  // one arrival (with its byte count) per producer warp of the ring
       mbar_init(k_empty0 + 8 * s, 1);
-      mbar_init(v_full0 + 8 * s, 1);
+      mbar_init(v_full0 + 8 * s, RING_PRODUCERS);
       mbar_init(v_empty0 + 8 * s, 1);
       mbar_init(s_full0 + 8 * s, 1);
     }
@@ -239,21 +240,24 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 0) {
-    // ---- producer: Q once, then K/V tiles through the ring -------------------------------------
-    if (lane == 0) {
+  if (warp == 0 || warp >= 6) {
+    // ---- producers: warp 0 loads Q once, then the K tiles; warp 6 the V tiles (with two producers
+    // a ring, warps 7 and 8 take the second half of a tile's 16-key groups). Issuing a box keeps a
+    // warp busy for about 70 ns: one warp for both rings spent more than half a tile's time on it
+    // (2,048 tokens: 61 us with one warp, 52 us with one per ring). ------------------------------
+    const int which = (warp == 0 || warp == 7) ? 0 : 1;  // 0 keys, 1 values
+    const int part = warp >= 7 ? 1 : 0;                  // which share of the tile's groups
+    constexpr int PART_GROUPS = BN / 16 / RING_PRODUCERS;
+    if (warp == 0 && lane == 0) {
       mbar_expect_tx(q_full, DH * ROWS * 128);
       for (int h = 0; h < DH; ++h)
         tma_load_3d(smem_u32(q_s) + h * HALF_BYTES, &map_q, q_full, h * 64, kvh * GROUP, q_begin + tok0);
     }
-    // K and V tiles go through rings of their own, in the order the tensor core wants them:
-    // K0, K1, V0, K2, V1, ... A K slot is free again as soon as its scores are computed, so
-    // the next keys are on their way long before the MMA warp asks for them.
     // Lane = group * DH + half: each of the tile's boxes (16 keys x 64 dims) is issued by its own lane.
     const int* table = block_table + (size_t)seq * max_pages;
     if (lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kv) : "memory");
-    const int g = lane / DH, h = lane % DH;
-    const bool active = lane < (BN / 16) * DH;
+    const int g = part * PART_GROUPS + lane / DH, h = lane % DH;
+    const bool active = lane < PART_GROUPS * DH;
     // The page of this lane's group in tile t (-2: the group lies outside what the block reads).
     // Page numbers are fetched a whole tile before they are used, so the table's latency is hidden.
     auto lookup = [&](int t) {
@@ -261,8 +265,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       return (active && t < n_tiles && pos <= last && pos + 15 >= first) ? table[pos / page_size] : -2;
     };
     bool ok = true;
-    int k_issued = 0, v_issued = 0;
-    auto load_tile = [&](int j, int which, int page) {  // which: 0 keys, 1 values
+    int issued = 0;
+    auto load_tile = [&](int j, int page) {
       const int s = j % KV_STAGES;
       const uint32_t full = (which ? v_full0 : k_full0) + 8 * s, empty = (which ? v_empty0 : k_empty0) + 8 * s;
       if (lane == 0) ok = mbar_wait(empty, ((j / KV_STAGES) & 1) ^ 1, abort_flag);
@@ -281,8 +285,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         if (which) {
           uint32_t mask = 0;
 #pragma unroll
-          for (int x = 0; x < BN / 16; ++x) mask |= ((loaded >> (x * DH)) & 1u) << x;
-          group_mask[s] = mask;
+          for (int x = 0; x < PART_GROUPS; ++x) mask |= ((loaded >> (x * DH)) & 1u) << (part * PART_GROUPS + x);
+          group_mask[RING_PRODUCERS * s + part] = mask;
         }
         mbar_expect_tx(full, __popc(loaded) * GROUP_BYTES);
       }
@@ -293,28 +297,22 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         tma_load_2d(dst, &map_kv, full, h * 64, y);
       }
       if (lane == 0) STAMP(0, j, which * 2 + 1);
-      if (which) v_issued = j + 1; else k_issued = j + 1;
+      issued = j + 1;
     };
-    // K and V tiles go through rings of their own, in the order the tensor core wants them:
-    // K0, K1, V0, K2, V1, ... A K slot is free again as soon as its scores are computed, so
-    // the next keys are on their way long before the MMA warp asks for them.
-    int page_cur = lookup(0), page_next = lookup(1);
-    load_tile(0, 0, page_cur);
+    // A K slot is free again as soon as its scores are computed, a V slot when its P V is: each
+    // ring runs up to two tiles ahead of the tensor core.
+    int page_cur = lookup(0);
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int page_after = lookup(j + 2);
-      if (j + 1 < n_tiles) load_tile(j + 1, 0, page_next);
-      if (ok) load_tile(j, 1, page_cur);
+      const int page_next = lookup(j + 1);
+      load_tile(j, page_cur);
       page_cur = page_next;
-      page_next = page_after;
     }
     if (lane == 0 && *abort_flag) {
-      for (int j = max(0, k_issued - KV_STAGES); j < k_issued; ++j)
-        for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(k_full0 + 8 * (j % KV_STAGES), (j / KV_STAGES) & 1); ++i) {
+      const uint32_t full0 = which ? v_full0 : k_full0;
+      for (int j = max(0, issued - KV_STAGES); j < issued; ++j)
+        for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(full0 + 8 * (j % KV_STAGES), (j / KV_STAGES) & 1); ++i) {
         }
-      for (int j = max(0, v_issued - KV_STAGES); j < v_issued; ++j)
-        for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(v_full0 + 8 * (j % KV_STAGES), (j / KV_STAGES) & 1); ++i) {
-        }
-      for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(q_full, 0); ++i) {
+      for (uint32_t i = 0; warp == 0 && i < WAIT_LIMIT && !mbar_try(q_full, 0); ++i) {
       }
     }
   } else if (warp == 1) {
@@ -356,7 +354,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         STAMP(1, j, 1);
-        const uint32_t mask = group_mask[s];
+        const uint32_t mask = group_mask[RING_PRODUCERS * s] | group_mask[RING_PRODUCERS * s + RING_PRODUCERS - 1];
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           if (!(mask & (1u << kk))) continue;  // keys never loaded: their P is zero, their V is stale
