@@ -45,8 +45,7 @@ constexpr int BM = 128, BN = 64;      // rows per block, keys per tile
 constexpr int TOKENS = BM / GROUP;         // tokens per block
 constexpr int ROWS = TOKENS * GROUP;       // rows in use (<= 128)
 constexpr int KV_STAGES = 2;
-constexpr int RING_PRODUCERS = 1;  // warps that share the issue of a ring's boxes (1 or 2; two measured no faster)
-constexpr int THREADS = 192 + 32 + (RING_PRODUCERS - 1) * 64;  // warps: 0 K producer, 1 MMA issuer, 2-5 softmax, 6 V producer (7 K, 8 V)
+constexpr int THREADS = 224;  // warps: 0 K producer, 1 MMA issuer, 2-5 softmax, 6 V producer
 constexpr uint32_t HALF_BYTES = 128 * 128;           // 128 rows of 128 bytes
 constexpr uint32_t Q_BYTES = DH * HALF_BYTES;
 constexpr uint32_t P_BYTES = HALF_BYTES;             // 128 rows x 64 keys
@@ -201,7 +200,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   // bars: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11 p_full | 12 o_done
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
-  volatile uint32_t* group_mask = reinterpret_cast<volatile uint32_t*>(tmem_holder + 2);  // [KV_STAGES][RING_PRODUCERS]
+  volatile uint32_t* group_mask = reinterpret_cast<volatile uint32_t*>(tmem_holder + 2);  // [KV_STAGES]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq = work[3 * blockIdx.x], tok0 = work[3 * blockIdx.x + 1], kvh = work[3 * blockIdx.x + 2];
@@ -219,9 +218,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(k_full0 + 8 * s, RING_PRODUCERS);  // one arrival (with its byte count) per producer warp of the ring
+      mbar_init(k_full0 + 8 * s, 1);
       mbar_init(k_empty0 + 8 * s, 1);
-      mbar_init(v_full0 + 8 * s, RING_PRODUCERS);
+      mbar_init(v_full0 + 8 * s, 1);
       mbar_init(v_empty0 + 8 * s, 1);
       mbar_init(s_full0 + 8 * s, 1);
     }
@@ -240,14 +239,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 0 || warp >= 6) {
-    // ---- producers: warp 0 loads Q once, then the K tiles; warp 6 the V tiles (with two producers
-    // a ring, warps 7 and 8 take the second half of a tile's 16-key groups). Issuing a box keeps a
-    // warp busy for about 70 ns: one warp for both rings spent more than half a tile's time on it
-    // (2,048 tokens: 61 us with one warp, 52 us with one per ring). ------------------------------
-    const int which = (warp == 0 || warp == 7) ? 0 : 1;  // 0 keys, 1 values
-    const int part = warp >= 7 ? 1 : 0;                  // which share of the tile's groups
-    constexpr int PART_GROUPS = BN / 16 / RING_PRODUCERS;
+  if (warp == 0 || warp == 6) {
+    // ---- producers: warp 0 loads Q once, then the K tiles; warp 6 the V tiles. Issuing a box keeps
+    // a warp busy for about 70 ns: one warp for both rings spent more than half a tile's time on it
+    // (2,048 tokens: 61 us with one warp, 52 us with one per ring; two per ring: no faster). ------
+    const int which = warp == 0 ? 0 : 1;  // 0 keys, 1 values
     if (warp == 0 && lane == 0) {
       mbar_expect_tx(q_full, DH * ROWS * 128);
       for (int h = 0; h < DH; ++h)
@@ -256,8 +252,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     // Lane = group * DH + half: each of the tile's boxes (16 keys x 64 dims) is issued by its own lane.
     const int* table = block_table + (size_t)seq * max_pages;
     if (lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kv) : "memory");
-    const int g = part * PART_GROUPS + lane / DH, h = lane % DH;
-    const bool active = lane < PART_GROUPS * DH;
+    const int g = lane / DH, h = lane % DH;
+    const bool active = lane < (BN / 16) * DH;
     // The page of this lane's group in tile t (-2: the group lies outside what the block reads).
     // Page numbers are fetched a whole tile before they are used, so the table's latency is hidden.
     auto lookup = [&](int t) {
@@ -285,8 +281,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         if (which) {
           uint32_t mask = 0;
 #pragma unroll
-          for (int x = 0; x < PART_GROUPS; ++x) mask |= ((loaded >> (x * DH)) & 1u) << (part * PART_GROUPS + x);
-          group_mask[RING_PRODUCERS * s + part] = mask;
+          for (int x = 0; x < BN / 16; ++x) mask |= ((loaded >> (x * DH)) & 1u) << x;
+          group_mask[s] = mask;
         }
         mbar_expect_tx(full, __popc(loaded) * GROUP_BYTES);
       }
@@ -354,7 +350,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         STAMP(1, j, 1);
-        const uint32_t mask = group_mask[RING_PRODUCERS * s] | group_mask[RING_PRODUCERS * s + RING_PRODUCERS - 1];
+        const uint32_t mask = group_mask[s];
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           if (!(mask & (1u << kk))) continue;  // keys never loaded: their P is zero, their V is stale
@@ -388,62 +384,54 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       // Which keys of the tile this row sees; a tile that the whole warp sees whole needs no masks.
       const int lo = max(row_lo - key0, 0), hi = min(row_hi - key0, BN - 1);  // visible columns [lo, hi]
       const bool whole = __all_sync(0xffffffffu, lo == 0 && hi == BN - 1);
-      // Pass 1: the row's maximum.
+      // The row's 64 scores, read once; then their maximum.
+      static_assert(BN == 64, "the softmax below handles one 64-column pass per tile");
+      uint32_t v[64];
+      tmem_load32(s_addr, v);
+      tmem_load32(s_addr + 32, v + 32);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       float tile_max = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 64) {
-        uint32_t v[64];
-        tmem_load32(s_addr + c, v);
-        tmem_load32(s_addr + c + 32, v + 32);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (whole) {
+      if (whole) {
+        float part[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one of 64
 #pragma unroll
-          for (int i = 0; i < 64; ++i) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
-        } else {
+        for (int i = 0; i < 64; ++i) part[i & 3] = fmaxf(part[i & 3], __uint_as_float(v[i]));
+        tile_max = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
+      } else {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            const int col = c + i;
-            if (col >= lo && col <= hi) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
-          }
-        }
+        for (int i = 0; i < 64; ++i)
+          if (i >= lo && i <= hi) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
       }
       if (row == 0) STAMP(2, j, 1);
       const float m_new = fmaxf(m, tile_max);
       const float offset = m_new == -INFINITY ? 0.f : m_new * sl2;
       const float alpha = (m == -INFINITY || m_new == m) ? 1.f : fast_exp2(m * sl2 - offset);
       m = m_new;
-      // Pass 2: P = exp2(s * scale * log2e - offset), rounded to bfloat16, kept in registers: the
+      // P = exp2(s * scale * log2e - offset), rounded to bfloat16, kept in registers: the
       // arithmetic overlaps the previous tile's P V, which still reads the shared P tile.
-      static_assert(BN == 64, "the softmax below handles one 64-column pass per tile");
-      float sum = 0.f;
+      float sums[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[32];
-      {
-        uint32_t v[64];
-        tmem_load32(s_addr, v);
-        tmem_load32(s_addr + 32, v + 32);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (whole) {
+      if (whole) {
 #pragma unroll
-          for (int i = 0; i < 64; i += 2) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), sl2, -offset));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), sl2, -offset));
-            sum += p0 + p1;
-            packed[i / 2] = pack_bf16(p0, p1);
+        for (int i = 0; i < 64; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), sl2, -offset));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), sl2, -offset));
+          sums[(i >> 1) & 3] += p0 + p1;
+          packed[i / 2] = pack_bf16(p0, p1);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) {
+          float p[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = i + e;
+            p[e] = (col >= lo && col <= hi) ? fast_exp2(fmaf(__uint_as_float(v[i + e]), sl2, -offset)) : 0.f;
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 64; i += 2) {
-            float p[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int col = i + e;
-              p[e] = (col >= lo && col <= hi) ? fast_exp2(fmaf(__uint_as_float(v[i + e]), sl2, -offset)) : 0.f;
-            }
-            sum += p[0] + p[1];
-            packed[i / 2] = pack_bf16(p[0], p[1]);
-          }
+          sums[(i >> 1) & 3] += p[0] + p[1];
+          packed[i / 2] = pack_bf16(p[0], p[1]);
         }
       }
+      const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
       // The previous tile's P V must be done before O is rescaled or P is overwritten.
       if (j > 0) {
         ok = mbar_wait(o_done, (j - 1) & 1, abort_flag);
