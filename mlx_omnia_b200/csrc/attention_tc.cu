@@ -402,6 +402,19 @@ __device__ __forceinline__ void combine_head(const float* __restrict__ part_o,
 //   part_o  [requests, nq, max_chunks, D] float32 (unnormalised), part_ml [requests, nq, max_chunks, 2]
 //   tickets [requests, nkv] int32, zero before the first launch; the merging block zeroes its
 //   ticket again, so the array is ready for the next launch.
+// What the decode kernel needs to do the step before it as well (a decode step's QK-norm, rotation
+// and cache write): the projected rows [.. q heads .. | .. k heads .. | .. v heads ..], each group
+// at its own column; `proj` null means q is given and the cache already holds the new token.
+struct FusedQK {
+  const bf16* proj;
+  int stride, q_col, k_col, v_col;
+  float eps;                       // of the weightless RMS norm of every q and k head; < 0: none
+  const float* inv_freq;           // D / 2 inverse frequencies (rotation of all D dims), or null
+  const long long* slot_mapping;   // where each token's key and value go: page * page_size + offset
+  bf16* pages;                     // the same pages, for writing
+  long long num_slots;
+};
+
 template <int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages,
@@ -411,7 +424,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
                         int* __restrict__ tickets, const bf16* __restrict__ gate, int gate_stride,
                         bf16* __restrict__ out, int chunk_keys, int max_chunks, int max_pages,
                         int num_pages, int nq, int nkv, int page_size, int window, float scale,
-                        int* err) {
+                        const FusedQK fused, int* err) {
   pdl_wait();
   constexpr int STAGES = WARPS == 1 ? DECODE_STAGES : 1;  // stages of each warp's own ring
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -470,9 +483,20 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
 
   // Query fragments straight from global memory: row g of the A operand is query head g of
   // the group (rows at or beyond GROUP are zero), columns 2t, 2t+1 (+8) of each 16-wide step.
+  // In the fused mode they are read from the projected row, normalised and rotated here: a
+  // thread holds 2 x 2 values of every 16 dims of heads g and g + 8, so a head's sum of squares
+  // is a sum over the four threads of its row, and a dim's rotation partner (D / 2 further)
+  // lies in the same thread, KSTEPS / 2 steps further.
+  // The token's rotation angles, once per warp: cos of the D / 2 angles, then their sin.
+  __shared__ float rope_cs[WARPS][D];
+  if (fused.proj && fused.inv_freq) {
+    for (int i = lane; i < D / 2; i += 32) sincosf((float)pos * fused.inv_freq[i], &rope_cs[warp][D / 2 + i], &rope_cs[warp][i]);
+    __syncwarp();
+  }
   unsigned qf[KSTEPS][4];
   {
     const int g = lane >> 2, t = lane & 3;
+    const bf16* q_src = fused.proj ? fused.proj + token * fused.stride + fused.q_col : q + token * nq * D;
 #pragma unroll
     for (int kstep = 0; kstep < KSTEPS; ++kstep) {
 #pragma unroll
@@ -480,12 +504,91 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
         const int dim = kstep * 16 + half * 8 + 2 * t;
         unsigned lo_row = 0u, hi_row = 0u;
         if (dim < D) {
-          if (g < GROUP) lo_row = __ldg(reinterpret_cast<const unsigned*>(q + (token * nq + kvh * GROUP + g) * D + dim));
-          if (g + 8 < GROUP) hi_row = __ldg(reinterpret_cast<const unsigned*>(q + (token * nq + kvh * GROUP + g + 8) * D + dim));
+          if (g < GROUP) lo_row = __ldcg(reinterpret_cast<const unsigned*>(q_src + (size_t)(kvh * GROUP + g) * D + dim));
+          if (g + 8 < GROUP) hi_row = __ldcg(reinterpret_cast<const unsigned*>(q_src + (size_t)(kvh * GROUP + g + 8) * D + dim));
         }
         qf[kstep][2 * half] = lo_row;
         qf[kstep][2 * half + 1] = hi_row;
       }
+    }
+    if (fused.proj) {
+      // v[row][kstep][half][e]: float32 copies of the fragment values.
+      float ss[2] = {0.f, 0.f};
+#pragma unroll
+      for (int kstep = 0; kstep < KSTEPS; ++kstep)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qf[kstep][x]));
+          ss[x & 1] += f.x * f.x + f.y * f.y;
+        }
+      float norm[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], 1);
+        ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], 2);
+        norm[r] = fused.eps >= 0.f ? rsqrtf(ss[r] / (float)D + fused.eps) : 1.f;
+      }
+#pragma unroll
+      for (int kstep = 0; kstep < KSTEPS / 2; ++kstep)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          // Slot x of step kstep holds dims (kstep * 16 + (x >> 1) * 8 + 2 t, + 1) of row g + 8 * (x & 1).
+          const int dim = kstep * 16 + (x >> 1) * 8 + 2 * t;
+          const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qf[kstep][x]));
+          const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qf[kstep + KSTEPS / 2][x]));
+          const float n = norm[x & 1];
+          float c0 = 1.f, s0 = 0.f, c1 = 1.f, s1 = 0.f;
+          if (fused.inv_freq) {
+            c0 = rope_cs[warp][dim], s0 = rope_cs[warp][D / 2 + dim];
+            c1 = rope_cs[warp][dim + 1], s1 = rope_cs[warp][D / 2 + dim + 1];
+          }
+          const float ax = a.x * n, ay = a.y * n, bx = b.x * n, by = b.y * n;
+          qf[kstep][x] = pack_bf16(ax * c0 - bx * s0, ay * c1 - by * s1);
+          qf[kstep + KSTEPS / 2][x] = pack_bf16(ax * s0 + bx * c0, ay * s1 + by * c1);
+        }
+    }
+  }
+  // Fused mode: the new token's key and value (this request's, this head's), for the warp whose
+  // tile holds position `pos`: lane l owns dims l * D / 32 .. of the head; a dim's rotation
+  // partner lives 16 lanes away. They go to the cache pages and, once that tile has landed,
+  // over its row of the tile (the cache had nothing there yet).
+  constexpr int VW = D / 32 > 0 ? D / 32 : 1;
+  float new_k[VW], new_v[VW];
+  const bool brings_new = fused.proj != nullptr && pos >= lo && pos <= hi &&
+                          ((pos / DECODE_BN - lo / DECODE_BN) % WARPS) == warp;
+  if (brings_new) {
+    const bf16* k_src = fused.proj + token * fused.stride + fused.k_col + (size_t)kvh * D + lane * VW;
+    const bf16* v_src = fused.proj + token * fused.stride + fused.v_col + (size_t)kvh * D + lane * VW;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VW; ++i) {
+      new_k[i] = __bfloat162float(k_src[i]);
+      new_v[i] = __bfloat162float(v_src[i]);
+      ss += new_k[i] * new_k[i];
+    }
+    const float n = fused.eps >= 0.f ? rsqrtf(warp_sum(ss) / (float)D + fused.eps) : 1.f;
+#pragma unroll
+    for (int i = 0; i < VW; ++i) {
+      float mine = new_k[i] * n;
+      if (fused.inv_freq) {
+        const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+        const float c = rope_cs[warp][(lane & 15) * VW + i], sn = rope_cs[warp][D / 2 + (lane & 15) * VW + i];
+        mine = lane < 16 ? mine * c - other * sn : other * sn + mine * c;
+      }
+      new_k[i] = __bfloat162float(__float2bfloat16_rn(mine));  // as the cache will hold it
+    }
+    const long long slot = fused.slot_mapping[token];
+    if (slot >= 0 && slot < fused.num_slots) {
+      const long long page = slot / page_size, off = slot % page_size;
+      bf16* k_dst = fused.pages + (((page * 2 + 0) * nkv + kvh) * page_size + off) * D + lane * VW;
+      bf16* v_dst = fused.pages + (((page * 2 + 1) * nkv + kvh) * page_size + off) * D + lane * VW;
+#pragma unroll
+      for (int i = 0; i < VW; ++i) {
+        k_dst[i] = __float2bfloat16_rn(new_k[i]);
+        v_dst[i] = __float2bfloat16_rn(new_v[i]);
+      }
+    } else if (slot >= fused.num_slots && lane == 0) {
+      atomicOr(err, OMNIA_ERR_SLOT);
     }
   }
   float o[NT_O][4];
@@ -507,7 +610,16 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     cp_async_commit();
     cp_async_wait<STAGES - 1>();
     __syncwarp();
-    const bf16* kt = kv + (tile % STAGES) * 2 * DECODE_BN * ROW;
+    bf16* kt = kv + (tile % STAGES) * 2 * DECODE_BN * ROW;
+    if (brings_new && (tile0 + tile * WARPS) == pos / DECODE_BN) {
+      const int row = pos - (tile0 + tile * WARPS) * DECODE_BN;
+#pragma unroll
+      for (int i = 0; i < VW; ++i) {
+        kt[row * ROW + lane * VW + i] = __float2bfloat16_rn(new_k[i]);
+        kt[(DECODE_BN + row) * ROW + lane * VW + i] = __float2bfloat16_rn(new_v[i]);
+      }
+      __syncwarp();
+    }
     attend_tile<DECODE_BN>(qf, kt, kt + DECODE_BN * ROW, (tile0 + tile * WARPS) * DECODE_BN, row_lo, row_hi,
                            sl2, m, l, o);
     __syncwarp();
@@ -627,17 +739,27 @@ extern "C" int omnia_attention_prefill_tc(const void* q, const void* pages, cons
   return OMNIA_LAUNCH_RESULT();
 }
 
+// proj non-null selects the fused mode: the kernel first does the step's QK-norm (eps < 0: none),
+// rotation (inv_freq: head_dim / 2 inverse frequencies, or null) and cache write from the
+// projected rows [tokens, stride] with q, k, v heads at q_col, k_col, v_col, and q is not read.
+// It needs a head size that is a multiple of 32.
 extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const int* block_table,
                                          const int* cu_seqlens, const int* seq_lens,
                                          const int* seq_ids, int requests, float* part_o,
                                          float* part_ml, int* tickets, int chunk_keys,
                                          int max_chunks, const void* gate, int gate_stride,
                                          void* out, int max_pages, int num_pages, int nq, int nkv,
-                                         int page_size, int window, float scale, int warps, int* err,
-                                         cudaStream_t stream) {
+                                         int page_size, int window, float scale, int warps,
+                                         const void* proj, int proj_stride, int q_col, int k_col, int v_col,
+                                         float eps, const float* inv_freq, const long long* slot_mapping,
+                                         int* err, cudaStream_t stream) {
   if (requests == 0) return 0;
   if (nq != nkv * GROUP || chunk_keys % DECODE_BN != 0 || max_chunks < 1 || (warps != 1 && warps != 4))
     return (int)cudaErrorInvalidValue;
+  if (proj != nullptr && (D % 32 != 0 || slot_mapping == nullptr || proj_stride % 2 || q_col % 2 || k_col % 2 || v_col % 2))
+    return (int)cudaErrorInvalidValue;
+  const FusedQK fused{(const bf16*)proj, proj_stride, q_col, k_col, v_col, eps, inv_freq, slot_mapping,
+                      (bf16*)const_cast<void*>(pages), (long long)num_pages * page_size};
   // One warp: a two-stage ring. Four warps: one stage each (a warp has few tiles), and the merge area fits in it.
   const size_t smem = (size_t)((warps == 1 ? DECODE_STAGES : 4) * 2 * DECODE_BN) * ROW * sizeof(bf16);
   static bool configured = false;
@@ -654,12 +776,12 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
     launch_pdl(attention_decode_kernel<1>, dim3(max_chunks, nkv, requests), 32, smem, stream,
         (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
         tickets, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
-        num_pages, nq, nkv, page_size, window, scale, err);
+        num_pages, nq, nkv, page_size, window, scale, fused, err);
   else
     launch_pdl(attention_decode_kernel<4>, dim3(max_chunks, nkv, requests), 128, smem, stream,
         (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
         tickets, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
-        num_pages, nq, nkv, page_size, window, scale, err);
+        num_pages, nq, nkv, page_size, window, scale, fused, err);
   return OMNIA_LAUNCH_RESULT();
 }
 
@@ -740,7 +862,7 @@ extern "C" int omnia_attention_decode_tc_static(const void* q, const void* pages
   launch_pdl(attention_decode_kernel<1>, dim3(max_chunks, nkv, requests), 32, smem, stream,
       (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
       ticket_area, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
-      num_pages, nq, nkv, page_size, window, scale, err);
+      num_pages, nq, nkv, page_size, window, scale, FusedQK{}, err);
   e = cudaGetLastError();
   if (e != cudaSuccess) snprintf(static_error, sizeof static_error, "launch: %s", cudaGetErrorString(e));
   return (int)e;

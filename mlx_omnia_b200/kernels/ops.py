@@ -13,6 +13,8 @@ from __future__ import annotations
 import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
+from dataclasses import dataclass
+
 import torch
 
 from mlx_omnia_b200.csrc.build import load_library
@@ -298,17 +300,53 @@ def tcgen05_attention_supported(dtype: torch.dtype, nq: int, nkv: int, d: int, p
             and nq // nkv <= 16)
 
 
-def paged_attention(q: torch.Tensor, kv: KVView, step: StepContext, scale: float,
-                    gate: torch.Tensor | None = None, gate_col: int = 0) -> torch.Tensor:
+@dataclass
+class Projection:
+    """A decode step's projected rows, for the decode attention kernel to normalise, rotate and
+    store by itself (what `qk_norm_rope_store` would do in a kernel of its own)."""
+    rows: torch.Tensor  # [tokens, stride]
+    q_col: int
+    k_col: int
+    v_col: int
+    nq: int
+    d: int
+    eps: float | None
+    inv_freq: torch.Tensor | None
+
+
+USE_FUSED_DECODE = True
+"""Decode-only steps leave QK-norm, rotation and the cache write to the attention kernel."""
+
+
+def decode_fusable(proj: torch.Tensor, nq: int, nkv: int, d: int, inv_freq: torch.Tensor | None,
+                   kv: KVView, step: StepContext) -> bool:
+    """Whether the decode attention kernel can take the projected rows as they are: a step of
+    single tokens, bfloat16, a head size that is a multiple of 32, rotated whole or not at all,
+    and a cache entry that this layer writes."""
+    return (USE_FUSED_DECODE and step.decode_only and proj.is_cuda and kv.writes and d % 32 == 0
+            and (inv_freq is None or 2 * inv_freq.shape[0] == d) and proj.shape[1] % 2 == 0
+            and tiled_attention_supported(proj.dtype, nq, nkv, d))
+
+
+def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale: float,
+                    gate: torch.Tensor | None = None, gate_col: int = 0,
+                    projection: Projection | None = None) -> torch.Tensor:
     """Causal (windowed) attention of this step's queries over the paged cache, the
     output multiplied by sigmoid(gate) when `gate` (the projected rows; the gate's
     columns start at `gate_col`) is given.  -> [tokens, nq * d]
+
+    With `projection` (only where `decode_fusable` holds) q is not given: the kernel makes the
+    queries and the new keys and values from the projected rows, and writes the latter to the cache.
 
     bfloat16 with a supported head size runs on the tensor-core kernels: the split-key
     decode kernel when every request brings one token; otherwise the tcgen05 prefill kernel
     (head sizes 64 and 128, pages of a multiple of 16) or the mma.sync prefill kernel. Other
     cases (the 32-bit path among them) run on the generic kernel."""
-    tokens, nq, d = q.shape
+    if projection is not None:
+        tokens, nq, d = projection.rows.shape[0], projection.nq, projection.d
+        q = projection.rows  # for its dtype and device only
+    else:
+        tokens, nq, d = q.shape
     nkv = kv.pages.shape[2]
     out = torch.empty(tokens, nq * d, dtype=q.dtype, device=q.device)
     gate_ptr = None if gate is None else gate.data_ptr() + gate_col * gate.element_size()
@@ -338,11 +376,16 @@ def paged_attention(q: torch.Tensor, kv: KVView, step: StepContext, scale: float
         fn = _function("attention_tc", "omnia_attention_decode_tc",
                        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                         c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                        c_float, c_int, c_void_p, c_void_p], defines)
-        _check(fn(_ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.seq_lens),
-                  _ptr(single), count, _ptr(part_o), _ptr(part_ml), _ptr(tickets), chunk, max_chunks, gate_ptr,
-                  gate_stride, _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size, kv.window or 0, scale, warps,
-                  err, _stream()), "attention_decode")
+                        c_float, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+                        c_void_p, c_void_p], defines)
+        p = projection
+        fused = (None, 0, 0, 0, 0, -1.0, None, None) if p is None else (
+            _ptr(p.rows), p.rows.shape[1], p.q_col, p.k_col, p.v_col, -1.0 if p.eps is None else p.eps,
+            _ptr(p.inv_freq), _ptr(kv.slot_mapping))
+        _check(fn(None if p is not None else _ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens),
+                  _ptr(step.seq_lens), _ptr(single), count, _ptr(part_o), _ptr(part_ml), _ptr(tickets), chunk,
+                  max_chunks, gate_ptr, gate_stride, _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size,
+                  kv.window or 0, scale, warps, *fused, err, _stream()), "attention_decode")
         if step.decode_only or all(n == 1 for n in step.q_lens):
             return out
     if USE_TCGEN05 and tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):

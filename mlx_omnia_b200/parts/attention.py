@@ -76,9 +76,18 @@ class GQAAttention(Mixer):
         if ctx.kv.writes and not self.own_kv:
             raise RuntimeError("a mixer without k/v projections cannot own a cache entry")
         proj = ops.linear(h, self.in_proj)
-        q = ops.qk_norm_rope_store(proj, self.q_col, self.k_col, self.v_col, self.heads, self.kv_heads,
-                                   self.head_dim, self.qk_norm_eps, self.position.table(), ctx.step.positions,
-                                   ctx.kv if self.own_kv else None)
-        out = ops.paged_attention(q, ctx.kv, ctx.step, self.scale,
-                                  gate=proj if self.gated else None, gate_col=self.gate_col)
+        inv_freq = self.position.table()
+        gate = proj if self.gated else None
+        if self.own_kv and ops.decode_fusable(proj, self.heads, self.kv_heads, self.head_dim, inv_freq, ctx.kv,
+                                              ctx.step):
+            # Single tokens only: the attention kernel normalises, rotates and stores by itself.
+            rows = ops.Projection(proj, self.q_col, self.k_col, self.v_col, self.heads, self.head_dim,
+                                  self.qk_norm_eps, inv_freq)
+            out = ops.paged_attention(None, ctx.kv, ctx.step, self.scale, gate=gate, gate_col=self.gate_col,
+                                      projection=rows)
+        else:
+            q = ops.qk_norm_rope_store(proj, self.q_col, self.k_col, self.v_col, self.heads, self.kv_heads,
+                                       self.head_dim, self.qk_norm_eps, inv_freq, ctx.step.positions,
+                                       ctx.kv if self.own_kv else None)
+            out = ops.paged_attention(q, ctx.kv, ctx.step, self.scale, gate=gate, gate_col=self.gate_col)
         return ops.linear(out, self.o_proj)

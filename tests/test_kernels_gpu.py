@@ -172,6 +172,46 @@ def test_paged_attention_decode_only(ops, dtype, nq, nkv, d, page, window):
     ops.raise_on_error(q.device)
 
 
+@pytest.mark.parametrize("rotated", [True, False])
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(6, 3, 128, 16, None), (6, 3, 128, 16, 200), (16, 8, 64, 16, None),
+                                                   (10, 2, 96, 16, None), (16, 1, 128, 32, 300), (4, 4, 64, 64, 70),
+                                                   (2, 1, 32, 16, 40)])
+def test_decode_attention_from_projected_rows(ops, nq, nkv, d, page, window, rotated):
+    """The decode kernel's fused mode: QK-norm, rotation and the cache write happen inside it.
+    The place of the new token holds NaN beforehand, so a kernel that attended what the cache
+    held there instead of its own key and value would show; lengths sit around tile and chunk edges."""
+    dtype = torch.bfloat16
+    seq_lens = [1, 31, 32, 33, 127, 128, 129, 257, 700]
+    step = step_of([1] * len(seq_lens), seq_lens)
+    pages, table = make_kv(seq_lens, nkv, d, page, dtype, 1 + sum(-(-n // page) for n in seq_lens), seed=8)
+    pages.fill_(float("nan"))
+    slots = []
+    for s, n in enumerate(seq_lens):
+        for first in range(0, n - 1, page):
+            count = min(page, n - 1 - first)
+            pages[int(table[s, first // page]), :, :, :count, :] = rand(2, nkv, count, d, dtype=dtype, seed=100 * s + first)
+        slots.append(int(table[s, (n - 1) // page]) * page + (n - 1) % page)
+    slots = torch.tensor(slots, device="cuda")
+    width = (2 * nq + 2 * nkv) * d + 8
+    proj = rand(step.num_tokens, width, dtype=dtype, seed=17)
+    inv_freq = (10000.0 ** (-torch.arange(d // 2, dtype=torch.float64) * 2 / d)).float().cuda() if rotated else None
+    q_col, k_col, v_col, gate_col = 8, 8 + 2 * nq * d, 8 + 2 * nq * d + nkv * d, 8 + nq * d
+    scale = 0.9 * d ** -0.5
+    for eps in (1e-6, None):
+        fused = KVView(pages.clone(), table, slots, page, window)
+        plain = KVView(pages.clone(), table, slots, page, window)
+        assert ops.decode_fusable(proj, nq, nkv, d, inv_freq, fused, step)
+        rows = ops.Projection(proj, q_col, k_col, v_col, nq, d, eps, inv_freq)
+        got = ops.paged_attention(None, fused, step, scale, gate=proj, gate_col=gate_col, projection=rows)
+        q = kernel_refs.qk_norm_rope_store(proj, q_col, k_col, v_col, nq, nkv, d, eps, inv_freq, step.positions, plain)
+        want = kernel_refs.paged_attention(q, plain, step, scale, gate=proj, gate_col=gate_col)
+        close(got, want, dtype)
+        written = ~torch.isnan(plain.pages)
+        assert torch.equal(written, ~torch.isnan(fused.pages))
+        close(fused.pages[written], plain.pages[written], dtype)
+    ops.raise_on_error(proj.device)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_paged_attention_finds_a_far_key(ops, dtype):
     """One key among hundreds matches the query: the output must be its value."""
