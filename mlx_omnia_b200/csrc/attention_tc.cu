@@ -425,7 +425,12 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
                         bf16* __restrict__ out, int chunk_keys, int max_chunks, int max_pages,
                         int num_pages, int nq, int nkv, int page_size, int window, float scale,
                         const FusedQK fused, int* err) {
-  pdl_wait();
+  // In the fused mode nothing up to the query fragments depends on the kernel before this one
+  // (the lengths and tables were copied in before the step began, the keys and values of earlier
+  // tokens were written in earlier steps), so the block's start and its first loads of the cache
+  // run while that kernel finishes. Every block waits before it leaves, also one with nothing to do.
+  const bool early = fused.proj != nullptr;
+  if (!early) pdl_wait();
   constexpr int STAGES = WARPS == 1 ? DECODE_STAGES : 1;  // stages of each warp's own ring
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -433,10 +438,12 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
   const int seq = seq_ids ? seq_ids[blockIdx.z] : blockIdx.z;
   const int kvh = blockIdx.y, chunk = blockIdx.x;
   const int pos = seq_lens[seq] - 1;
-  if (pos < 0) return;
   const int first = window > 0 ? max(0, pos - window + 1) : 0;
   const int lo = max(first, chunk * chunk_keys), hi = min(pos, (chunk + 1) * chunk_keys - 1);
-  if (lo > hi) return;
+  if (pos < 0 || lo > hi) {
+    if (early) pdl_wait();
+    return;
+  }
   const size_t token = (size_t)cu_seqlens[seq];
   // The chunk's block-table entries are read once, up front: a tile's loads then never wait
   // for a table lookup. (Chunks of more than DECODE_TABLE pages read the table directly.)
@@ -475,8 +482,10 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
       cp_async16(vt + key * ROW + c * 8, kp ? kp + v_offset + c * 8 : pages, kp != nullptr);
     }
   };
+  // In flight before the loop: all stages but one of a ring, the one stage of a warp without a ring.
+  constexpr int AHEAD = STAGES > 1 ? STAGES - 1 : 1;
 #pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) {
+  for (int s = 0; s < AHEAD; ++s) {
     if (s < tiles) load_tile(s, s);
     cp_async_commit();
   }
@@ -493,6 +502,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     for (int i = lane; i < D / 2; i += 32) sincosf((float)pos * fused.inv_freq[i], &rope_cs[warp][D / 2 + i], &rope_cs[warp][i]);
     __syncwarp();
   }
+  if (early) pdl_wait();
   unsigned qf[KSTEPS][4];
   {
     const int g = lane >> 2, t = lane & 3;
@@ -605,10 +615,14 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
   const float sl2 = scale * LOG2E;
 
   for (int tile = 0; tile < tiles; ++tile) {
-    const int ahead = tile + STAGES - 1;
-    if (ahead < tiles) load_tile(ahead, ahead % STAGES);
-    cp_async_commit();
-    cp_async_wait<STAGES - 1>();
+    if (STAGES > 1) {
+      const int ahead = tile + STAGES - 1;
+      if (ahead < tiles) load_tile(ahead, ahead % STAGES);
+      cp_async_commit();
+      cp_async_wait<STAGES - 1>();
+    } else {
+      cp_async_wait<0>();
+    }
     __syncwarp();
     bf16* kt = kv + (tile % STAGES) * 2 * DECODE_BN * ROW;
     if (brings_new && (tile0 + tile * WARPS) == pos / DECODE_BN) {
@@ -623,6 +637,10 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     attend_tile<DECODE_BN>(qf, kt, kt + DECODE_BN * ROW, (tile0 + tile * WARPS) * DECODE_BN, row_lo, row_hi,
                            sl2, m, l, o);
     __syncwarp();
+    if (STAGES == 1) {  // the one stage is free again
+      if (tile + 1 < tiles) load_tile(tile + 1, 0);
+      cp_async_commit();
+    }
   }
   cp_async_wait<0>();
   pdl_launch_dependents();  // the cache is read: the next kernel may begin its preamble
