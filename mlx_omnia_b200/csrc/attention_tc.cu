@@ -336,60 +336,79 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pa
   }
 }
 
-// Merge chunks c0..c1 of one (token, head), ascending, then gate and round; run by one warp.
-// Lanes hold the chunks' weights (32 chunks per round, rescaled online across rounds), then
-// every lane accumulates its own dims over the chunks. Partials are read from L2.
-__device__ __forceinline__ void combine_head(const float* __restrict__ part_o,
-                                             const float* __restrict__ part_ml, size_t base,
-                                             int c0, int c1, const bf16* gate_row, bf16* out_row) {
+// Merge chunks c0..c1 of H heads of one token (heads head0 .., whose partials lie max_chunks apart),
+// ascending, then gate and round; run by one warp. The merge is the tail of the whole kernel and
+// nothing but memory round trips (the partials were written to L2 a moment ago by other blocks), so
+// everything a round needs is asked for before anything is used: the gates at once, then per
+// round of eight chunks the chunks' (max, sum) pairs, one chunk per lane, and the H x 8 partial
+// rows, every lane its own dims. Eight chunks or fewer are one round trip for all H heads.
+template <int H>
+__device__ __forceinline__ void combine_heads(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              size_t base, int max_chunks, int c0, int c1, const bf16* gate_row,
+                                              bf16* out_row) {
   const int lane = threadIdx.x & 31;
   constexpr int PER_LANE = (D + 31) / 32;
-  float acc[PER_LANE];
+  float gate_v[H][PER_LANE];
 #pragma unroll
-  for (int k = 0; k < PER_LANE; ++k) acc[k] = 0.f;
-  float mx = -INFINITY, total = 0.f;
-  for (int r0 = c0; r0 <= c1; r0 += 32) {
-    const int c = r0 + lane;
-    const bool live = c <= c1;
-    const float mc = live ? __ldcg(part_ml + (base + c) * 2) : -INFINITY;
-    const float lc = live ? __ldcg(part_ml + (base + c) * 2 + 1) : 0.f;
-    const float mx_new = fmaxf(mx, warp_max(mc));
-    const float rescale = mx == -INFINITY ? 0.f : exp2f(mx - mx_new);
-    const float w = live ? exp2f(mc - mx_new) : 0.f;
-    total = total * rescale + warp_sum(lc * w);
-    mx = mx_new;
+  for (int h = 0; h < H; ++h)
 #pragma unroll
-    for (int k = 0; k < PER_LANE; ++k) acc[k] *= rescale;
-    const int count = min(32, c1 - r0 + 1);
-    for (int j0 = 0; j0 < count; j0 += 8) {
-      float vals[8][PER_LANE];
+    for (int k = 0; k < PER_LANE; ++k) {
+      const int dim = lane + 32 * k;
+      gate_v[h][k] = gate_row && dim < D ? __bfloat162float(gate_row[(size_t)h * D + dim]) : 0.f;
+    }
+  float acc[H][PER_LANE], mx[H], total[H];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {  // the loads of eight chunks are in flight together
-        const float* src = part_o + (base + r0 + min(j0 + u, count - 1)) * D;
+  for (int h = 0; h < H; ++h) {
+    mx[h] = -INFINITY, total[h] = 0.f;
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k) acc[h][k] = 0.f;
+  }
+  for (int r0 = c0; r0 <= c1; r0 += 8) {
+    const int count = min(8, c1 - r0 + 1);
+    float mc[H], lc[H], vals[H][8][PER_LANE];
+#pragma unroll
+    for (int h = 0; h < H; ++h) {
+      const size_t slot = base + (size_t)h * max_chunks + r0;
+      mc[h] = lane < count ? __ldcg(part_ml + (slot + lane) * 2) : -INFINITY;
+      lc[h] = lane < count ? __ldcg(part_ml + (slot + lane) * 2 + 1) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float* src = part_o + (slot + min(u, count - 1)) * D;
 #pragma unroll
         for (int k = 0; k < PER_LANE; ++k) {
           const int dim = lane + 32 * k;
-          vals[u][k] = dim < D ? __ldcg(src + dim) : 0.f;
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const float wj = __shfl_sync(0xffffffffu, w, (j0 + u) & 31);
-        if (j0 + u < count) {
-#pragma unroll
-          for (int k = 0; k < PER_LANE; ++k) acc[k] += vals[u][k] * wj;
+          vals[h][u][k] = dim < D ? __ldcg(src + dim) : 0.f;
         }
       }
     }
-  }
-  const float inv = total > 0.f ? 1.f / total : 0.f;
 #pragma unroll
-  for (int k = 0; k < PER_LANE; ++k) {
-    const int dim = lane + 32 * k;
-    if (dim >= D) continue;
-    float v = acc[k] * inv;
-    if (gate_row) v *= 1.f / (1.f + expf(-__bfloat162float(gate_row[dim])));
-    out_row[dim] = __float2bfloat16_rn(v);
+    for (int h = 0; h < H; ++h) {
+      const float mx_new = fmaxf(mx[h], warp_max(mc[h]));
+      const float rescale = mx[h] == -INFINITY ? 0.f : exp2f(mx[h] - mx_new);
+      const float w = lane < count && mc[h] != -INFINITY ? exp2f(mc[h] - mx_new) : 0.f;
+      total[h] = total[h] * rescale + warp_sum(lc[h] * w);
+      mx[h] = mx_new;
+#pragma unroll
+      for (int k = 0; k < PER_LANE; ++k) acc[h][k] *= rescale;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float wj = __shfl_sync(0xffffffffu, w, u);  // zero beyond `count`
+#pragma unroll
+        for (int k = 0; k < PER_LANE; ++k) acc[h][k] += vals[h][u][k] * wj;
+      }
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < H; ++h) {
+    const float inv = total[h] > 0.f ? 1.f / total[h] : 0.f;
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k) {
+      const int dim = lane + 32 * k;
+      if (dim >= D) continue;
+      float v = acc[h][k] * inv;
+      if (gate_row) v *= 1.f / (1.f + expf(-gate_v[h][k]));
+      out_row[(size_t)h * D + dim] = __float2bfloat16_rn(v);
+    }
   }
 }
 
@@ -430,6 +449,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
   // tokens were written in earlier steps), so the block's start and its first loads of the cache
   // run while that kernel finishes. Every block waits before it leaves, also one with nothing to do.
   const bool early = fused.proj != nullptr;
+  OMNIA_TRACE_BLOCK(2);
   if (!early) pdl_wait();
   constexpr int STAGES = WARPS == 1 ? DECODE_STAGES : 1;  // stages of each warp's own ring
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -502,7 +522,9 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     for (int i = lane; i < D / 2; i += 32) sincosf((float)pos * fused.inv_freq[i], &rope_cs[warp][D / 2 + i], &rope_cs[warp][i]);
     __syncwarp();
   }
+  OMNIA_TRACE_BLOCK(3);
   if (early) pdl_wait();
+  OMNIA_TRACE_BLOCK(4);
   unsigned qf[KSTEPS][4];
   {
     const int g = lane >> 2, t = lane & 3;
@@ -643,6 +665,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     }
   }
   cp_async_wait<0>();
+  OMNIA_TRACE_BLOCK(5);
   pdl_launch_dependents();  // the cache is read: the next kernel may begin its preamble
 
 #pragma unroll
@@ -714,16 +737,25 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
   int* counter = tickets + (size_t)blockIdx.z * nkv + kvh;
   if (lane == 0) ticket = atomicAdd(counter, 1);
   ticket = __shfl_sync(0xffffffffu, ticket, 0);
+  OMNIA_TRACE_BLOCK(6);
   if (ticket != c1 - c0) return;
   if (lane == 0) *counter = 0;
   __threadfence();
+  // Two heads at a time (their loads travel together; one at a time where a head's rows would not
+  // fit in registers twice), then the odd one.
+  constexpr int TOGETHER = D <= 128 ? 2 : 1;
 #pragma unroll 1
-  for (int r = 0; r < GROUP; ++r) {
+  for (int r = 0; r + TOGETHER <= GROUP; r += TOGETHER) {
     const int head = kvh * GROUP + r;
-    combine_head(part_o, part_ml, ((size_t)blockIdx.z * nq + head) * max_chunks, c0, c1,
-                 gate ? gate + token * gate_stride + (size_t)head * D : nullptr,
-                 out + (token * nq + head) * D);
+    combine_heads<TOGETHER>(part_o, part_ml, ((size_t)blockIdx.z * nq + head) * max_chunks, max_chunks, c0, c1,
+                     gate ? gate + token * gate_stride + (size_t)head * D : nullptr, out + (token * nq + head) * D);
   }
+  if (GROUP % TOGETHER) {
+    const int head = kvh * GROUP + GROUP - 1;
+    combine_heads<1>(part_o, part_ml, ((size_t)blockIdx.z * nq + head) * max_chunks, max_chunks, c0, c1,
+                     gate ? gate + token * gate_stride + (size_t)head * D : nullptr, out + (token * nq + head) * D);
+  }
+  OMNIA_TRACE_BLOCK(7);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -757,6 +789,11 @@ extern "C" int omnia_attention_prefill_tc(const void* q, const void* pages, cons
   return OMNIA_LAUNCH_RESULT();
 }
 
+// Shared memory of an SM, the most a block may ask for, and what a block costs beside its dynamic
+// part (the system's kilobyte and the kernel's static arrays). Both decode entry points allow the
+// kernels the same dynamic size, so neither undoes the other's setting.
+constexpr size_t SM_SHARED = 228 * 1024, BLOCK_MOST = 227 * 1024, BLOCK_OVERHEAD = 1024 + 5 * 1024;
+
 // proj non-null selects the fused mode: the kernel first does the step's QK-norm (eps < 0: none),
 // rotation (inv_freq: head_dim / 2 inverse frequencies, or null) and cache write from the
 // projected rows [tokens, stride] with q, k, v heads at q_col, k_col, v_col, and q is not read.
@@ -770,7 +807,7 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
                                          int page_size, int window, float scale, int warps,
                                          const void* proj, int proj_stride, int q_col, int k_col, int v_col,
                                          float eps, const float* inv_freq, const long long* slot_mapping,
-                                         int* err, cudaStream_t stream) {
+                                         int spread, int* err, cudaStream_t stream) {
   if (requests == 0) return 0;
   if (nq != nkv * GROUP || chunk_keys % DECODE_BN != 0 || max_chunks < 1 || (warps != 1 && warps != 4))
     return (int)cudaErrorInvalidValue;
@@ -779,16 +816,32 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
   const FusedQK fused{(const bf16*)proj, proj_stride, q_col, k_col, v_col, eps, inv_freq, slot_mapping,
                       (bf16*)const_cast<void*>(pages), (long long)num_pages * page_size};
   // One warp: a two-stage ring. Four warps: one stage each (a warp has few tiles), and the merge area fits in it.
-  const size_t smem = (size_t)((warps == 1 ? DECODE_STAGES : 4) * 2 * DECODE_BN) * ROW * sizeof(bf16);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)((size_t)(DECODE_STAGES * 2 * DECODE_BN) * ROW * sizeof(bf16)));
+  size_t smem = (size_t)((warps == 1 ? DECODE_STAGES : 4) * 2 * DECODE_BN) * ROW * sizeof(bf16);
+  static int sms = 0;
+  if (sms == 0) {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)(BLOCK_MOST - BLOCK_OVERHEAD));
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(attention_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               (int)((size_t)(4 * 2 * DECODE_BN) * ROW * sizeof(bf16)));
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
+                               (int)(BLOCK_MOST - BLOCK_OVERHEAD));
+    if (e != cudaSuccess) {
+      sms = 0;
+      return (int)e;
+    }
+  }
+  if (spread) {
+    // The blocks are handed to SMs as these become free, as many to an SM as fit, and the kernel
+    // before this one frees its SMs one after the other: left alone, six blocks each go to the first
+    // SMs (seen: 512 blocks on 86 of 148 SMs) and the rest of the GPU idles. So every block asks
+    // for so much shared memory that an SM holds no more than its share of the grid.
+    const long long blocks = (long long)max_chunks * nkv * requests;
+    const long long share = (blocks + sms - 1) / sms;
+    const size_t room = SM_SHARED / (size_t)share;
+    if (room > smem + BLOCK_OVERHEAD) smem = (room > BLOCK_MOST ? BLOCK_MOST : room) - BLOCK_OVERHEAD;
   }
   if (warps == 1)
     launch_pdl(attention_decode_kernel<1>, dim3(max_chunks, nkv, requests), 32, smem, stream,
@@ -859,8 +912,8 @@ extern "C" int omnia_attention_decode_tc_static(const void* q, const void* pages
       snprintf(static_error, sizeof static_error, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
       return (int)e;
     }
-    const size_t smem = (size_t)(DECODE_STAGES * 2 * DECODE_BN) * ROW * sizeof(bf16);
-    e = cudaFuncSetAttribute(attention_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaFuncSetAttribute(attention_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)(BLOCK_MOST - BLOCK_OVERHEAD));
     if (e != cudaSuccess) {
       snprintf(static_error, sizeof static_error, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
       return (int)e;

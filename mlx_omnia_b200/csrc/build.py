@@ -28,6 +28,11 @@ BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "--shared", "-Xcompiler", "-fPIC
 
 _loaded: dict[str, ctypes.CDLL] = {}
 
+TIMELINE = bool(os.environ.get("OMNIA_TIMELINE"))
+"""With OMNIA_TIMELINE set in the environment every library is the tracing build (see common.cuh):
+kernels stamp the GPU's clock around their wait for the kernel before them, and `timeline()` reads
+the marks. A tracing build is a library of its own beside the ordinary one."""
+
 
 class KernelBuildError(RuntimeError):
     """The CUDA extension could not be compiled or loaded."""
@@ -64,8 +69,15 @@ def _digest(source: Path, defines: dict[str, object], extra: list[str]) -> str:
     return h.hexdigest()[:16]
 
 
+def _with_mode(defines: dict[str, object] | None) -> dict[str, object]:
+    defines = dict(defines or {})
+    if TIMELINE:
+        defines["OMNIA_TIMELINE"] = 1
+    return defines
+
+
 def library_path(name: str, defines: dict[str, object] | None = None, extra: list[str] | None = None) -> Path:
-    defines = defines or {}
+    defines = _with_mode(defines)
     extra = extra or []
     source = SOURCE_DIR / f"{name}.cu"
     tag = "".join(f"_{k}{v}" for k, v in sorted(defines.items()))
@@ -75,7 +87,7 @@ def library_path(name: str, defines: dict[str, object] | None = None, extra: lis
 def compile_library(name: str, defines: dict[str, object] | None = None, extra: list[str] | None = None,
                     verbose: bool = True) -> Path:
     """Compile `name`.cu if its library is not there yet; return the library's path."""
-    defines = defines or {}
+    defines = _with_mode(defines)
     extra = extra or []
     target = library_path(name, defines, extra)
     if target.exists():
@@ -122,3 +134,28 @@ def load_library(name: str, defines: dict[str, object] | None = None, extra: lis
             raise KernelBuildError(f"could not load {path}: {error}") from error
         _loaded[key] = lib
     return lib
+
+
+def timeline() -> list[tuple[int, str, int, int, int, int]]:
+    """The marks that kernels of a tracing build (OMNIA_TIMELINE) have left since the last call, in
+    order of time: (nanoseconds on the GPU's clock, library, source line, phase, block, SM). Phase
+    0: block 0 of a kernel reached its wait for the kernel before it; 1: that wait was over; 2 and
+    up: a block trace (OMNIA_TRACE_BLOCK in the source), from every block. Synchronise the device first."""
+    if not TIMELINE:
+        raise KernelBuildError("set OMNIA_TIMELINE=1 before the package is imported to get the tracing build")
+    capacity = 65536
+    buffer = (ctypes.c_ulonglong * (3 * capacity))()
+    marks = []
+    for key, lib in _loaded.items():
+        take = getattr(lib, "omnia_timeline_take", None)
+        if take is None:  # a library none of whose kernels waits
+            continue
+        take.argtypes, take.restype = [ctypes.c_void_p, ctypes.c_int], ctypes.c_int
+        count = take(buffer, capacity)
+        if count < 0:
+            raise KernelBuildError(f"could not read the marks of {key}")
+        name = key.split("|")[0]
+        for i in range(count):
+            tag, where = int(buffer[3 * i + 1]), int(buffer[3 * i + 2])
+            marks.append((int(buffer[3 * i]), name, tag // 8, tag % 8, where & 0xFFFFFFFF, where >> 32))
+    return sorted(marks)

@@ -73,7 +73,54 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // an SM where the first kernel still runs, and later find in L1, through a cached load, lines
 // that the first kernel's blocks fetched from memory which has since been freed, handed out
 // again and rewritten. That was seen as a rare wrong token.)
+#ifndef OMNIA_TIMELINE
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#define OMNIA_TRACE_BLOCK(phase) do { } while (0)
+#else
+// Tracing build (-DOMNIA_TIMELINE): thread 0 of block (0, 0, 0) of every kernel stamps the GPU's
+// nanosecond clock when it reaches its wait and when the wait is over, i.e. when the kernel
+// before it has finished, tagged with the source line of the call. Each library keeps its own
+// marks; omnia_timeline_take hands them to the host and starts afresh. The distance between two
+// kernels' second marks is the time the earlier one takes in the stream as it really runs,
+// overlaps included, which no profiler that serialises launches shows.
+#define OMNIA_TIMELINE_MARKS 65536
+static __device__ unsigned long long omnia_marks[3 * OMNIA_TIMELINE_MARKS];
+static __device__ unsigned omnia_mark_count;
+// A mark: time, tag, and where it was made (block number within the grid, and the SM above bit 32).
+__device__ __forceinline__ void timeline_stamp(unsigned tag) {
+  unsigned long long now;
+  unsigned sm;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+  const unsigned at = atomicAdd(&omnia_mark_count, 1u);
+  const unsigned long long block = blockIdx.x + (unsigned long long)gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z);
+  if (at < OMNIA_TIMELINE_MARKS)
+    omnia_marks[3 * at] = now, omnia_marks[3 * at + 1] = tag, omnia_marks[3 * at + 2] = block | ((unsigned long long)sm << 32);
+}
+__device__ __forceinline__ void timeline_mark(unsigned tag) {
+  if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) timeline_stamp(tag);
+}
+// For looking inside one kernel: thread 0 of every block stamps (phases 2.. of the line's tag).
+#define OMNIA_TRACE_BLOCK(phase) do { if (threadIdx.x == 0) timeline_stamp(8 * __LINE__ + (phase)); } while (0)
+__device__ __forceinline__ void pdl_wait_at(unsigned line) {
+  timeline_mark(8 * line);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  timeline_mark(8 * line + 1);
+}
+#define pdl_wait() pdl_wait_at(__LINE__)
+// -> the number of marks copied: out[3 i] nanoseconds, out[3 i + 1] = 8 * line + phase (0 at the
+// wait, 1 after it, 2.. a block trace), out[3 i + 2] = block | sm << 32.
+extern "C" int omnia_timeline_take(unsigned long long* out, int capacity) {
+  unsigned count = 0;
+  if (cudaMemcpyFromSymbol(&count, omnia_mark_count, sizeof count) != cudaSuccess) return -1;
+  if (count > OMNIA_TIMELINE_MARKS) count = OMNIA_TIMELINE_MARKS;
+  if ((int)count > capacity) count = capacity;
+  if (count && cudaMemcpyFromSymbol(out, omnia_marks, 3 * sizeof(unsigned long long) * count) != cudaSuccess) return -1;
+  const unsigned zero = 0;
+  if (cudaMemcpyToSymbol(omnia_mark_count, &zero, sizeof zero) != cudaSuccess) return -1;
+  return (int)count;
+}
+#endif
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 template <typename... KernelArgs, typename... Args>

@@ -19,6 +19,15 @@
 // columns, and the block stores silu(gate) * up); soft cap (float32 logits).
 // bfloat16 operands, float32 accumulation; k a multiple of 8; a, w 16-byte aligned.
 //
+// A residual step that is still pending can ride along (PENDING): instead of activations the kernel
+// is given the float32 residual x, the branch that is to be added to it and the two norms' weights,
+//   x_out = x + rms(branch) * wb,   a = bfloat16(rms(x_out) * wo),
+// and every block works this out for itself while its first weights are on their way: a consumer
+// warp takes a row (hence at most eight), a lane holds its 1/32 of the row in registers (hence at
+// most 2,048 columns), the normalised row goes to shared memory, where the activations
+// are then fetched from, and one block per row writes x_out. x is not updated in place: other
+// blocks are still reading it.
+//
 // Every wait on a barrier is bounded: when the bound is hit the block raises OMNIA_ERR_TIMEOUT
 // in the error word, its warps leave their loops, the producer waits (bounded again) for the
 // copies it still has in flight, and the block returns.
@@ -60,6 +69,21 @@ constexpr int GROUP_TILES = GEMV_GROUP_TILES;              // tiles that share o
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
 
 enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_SOFTCAP = 2 };
+
+// A pending residual step (see the head of the file). wb / wo null: a norm without weights;
+// norm_branch 0: the branch is added as it is.
+struct PendingStep {
+  const float* x;
+  float* x_out;
+  const bf16* branch;
+  const float* wb;
+  const float* wo;
+  float eps_b, eps_o;
+  int norm_branch;
+};
+constexpr int PENDING_MAX_K = 2048;                        // a lane holds k / 32 values of a row
+constexpr int PENDING_CHUNKS = PENDING_MAX_K / (32 * 8);   // 8-column chunks of a row per lane
+constexpr int PENDING_PAD = 8;                             // columns between the rows in shared memory
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -110,6 +134,10 @@ __device__ __forceinline__ void mma_bf16(float* c, unsigned a0, unsigned a1, uns
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&v);
+}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS) : "memory"); }
 
 // The matrix row that row r (0..15) of tile `tile` holds, or -1 when it lies outside the matrix.
@@ -124,14 +152,21 @@ __device__ __forceinline__ int tile_row(int tile, int r, int n, int inner) {
 }
 
 // NT: activation tiles of 8 rows (1 for m <= 8, 2 for m <= 16).
-template <int NT, int EPI>
+__host__ __device__ constexpr size_t partial_bytes(int nt) { return sizeof(float) * CONSUMER_WARPS * GROUP_TILES * TILE_ROWS * (nt * 8 + 1); }
+
+template <int NT, int EPI, bool PENDING>
 __global__ void __launch_bounds__(THREADS, 1)
 gemv_stream_kernel(const bf16* __restrict__ a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
-                   int m, int n, int k, int inner, int tiles, float multiplier, float cap, int* __restrict__ err) {
+                   int m, int n, int k, int inner, int tiles, float multiplier, float cap, const PendingStep pending,
+                   int* __restrict__ err) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* ring = smem;
   float (*partial)[GROUP_TILES * TILE_ROWS][NT * 8 + 1] =
       reinterpret_cast<float (*)[GROUP_TILES * TILE_ROWS][NT * 8 + 1]>(smem + STAGES * STAGE_BYTES);
+  // PENDING: the normalised rows, [NT * 8][k + PENDING_PAD] bfloat16.
+  bf16* normed = reinterpret_cast<bf16*>(smem + STAGES * STAGE_BYTES + ((partial_bytes(NT) + 15) & ~(size_t)15));
+  // PENDING: the two norms' weights, [2][k] float32 (ones where a norm has none).
+  float* norm_w = reinterpret_cast<float*>(normed + (size_t)NT * 8 * (k + PENDING_PAD));
   __shared__ __align__(8) unsigned long long bars[2 * STAGES];
   __shared__ int abort_word;
   volatile int* abort_flag = &abort_word;
@@ -207,19 +242,117 @@ gemv_stream_kernel(const bf16* __restrict__ a, const __grid_constant__ CUtensorM
     }
     const uint4 zero = make_uint4(0, 0, 0, 0);
     const int in_stage = warp * WARP_COLS + 8 * t;  // this thread's first column within a stage
+    if (PENDING) {
+      // The norms' weights depend on no kernel, and the stream of matrices has long pushed them
+      // out of L2: they are fetched before the wait, so that after it only x and the branch are far.
+      for (int col = (threadIdx.x) * 4; col < k; col += CONSUMERS * 4) {
+        const float4 one = make_float4(1.f, 1.f, 1.f, 1.f);
+        *reinterpret_cast<float4*>(norm_w + col) =
+            pending.norm_branch && pending.wb ? __ldg(reinterpret_cast<const float4*>(pending.wb + col)) : one;
+        *reinterpret_cast<float4*>(norm_w + k + col) =
+            pending.wo ? __ldg(reinterpret_cast<const float4*>(pending.wo + col)) : one;
+      }
+      consumer_sync();
+    }
     pdl_wait();  // the activations come from the kernel before
     // From here on every earlier kernel is complete, so the next kernel's blocks may move in beside
     // this one (never more than two kernels overlap). Activations are read through L2 (__ldcg): a
     // block that started while an earlier kernel was still running must not find lines in L1 that
     // that kernel's blocks on the same SM left there.
     pdl_launch_dependents();
+    if (PENDING) {
+      const int stride = k + PENDING_PAD;
+#pragma unroll 1
+      for (int j = 0; j < NT; ++j) {
+        const int row = warp + 8 * j;
+        if (row >= m) break;
+        const bf16* br = pending.branch + (size_t)row * k;
+        const float* xr = pending.x + (size_t)row * k;
+        uint4 bv[PENDING_CHUNKS];
+        float xn[PENDING_CHUNKS][8];
+        // Everything the row needs is asked for at once; the two sums then only wait for it.
+#pragma unroll
+        for (int i = 0; i < PENDING_CHUNKS; ++i) {
+          const int col = (i * 32 + lane) * 8;
+          bv[i] = col < k ? __ldcg(reinterpret_cast<const uint4*>(br + col)) : zero;
+          const float4 lo = col < k ? __ldcg(reinterpret_cast<const float4*>(xr + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          const float4 hi = col < k ? __ldcg(reinterpret_cast<const float4*>(xr + col + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          xn[i][0] = lo.x, xn[i][1] = lo.y, xn[i][2] = lo.z, xn[i][3] = lo.w;
+          xn[i][4] = hi.x, xn[i][5] = hi.y, xn[i][6] = hi.z, xn[i][7] = hi.w;
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < PENDING_CHUNKS; ++i) {
+          const unsigned w4[4] = {bv[i].x, bv[i].y, bv[i].z, bv[i].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w4[e]));
+            ss += f.x * f.x + f.y * f.y;
+          }
+        }
+        const float scale_b = pending.norm_branch ? rsqrtf(warp_sum(ss) / (float)k + pending.eps_b) : 1.f;
+        const bool writes = (int)blockIdx.x == row % (int)gridDim.x;  // one block stores the row's new residual
+        ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < PENDING_CHUNKS; ++i) {
+          const int col = (i * 32 + lane) * 8;
+          if (col >= k) continue;
+          float gb[8];
+          {
+            const float4 lo = *reinterpret_cast<const float4*>(norm_w + col);
+            const float4 hi = *reinterpret_cast<const float4*>(norm_w + col + 4);
+            gb[0] = lo.x, gb[1] = lo.y, gb[2] = lo.z, gb[3] = lo.w, gb[4] = hi.x, gb[5] = hi.y, gb[6] = hi.z, gb[7] = hi.w;
+          }
+          const unsigned w4[4] = {bv[i].x, bv[i].y, bv[i].z, bv[i].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w4[e]));
+            float v0 = f.x, v1 = f.y;
+            if (pending.norm_branch) v0 = v0 * scale_b * gb[2 * e], v1 = v1 * scale_b * gb[2 * e + 1];
+            xn[i][2 * e] += v0;
+            xn[i][2 * e + 1] += v1;
+            ss += xn[i][2 * e] * xn[i][2 * e] + xn[i][2 * e + 1] * xn[i][2 * e + 1];
+          }
+          if (writes) {
+            float* dst = pending.x_out + (size_t)row * k + col;
+            *reinterpret_cast<float4*>(dst) = make_float4(xn[i][0], xn[i][1], xn[i][2], xn[i][3]);
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(xn[i][4], xn[i][5], xn[i][6], xn[i][7]);
+          }
+        }
+        const float scale_o = rsqrtf(warp_sum(ss) / (float)k + pending.eps_o);
+#pragma unroll
+        for (int i = 0; i < PENDING_CHUNKS; ++i) {
+          const int col = (i * 32 + lane) * 8;
+          if (col >= k) continue;
+          float go[8];
+          {
+            const float4 lo = *reinterpret_cast<const float4*>(norm_w + k + col);
+            const float4 hi = *reinterpret_cast<const float4*>(norm_w + k + col + 4);
+            go[0] = lo.x, go[1] = lo.y, go[2] = lo.z, go[3] = lo.w, go[4] = hi.x, go[5] = hi.y, go[6] = hi.z, go[7] = hi.w;
+          }
+          uint4 packed;
+          packed.x = pack_bf16(xn[i][0] * scale_o * go[0], xn[i][1] * scale_o * go[1]);
+          packed.y = pack_bf16(xn[i][2] * scale_o * go[2], xn[i][3] * scale_o * go[3]);
+          packed.z = pack_bf16(xn[i][4] * scale_o * go[4], xn[i][5] * scale_o * go[5]);
+          packed.w = pack_bf16(xn[i][6] * scale_o * go[6], xn[i][7] * scale_o * go[7]);
+          *reinterpret_cast<uint4*>(normed + (size_t)row * stride + col) = packed;
+        }
+      }
+      consumer_sync();  // every warp reads every row
+    }
     auto fetch = [&](int c, uint4 (&dst)[KBLOCKS][NT]) {
       const int col0 = c * STAGE_COLS + in_stage;
 #pragma unroll
       for (int h = 0; h < KBLOCKS; ++h)
 #pragma unroll
-        for (int j = 0; j < NT; ++j)
-          dst[h][j] = alive[j] && col0 + 32 * h < k ? __ldcg(reinterpret_cast<const uint4*>(arow[j] + col0 + 32 * h)) : zero;
+        for (int j = 0; j < NT; ++j) {
+          if (!alive[j] || col0 + 32 * h >= k)
+            dst[h][j] = zero;
+          else if (PENDING)
+            dst[h][j] = *reinterpret_cast<const uint4*>(normed + (size_t)(8 * j + g) * (k + PENDING_PAD) + col0 + 32 * h);
+          else
+            dst[h][j] = __ldcg(reinterpret_cast<const uint4*>(arow[j] + col0 + 32 * h));
+        }
     };
     uint4 av[KBLOCKS][NT], av_next[KBLOCKS][NT];
     if (my_tiles > 0) fetch(0, av_next);
@@ -347,18 +480,26 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int k) {
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int NT, int EPI>
+// The most dynamic shared memory a launch of this shape asks for.
+template <int NT, bool PENDING>
+constexpr size_t fixed_most() {
+  return (size_t)STAGES * STAGE_BYTES + ((partial_bytes(NT) + 15) & ~(size_t)15) +
+         (PENDING ? sizeof(bf16) * NT * 8 * (size_t)(PENDING_MAX_K + PENDING_PAD) + sizeof(float) * 2 * PENDING_MAX_K : 0);
+}
+
+template <int NT, int EPI, bool PENDING>
 int launch(const bf16* a, const bf16* w, void* out, int m, int n, int k, int inner, float multiplier, float cap,
-           int* err, cudaStream_t stream) {
-  constexpr size_t smem =
-      (size_t)STAGES * STAGE_BYTES + sizeof(float) * CONSUMER_WARPS * GROUP_TILES * TILE_ROWS * (NT * 8 + 1);
+           const PendingStep& pending, int* err, cudaStream_t stream) {
+  const size_t fixed = (size_t)STAGES * STAGE_BYTES + ((partial_bytes(NT) + 15) & ~(size_t)15);
+  const size_t smem = fixed + (PENDING ? sizeof(bf16) * NT * 8 * (size_t)(k + PENDING_PAD) + sizeof(float) * 2 * k : 0);
+  constexpr size_t most = fixed_most<NT, PENDING>();
   static int sms = 0;
   if (sms == 0) {
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemv_stream_kernel<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      e = cudaFuncSetAttribute(gemv_stream_kernel<NT, EPI, PENDING>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
     if (e != cudaSuccess) {
       sms = 0;
       return (int)e;
@@ -367,16 +508,17 @@ int launch(const bf16* a, const bf16* w, void* out, int m, int n, int k, int inn
   CUtensorMap map_w;
   if (!make_map(&map_w, w, n, k)) return (int)cudaErrorInvalidValue;
   const int tiles = EPI == EPI_SWIGLU ? (inner + 7) / 8 : (n + TILE_ROWS - 1) / TILE_ROWS;
-  launch_pdl(gemv_stream_kernel<NT, EPI>, min(tiles, sms), THREADS, smem, stream, a, map_w, out, m, n, k, inner, tiles,
-             multiplier, cap, err);
+  launch_pdl(gemv_stream_kernel<NT, EPI, PENDING>, min(tiles, sms), THREADS, smem, stream, a, map_w, out, m, n, k, inner,
+             tiles, multiplier, cap, pending, err);
   return OMNIA_LAUNCH_RESULT();
 }
 
-template <int EPI>
+template <int EPI, bool PENDING>
 int launch_rows(const bf16* a, const bf16* w, void* out, int m, int n, int k, int inner, float multiplier, float cap,
-                int* err, cudaStream_t stream) {
-  if (m <= 8) return launch<1, EPI>(a, w, out, m, n, k, inner, multiplier, cap, err, stream);
-  return launch<2, EPI>(a, w, out, m, n, k, inner, multiplier, cap, err, stream);
+                const PendingStep& pending, int* err, cudaStream_t stream) {
+  if (m <= 8) return launch<1, EPI, PENDING>(a, w, out, m, n, k, inner, multiplier, cap, pending, err, stream);
+  if (PENDING) return (int)cudaErrorInvalidValue;  // sixteen normalised rows and the weights do not fit beside the ring
+  return launch<2, EPI, false>(a, w, out, m, n, k, inner, multiplier, cap, pending, err, stream);
 }
 
 }  // namespace
@@ -390,11 +532,37 @@ extern "C" int omnia_gemv_stream(const void* a, const void* w, void* out, int m,
   if (((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) != 0) return (int)cudaErrorInvalidValue;
   const bf16* ap = (const bf16*)a;
   const bf16* wp = (const bf16*)w;
+  const PendingStep none{};
   if (epilogue == EPI_SWIGLU) {
     if (n % 2) return (int)cudaErrorInvalidValue;
-    return launch_rows<EPI_SWIGLU>(ap, wp, out, m, n, k, n / 2, 1.f, 0.f, err, stream);
+    return launch_rows<EPI_SWIGLU, false>(ap, wp, out, m, n, k, n / 2, 1.f, 0.f, none, err, stream);
   }
-  if (epilogue == EPI_SOFTCAP) return launch_rows<EPI_SOFTCAP>(ap, wp, out, m, n, k, 0, multiplier, cap, err, stream);
+  if (epilogue == EPI_SOFTCAP)
+    return launch_rows<EPI_SOFTCAP, false>(ap, wp, out, m, n, k, 0, multiplier, cap, none, err, stream);
   if (epilogue != EPI_STORE) return (int)cudaErrorInvalidValue;
-  return launch_rows<EPI_STORE>(ap, wp, out, m, n, k, 0, 1.f, 0.f, err, stream);
+  return launch_rows<EPI_STORE, false>(ap, wp, out, m, n, k, 0, 1.f, 0.f, none, err, stream);
+}
+
+extern "C" int omnia_gemv_stream_pending_max_k(void) { return PENDING_MAX_K; }
+
+// The same product with a pending residual step in front of it (epilogues 0 and 1):
+//   x_out = x + (norm_branch ? rms(branch, eps_b) * wb : branch),  a = bfloat16(rms(x_out, eps_o) * wo),
+// x, x_out float32 [m, k] (different buffers, m <= 8), branch bfloat16 [m, k], wb, wo float32 [k] or null.
+extern "C" int omnia_gemv_stream_pending(const float* x, float* x_out, const void* branch, const float* wb,
+                                         float eps_b, int norm_branch, const float* wo, float eps_o, const void* w,
+                                         void* out, int m, int n, int k, int epilogue, int* err,
+                                         cudaStream_t stream) {
+  if (m == 0 || n == 0) return 0;
+  if (m > 8 || k % 8 != 0 || k <= 0 || k > PENDING_MAX_K || x == x_out) return (int)cudaErrorInvalidValue;
+  if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(x_out) | reinterpret_cast<uintptr_t>(branch) |
+        reinterpret_cast<uintptr_t>(wb) | reinterpret_cast<uintptr_t>(wo) | reinterpret_cast<uintptr_t>(w)) & 15) != 0)
+    return (int)cudaErrorInvalidValue;
+  const PendingStep pending{x, x_out, (const bf16*)branch, wb, wo, eps_b, eps_o, norm_branch};
+  const bf16* wp = (const bf16*)w;
+  if (epilogue == EPI_SWIGLU) {
+    if (n % 2) return (int)cudaErrorInvalidValue;
+    return launch_rows<EPI_SWIGLU, true>(nullptr, wp, out, m, n, k, n / 2, 1.f, 0.f, pending, err, stream);
+  }
+  if (epilogue != EPI_STORE) return (int)cudaErrorInvalidValue;
+  return launch_rows<EPI_STORE, true>(nullptr, wp, out, m, n, k, 0, 1.f, 0.f, pending, err, stream);
 }

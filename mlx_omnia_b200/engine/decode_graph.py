@@ -3,7 +3,7 @@
 A step in which every request brings one token launches some three hundred small
 kernels; issued one by one from Python they cost more host time than the GPU needs to
 run them. Such steps are therefore captured once per *bucket* (requests rounded up to
-a power of two, block-table width rounded up to a power of two) and replayed: the
+a power of two, block-table width rounded up to three significant bits) and replayed: the
 host writes the step's metadata into one pinned buffer, one copy brings it to the
 device buffer the captured kernels read, and the graph runs. Rows beyond the live
 requests are padding: sequence length 0, slot -1, position -1, which every kernel
@@ -31,8 +31,8 @@ from mlx_omnia_b200.kernels import ops
 from mlx_omnia_b200.parts.base import StepContext
 
 
-def _bucket(n: int, floor: int = 1) -> int:
-    b = floor
+def _bucket(n: int) -> int:
+    b = 1
     while b < n:
         b *= 2
     return b
@@ -168,7 +168,7 @@ class DecodeGraphs:
                 runner._shrink(request, 1)
             raise
         batch = _bucket(len(entries))
-        width = _bucket(max(max(len(t) for t in e.request.tables) for e in entries), 8)
+        width = ops.width_bucket(max(max(len(t) for t in e.request.tables) for e in entries))
         key = (batch, width)
         captured = self.captured.get(key)
         if captured is None:

@@ -193,37 +193,41 @@ def _step_buffers(step: StepContext, device: torch.device, wanted: dict) -> list
     return buffers
 
 
-def decode_plan(pairs: int, longest: int, sms: int = 148) -> tuple[int, int]:
-    """(keys per block, warps per block) of the decode attention kernel for `pairs` (request,
-    key/value head) pairs whose longest request holds `longest` positions. A warp keeps one
-    32-key tile (16 KB at head size 128) in flight. A block's time is a fixed part (about four
-    tiles' worth: its start, its partial result, the merge) plus its tiles (with four warps: a
-    quarter of them each); a tile takes the memory's latency (1.2 us) or, when the warps on the
-    GPU together ask for more than the memory delivers in that time, its share of the bandwidth;
-    the GPU holds about six one-warp blocks or three four-warp blocks per SM at a time. The plan
-    is the chunk (a multiple of 64 keys, 128 to 1024) and warp count with the smallest rounds x
-    (fixed + tiles per warp) x tile time; on a tie the larger chunk (fewer partials to merge)
-    and the single warp. Measured at 4,096 positions this picks within 5 % of the best chunk
-    from batch 1 to 64. Both arguments are rounded up to powers of two first, so a step takes
-    the same plan whether it runs on its own or from a captured graph (which is sized for such
-    bounds)."""
-    def pow2(n: int) -> int:
-        return 1 << max(n - 1, 0).bit_length()
-    pairs, longest = pow2(max(pairs, 1)), pow2(max(longest, 1))
-    best, best_cost = (DECODE_CHUNK, 1), None
-    for warps, per_sm, fixed in ((4, 3, 4.5), (1, 6, 4.0)):
-        for chunk in range(DECODE_CHUNK, 1024 + 1, 64):
-            blocks = pairs * -(-longest // chunk)
-            tile_us = max(1.2, min(blocks, per_sm * sms) * warps * 16384 / 6.65e6)
-            cost = -(-blocks // (per_sm * sms)) * (fixed + -(-(chunk // 32) // warps)) * tile_us
-            if best_cost is None or cost <= best_cost * (1 + 1e-9):
-                best, best_cost = (chunk, warps), cost
+def width_bucket(pages: int) -> int:
+    """`pages` (of the longest block table of a step) rounded up to three significant bits, at
+    least 8: the widths that captured decode graphs are made for, and the bound that the decode
+    attention kernel's plan is made from, so that a step takes the same plan whether it runs on
+    its own or from a captured graph. Rounding to powers of two would be fewer graphs, but a
+    request just past 4,096 tokens would then run the grid of one of 8,192."""
+    pages = max(pages, 8)
+    step = 1 << max(pages.bit_length() - 3, 0)
+    return -(-pages // step) * step
+
+
+def decode_plan(requests: int, nkv: int, longest: int, sms: int = 148) -> tuple[int, int]:
+    """(keys per block, warps per block) of the decode attention kernel for `requests` requests
+    (rounded up to a power of two, as a captured graph's batch is) of `nkv` key/value heads whose
+    longest holds `longest` positions. A block of one warp walks its chunk's 32-key tiles one after
+    the other, a chain of memory round trips; the GPU holds six such blocks per SM at a time, and
+    measured inside whole decode steps the best plan is the one with the most blocks that still
+    run in one wave: enough loads in flight to fill the memory's bandwidth, short chains, and SMs
+    that all get their share. Where even the shortest chunk leaves most SMs without a block (a
+    batch of one or two), a block has four warps that take the chunk's tiles in turn (three such
+    blocks per SM). The cost of a plan, in tile times: waves x (4 for a block's start and its
+    partial result + tiles per warp) + a round trip of the merge per eight chunks; the plan is the
+    cheapest chunk (a multiple of 64 keys, 128 to 1024), the shorter on a tie. At 4,096 positions
+    its pick was the best of the plans tried at batches 1, 2, 4, 8 and 16."""
+    pairs = (1 << max(requests - 1, 0).bit_length()) * max(nkv, 1)
+    longest = max(longest, 1)
+    warps, per_sm = (4, 3) if pairs * -(-longest // DECODE_CHUNK) < 4.5 * sms else (1, 6)
+    best, best_cost = (DECODE_CHUNK, warps), None
+    for chunk in range(DECODE_CHUNK, 1024 + 1, 64):
+        chunks = -(-longest // chunk)
+        waves = -(-pairs * chunks // (per_sm * sms))
+        cost = waves * (4 + -(-(chunk // 32) // warps)) + -(-chunks // 8)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = (chunk, warps), cost
     return best
-
-
-def decode_chunk(pairs: int, longest: int, sms: int = 148) -> int:
-    """The chunk of `decode_plan`."""
-    return decode_plan(pairs, longest, sms)[0]
 
 
 def tiled_attention_supported(dtype: torch.dtype, nq: int, nkv: int, d: int) -> bool:
@@ -314,6 +318,9 @@ class Projection:
     inv_freq: torch.Tensor | None
 
 
+DECODE_SPREAD = True
+"""The decode attention kernel's blocks ask for enough shared memory that they spread over all SMs."""
+
 USE_FUSED_DECODE = True
 """Decode-only steps leave QK-norm, rotation and the cache write to the attention kernel."""
 
@@ -367,7 +374,8 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
     single, longest = (None, step.max_seq_len) if step.decode_only else _single_token_requests(step, q.device)
     if step.decode_only or single is not None:
         count = step.num_seqs if step.decode_only else single.shape[0]
-        chunk, warps = decode_plan(count * nkv, longest)
+        longest = width_bucket(-(-longest // kv.page_size)) * kv.page_size
+        chunk, warps = decode_plan(count, nkv, longest)
         max_chunks = -(-longest // chunk)
         part_o, part_ml, tickets = _step_buffers(step, q.device, {
             "attention_part_o": (count * nq * max_chunks * d, torch.float32, False),
@@ -377,7 +385,7 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
                        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                         c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_float, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
-                        c_void_p, c_void_p], defines)
+                        c_int, c_void_p, c_void_p], defines)
         p = projection
         fused = (None, 0, 0, 0, 0, -1.0, None, None) if p is None else (
             _ptr(p.rows), p.rows.shape[1], p.q_col, p.k_col, p.v_col, -1.0 if p.eps is None else p.eps,
@@ -385,7 +393,7 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
         _check(fn(None if p is not None else _ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens),
                   _ptr(step.seq_lens), _ptr(single), count, _ptr(part_o), _ptr(part_ml), _ptr(tickets), chunk,
                   max_chunks, gate_ptr, gate_stride, _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size,
-                  kv.window or 0, scale, warps, *fused, err, _stream()), "attention_decode")
+                  kv.window or 0, scale, warps, *fused, int(DECODE_SPREAD), err, _stream()), "attention_decode")
         if step.decode_only or all(n == 1 for n in step.q_lens):
             return out
     if USE_TCGEN05 and tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):
@@ -536,11 +544,89 @@ def _library_mm(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return torch.mm(a, weight.t())
 
 
-def linear(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+USE_PENDING_STEP = True
+"""A decode step's residual updates run inside the product that takes their result."""
+
+PENDING_MAX_ROWS = 8
+PENDING_MAX_WIDTH = 2048
+"""The most rows and the widest residual stream whose pending step the weight-streaming kernel runs itself."""
+
+
+@dataclass
+class PendingStep:
+    """A residual step that has not run yet: x_new = x + norm_b(branch), h = norm_o(x_new). The
+    product that takes h (`linear`, `linear_swiglu`) runs it in its own kernel where it can, and
+    anything else settles it first with `settle`. Either way `x_new` then holds the new residual
+    (a buffer of its own when a product ran the step, since a kernel whose blocks all read x
+    cannot update it in place; x itself otherwise)."""
+
+    x: torch.Tensor
+    branch: torch.Tensor
+    branch_weight: torch.Tensor | None
+    branch_eps: float | None
+    out_weight: torch.Tensor | None
+    out_eps: float
+    x_new: torch.Tensor | None = None
+    h: torch.Tensor | None = None
+
+
+def pending_supported(x: torch.Tensor, branch: torch.Tensor) -> bool:
+    """Whether a product of this step's rows could run the residual step itself."""
+    return (USE_PENDING_STEP and USE_GEMV_STREAM and x.is_cuda and branch.dtype == torch.bfloat16
+            and 0 < x.shape[0] <= PENDING_MAX_ROWS and x.shape[1] % 8 == 0 and x.shape[1] <= PENDING_MAX_WIDTH
+            and x.is_contiguous() and branch.is_contiguous())
+
+
+def settle(h):
+    """The activations of `h`; a pending step is run now, by the kernel of its own."""
+    if not isinstance(h, PendingStep):
+        return h
+    if h.x_new is None:
+        h.h = add_rmsnorm(h.x, h.branch, h.branch_weight, h.branch_eps, h.out_weight, h.out_eps)
+        h.x_new = h.x
+    if h.h is None:
+        raise RuntimeError("a pending residual step was already consumed by a product; its activations were not kept")
+    return h.h
+
+
+def residual_after(h, x: torch.Tensor) -> torch.Tensor:
+    """The residual stream after whatever took `h` has run: `x` itself, or the new residual of a
+    pending step (settled now if nothing took it)."""
+    if not isinstance(h, PendingStep):
+        return x
+    if h.x_new is None:
+        settle(h)
+    return h.x_new
+
+
+def _pending_product(step: PendingStep, weight: torch.Tensor, epilogue: int) -> torch.Tensor | None:
+    """The product with the pending step in front, or None where the kernel does not take it."""
+    if step.x_new is not None or not (weight.dtype == torch.bfloat16 and weight.shape[1] == step.x.shape[1]
+                                      and weight.data_ptr() % 16 == 0 and pending_supported(step.x, step.branch)):
+        return None
+    rows, n = step.x.shape[0], weight.shape[0]
+    out = torch.empty(rows, n // 2 if epilogue == 1 else n, dtype=torch.bfloat16, device=step.x.device)
+    x_new = torch.empty_like(step.x)
+    fn = _function("gemv_stream", "omnia_gemv_stream_pending",
+                   [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_float, c_void_p, c_void_p,
+                    c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(step.x), _ptr(x_new), _ptr(step.branch), _ptr(step.branch_weight), step.branch_eps or 0.0,
+              int(step.branch_eps is not None), _ptr(step.out_weight), step.out_eps, _ptr(weight), _ptr(out), rows, n,
+              weight.shape[1], epilogue, _ptr(error_word(step.x.device)), _stream()), "gemv_stream_pending")
+    step.x_new = x_new
+    return out
+
+
+def linear(a, weight: torch.Tensor) -> torch.Tensor:
     """a [rows, k] times weight [n, k] transposed -> [rows, n], float32 accumulation.
     A few bfloat16 rows (a decode step) run on this package's weight-streaming kernel.
     Otherwise the matrix product is the vendor library's (as the reference's is MLX's);
-    on the 32-bit path it runs without any reduced-precision mode."""
+    on the 32-bit path it runs without any reduced-precision mode. `a` may be a PendingStep."""
+    if isinstance(a, PendingStep):
+        out = _pending_product(a, weight, 0)
+        if out is not None:
+            return out
+        a = settle(a)
     if _skinny(a, weight):
         out = torch.empty(a.shape[0], weight.shape[0], dtype=a.dtype, device=a.device)
         return _small_product(a, weight, out, 0)
@@ -550,8 +636,14 @@ def linear(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return _library_mm(a, weight)
 
 
-def linear_swiglu(a: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
-    """silu(a @ gate^T) * (a @ up^T) with gate_up = [gate rows | up rows] -> [rows, inner]."""
+def linear_swiglu(a, gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(a @ gate^T) * (a @ up^T) with gate_up = [gate rows | up rows] -> [rows, inner].
+    `a` may be a PendingStep."""
+    if isinstance(a, PendingStep):
+        out = _pending_product(a, gate_up, 1)
+        if out is not None:
+            return out
+        a = settle(a)
     if _skinny(a, gate_up):
         out = torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device)
         return _small_product(a, gate_up, out, 1)

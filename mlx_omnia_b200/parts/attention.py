@@ -29,6 +29,7 @@ class GQAAttention(Mixer):
     """
 
     graph_safe = True  # no host-side work per request: a decode step can be captured
+    takes_pending = True  # h goes to the in-projection and nowhere else
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, scale: float,
                  window: int | None = None, qk_norm_eps: float | None = None, gated: bool = False,

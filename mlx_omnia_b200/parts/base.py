@@ -17,6 +17,9 @@ Mixer additionally:
     ``state_spec() -> StateSpec | None``        fixed-size state it keeps per request
     ``forward(h, ctx: LayerContext) -> branch`` h, branch: [tokens, hidden] engine dtype
 FeedForward:  ``forward(h, ctx) -> branch``
+              A mixer or feed-forward whose `forward` gives `h` to one ``ops.linear`` or
+              ``ops.linear_swiglu`` and to nothing else may set ``takes_pending = True``; `h` can
+              then be an ``ops.PendingStep`` (a residual step that product runs in its own kernel).
 Norm:         ``forward(x) -> h`` and the attributes ``weight``, ``eps`` that the
               fused residual kernel reads (``weight is None`` means weightless)
 Position:     ``table() -> float32[rotary_dims / 2] | None`` of inverse frequencies
@@ -83,6 +86,10 @@ class Part:
 
 
 class Mixer(Part):
+    takes_pending = False
+    """True when `forward` hands `h` straight to `ops.linear` or `ops.linear_swiglu` and uses it
+    nowhere else: `h` may then be an `ops.PendingStep`, which that product runs in its own kernel."""
+
     def kv_spec(self) -> KVSpec | None:
         return None
 
@@ -94,6 +101,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_pending = False  # as for a Mixer
+
     def forward(self, h: torch.Tensor, ctx: "LayerContext") -> torch.Tensor:  # pragma: no cover
         raise NotImplementedError
 
@@ -231,3 +240,4 @@ class LayerContext:
     kv: KVView | None
     state: torch.Tensor | None  # [num_slots, *StateSpec.shape]
     entry: int
+    exit_may_pend: bool = False  # whatever takes this entry's h takes a pending residual step too

@@ -4,6 +4,10 @@ The residual stream `x` is float32 [tokens, hidden] and is updated in place. A b
 is handed `h`, its own entry norm already applied to `x` (the previous block's last
 kernel produced it), and the norm that whatever runs next wants applied on the way
 out, so each residual update is one fused pass: add the (normed) branch, then norm.
+In a step of few rows that pass need not be a kernel of its own: where the part that
+takes its result says `takes_pending`, the block hands it an `ops.PendingStep` instead
+of `h`, the part's first product runs the step in front of itself, and the block then
+picks up the new residual with `ops.residual_after`.
 
 Reference: sandwich arrangement x + post(attn(input_ln(x))), then + post(mlp(pre_ff(.)))
 (src/mlx_omnia/engine/models/muse_glimmer/layers/block.py:11-26).
@@ -19,11 +23,17 @@ from mlx_omnia_b200.parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Blo
 from mlx_omnia_b200.parts.norms import RMSNorm
 
 
-def residual_step(x: torch.Tensor, branch: torch.Tensor, branch_norm: Norm | None, out_norm: Norm | None):
+def residual_step(x: torch.Tensor, branch: torch.Tensor, branch_norm: Norm | None, out_norm: Norm | None,
+                  may_pend: bool = False):
     """x += branch_norm(branch); return out_norm(x) (None without an out_norm).
-    RMS norms take the fused kernel; any other norm class is applied by its own forward."""
+    RMS norms take the fused kernel; any other norm class is applied by its own forward.
+    With `may_pend` (whoever takes the result says it `takes_pending`) a step of few rows is
+    not run here but handed on as an `ops.PendingStep`, for the taker's first product to run."""
     fused_b = branch_norm is None or isinstance(branch_norm, RMSNorm)
     fused_o = out_norm is None or isinstance(out_norm, RMSNorm)
+    if may_pend and fused_b and fused_o and out_norm is not None and ops.pending_supported(x, branch):
+        return ops.PendingStep(x, branch, None if branch_norm is None else branch_norm.weight,
+                               None if branch_norm is None else branch_norm.eps, out_norm.weight, out_norm.eps)
     if not fused_b:
         branch = branch_norm.forward(branch.float())
         branch_norm = None
@@ -51,6 +61,11 @@ class _TwoBranchBlock(Block):
         self.mixer_name, self.feed_forward_name = mixer_name, feed_forward_name
         self.entry_norm = self.norms[self.norm_names[0]]
 
+    def _mix(self, h, ctx):
+        """The mixer's branch; `h` may be the block before's pending step, which a mixer that does
+        not take such gets settled."""
+        return self.mixer.forward(h if getattr(self.mixer, "takes_pending", False) else ops.settle(h), ctx)
+
     def children(self):
         yield self.mixer_name, self.mixer
         yield self.feed_forward_name, self.feed_forward
@@ -75,10 +90,13 @@ class SandwichBlock(_TwoBranchBlock):
 
     def forward(self, x, h, ctx, exit_norm):
         n = self.norms
-        a = self.mixer.forward(h, ctx)
-        h2 = residual_step(x, a, n["post_attention_layernorm"], n["pre_feedforward_layernorm"])
+        a = self._mix(h, ctx)
+        x = ops.residual_after(h, x)
+        h2 = residual_step(x, a, n["post_attention_layernorm"], n["pre_feedforward_layernorm"],
+                           getattr(self.feed_forward, "takes_pending", False))
         m = self.feed_forward.forward(h2, ctx)
-        return x, residual_step(x, m, n["post_feedforward_layernorm"], exit_norm)
+        x = ops.residual_after(h2, x)
+        return x, residual_step(x, m, n["post_feedforward_layernorm"], exit_norm, ctx.exit_may_pend)
 
 
 @register_block("pre_norm")
@@ -88,7 +106,10 @@ class PreNormBlock(_TwoBranchBlock):
     norm_names = ("input_layernorm", "post_attention_layernorm")
 
     def forward(self, x, h, ctx, exit_norm):
-        a = self.mixer.forward(h, ctx)
-        h2 = residual_step(x, a, None, self.norms["post_attention_layernorm"])
+        a = self._mix(h, ctx)
+        x = ops.residual_after(h, x)
+        h2 = residual_step(x, a, None, self.norms["post_attention_layernorm"],
+                           getattr(self.feed_forward, "takes_pending", False))
         m = self.feed_forward.forward(h2, ctx)
-        return x, residual_step(x, m, None, exit_norm)
+        x = ops.residual_after(h2, x)
+        return x, residual_step(x, m, None, exit_norm, ctx.exit_may_pend)

@@ -20,6 +20,8 @@ class GatedMLP(FeedForward):
     one [2 * inner, hidden] operand at load so the step runs one product for both.
     """
 
+    takes_pending = True
+
     def __init__(self, hidden: int, inner: int) -> None:
         self.hidden, self.inner = hidden, inner
 

@@ -115,7 +115,9 @@ class DecoderModel:
         x = self.embedding.forward(step.token_ids)
         h = self.blocks[schedule[0].layer].entry_norm.forward(x)
         for e, entry in enumerate(schedule):
-            following = self.blocks[schedule[e + 1].layer].entry_norm if e + 1 < len(schedule) else self.final_norm
+            after = self.blocks[schedule[e + 1].layer] if e + 1 < len(schedule) else None
+            following = after.entry_norm if after is not None else self.final_norm
+            layers[e].exit_may_pend = after is not None and getattr(after.mixer, "takes_pending", False)
             x, h = self.blocks[entry.layer].forward(x, h, layers[e], following)
         if step.logit_rows.shape[0] == 0:
             return torch.empty(0, self.head.vocab, dtype=torch.float32, device=x.device)

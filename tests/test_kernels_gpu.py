@@ -282,6 +282,44 @@ def test_skinny_products(ops, kernel, m, n, k):
     ops.raise_on_error(a.device)
 
 
+@pytest.mark.parametrize("m", [1, 3, 5, 8])
+@pytest.mark.parametrize("n,k", [(6144, 2048), (3072, 2048), (1000, 520), (600, 264), (48, 8)])
+def test_product_runs_a_pending_residual_step(ops, m, n, k):
+    """The ring-fed kernel with a residual step in front (x_new = x + norm(branch), h = norm(x_new),
+    out = h w^T) against the residual kernel's reference followed by a float64 product; with and
+    without weights and branch norm; the old residual stays as it was."""
+    x = rand(m, k, scale=2.0, seed=m + k)
+    branch = rand(m, k, dtype=torch.bfloat16, scale=0.7, seed=n)
+    w = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=n + k)
+    wb, wo = 1 + rand(k, scale=0.1, seed=4), 1 + rand(k, scale=0.1, seed=5)
+    for args in [(wb, 1e-6, wo, 1e-5), (None, None, wo, 1e-5), (wb, 1e-6, None, 1e-6), (None, 1e-6, None, 1e-5)]:
+        for gated in (False, True):
+            kept, x_ref = x.clone(), x.clone()
+            step = ops.PendingStep(kept, branch, *args)
+            assert ops.pending_supported(kept, branch)
+            got = ops.linear_swiglu(step, w) if gated else ops.linear(step, w)
+            h = kernel_refs.add_rmsnorm(x_ref, branch, *args)
+            z = (h.double() @ w.double().t()).float().bfloat16().double()
+            want = z[:, : n // 2] * torch.sigmoid(z[:, : n // 2]) * z[:, n // 2:] if gated else z
+            assert step.x_new is not None and step.x_new.data_ptr() != kept.data_ptr() and step.h is None
+            assert torch.equal(kept, x)
+            close(step.x_new, x_ref, torch.float32)
+            close(got, want, torch.bfloat16)
+            assert ops.residual_after(step, kept) is step.x_new
+    # Wider than the kernel holds in registers: the step is settled by its own kernel, in place.
+    wide = ops.PENDING_MAX_WIDTH + 64
+    x, branch = rand(2, wide, seed=1), rand(2, wide, dtype=torch.bfloat16, seed=2)
+    assert not ops.pending_supported(x, branch)
+    step = ops.PendingStep(x, branch, None, 1e-6, None, 1e-6)
+    w = rand(40, wide, dtype=torch.bfloat16, scale=0.05, seed=3)
+    x_ref = x.clone()
+    h = kernel_refs.add_rmsnorm(x_ref, branch, None, 1e-6, None, 1e-6)
+    close(ops.linear(step, w), h.double() @ w.double().t(), torch.bfloat16)
+    assert step.x_new is x
+    close(x, x_ref, torch.float32)
+    ops.raise_on_error(x.device)
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 128, 128), (129, 1000, 96), (200, 300, 136), (300, 778, 160),
                                    (2048, 2048, 2048), (1000, 6144, 2048), (260, 2048, 6144), (130, 12288, 512),
                                    (2048, 6144, 2048), (777, 1000, 520)])

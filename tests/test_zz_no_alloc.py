@@ -34,7 +34,7 @@ def test_static_scratch_entry_point_matches_the_allocating_one(monkeypatch):
 
     # The ordinary entry point picks its chunk and warps per block from the batch; held to the
     # chunk and the single warp that this test gives the static one, the two add in the same order.
-    monkeypatch.setattr(ops, "decode_plan", lambda pairs, longest, sms=148: (ops.DECODE_CHUNK, 1))
+    monkeypatch.setattr(ops, "decode_plan", lambda requests, nkv, longest, sms=148: (ops.DECODE_CHUNK, 1))
 
     device = torch.device("cuda:0")
     torch.cuda.set_device(device)
