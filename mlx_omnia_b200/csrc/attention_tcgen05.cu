@@ -80,6 +80,12 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait; false when the block is giving up (its own limit, or another role's).
+// 1 / (1 + e^-x) from the hardware's exponential and reciprocal (a few units in the last place of
+// float32, far below the bfloat16 the result is rounded to). The exact expf and division are some
+// forty instructions an element; unrolled over a row they made the epilogue a 5,000-instruction
+// stretch that every warp ran once, and the block spent 12 to 25 us fetching it.
+__device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
     if (mbar_try(bar, parity)) return true;
@@ -181,6 +187,7 @@ __device__ __forceinline__ void stamp(int slot) {
 // the request's tokens of this step, key/value head); the caller lists the longest blocks first.
 __global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                                 const __grid_constant__ CUtensorMap map_gate, int gate_tma,
                                  const int* __restrict__ block_table, const int* __restrict__ cu_seqlens,
                                  const int* __restrict__ seq_lens, const int* __restrict__ work,
                                  const bf16* __restrict__ gate, int gate_stride, bf16* __restrict__ out,
@@ -197,8 +204,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   unsigned char* p_s = q_s + Q_BYTES;
   unsigned char* kv_s = p_s + P_BYTES;  // KV_STAGES x (K, V)
   uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + KV_STAGES * STAGE_BYTES);
-  // bars: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11 p_full | 12 o_done
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 13);
+  // bars: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11 p_full | 12 o_done | 13 g_full
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   volatile uint32_t* group_mask = reinterpret_cast<volatile uint32_t*>(tmem_holder + 2);  // [KV_STAGES]
 
@@ -214,7 +221,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t q_full = bar0, k_full0 = bar0 + 8, k_empty0 = bar0 + 24, v_full0 = bar0 + 40,
-                 v_empty0 = bar0 + 56, s_full0 = bar0 + 72, p_full = bar0 + 88, o_done = bar0 + 96;
+                 v_empty0 = bar0 + 56, s_full0 = bar0 + 72, p_full = bar0 + 88, o_done = bar0 + 96, g_full = bar0 + 104;
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < KV_STAGES; ++s) {
@@ -226,6 +233,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     }
     mbar_init(p_full, 128);
     mbar_init(o_done, 1);
+    mbar_init(g_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -238,6 +246,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_holder;
+  // Everything so far needed nothing from the kernel before this one and ran while it finished
+  // (the launch is a programmatic dependent launch); from here on its results are read.
+  OMNIA_TRACE_BLOCK(2);
+  pdl_wait();
+  pdl_launch_dependents();
+  OMNIA_TRACE_BLOCK(3);
 
   if (warp == 0 || warp == 6) {
     // ---- producers: warp 0 loads Q once, then the K tiles; warp 6 the V tiles. Issuing a box keeps
@@ -373,12 +387,22 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const uint32_t lane_field = (uint32_t)(quarter * 32) << 16;
     const float sl2 = scale * LOG2E;
     float m = -INFINITY, l = 0.f;
-    bool ok = true;
+    bool ok = true, gate_issued = false;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int key0 = (tile0 + j) * BN;
       ok = mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (j == n_tiles - 1 && row == 0 && gate_tma) {
+        // The last scores are there, so Q has been read for the last time: the block's gate
+        // values (the same rows and columns as Q, of another matrix) take its place, on their
+        // way while the last softmax and product run.
+        mbar_expect_tx(g_full, DH * ROWS * 128);
+        for (int h = 0; h < DH; ++h)
+          tma_load_3d(smem_u32(q_s) + h * HALF_BYTES, &map_gate, g_full, h * 64, kvh * GROUP, q_begin + tok0);
+        gate_issued = true;
+      }
+      OMNIA_TRACE_IF(row == 0 && j == 0, 5);
       if (row == 0) STAMP(2, j, 0);
       const uint32_t s_addr = tmem_base + lane_field + S_COL + (j & 1) * BN;
       // Which keys of the tile this row sees; a tile that the whole warp sees whole needs no masks.
@@ -467,41 +491,74 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       mbar_arrive(p_full);
       if (row == 0) STAMP(2, j, 3);
     }
-    // Epilogue: O / l, gate, store.
+    // Epilogue: O / l, gate, store. A thread owns a row, so a warp's loads and stores go to 32
+    // different rows, each a trip to L2 of its own: read that way (two bytes at a time, then
+    // sixteen) the gate cost a block 30 and 13 us. It comes by TMA into Q's place instead (see the
+    // loop) and is read from shared memory, 16 bytes at a time, like everything stored.
+    OMNIA_TRACE_IF(row == 0, 6);
+    const size_t token = (size_t)(q_begin + tok0 + row / GROUP);
+    const int head = kvh * GROUP + row % GROUP;
+    const bf16* gp = gate ? gate + token * gate_stride + (size_t)head * D : nullptr;
+    const bool gate_wide = gp != nullptr && (reinterpret_cast<uintptr_t>(gp) & 15) == 0;
     if (ok) ok = mbar_wait(o_done, (n_tiles - 1) & 1, abort_flag);
+    if (ok && gate_tma) ok = mbar_wait(g_full, 0, abort_flag);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    OMNIA_TRACE_IF(row == 0, 7);
     if (ok) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      const size_t token = (size_t)(q_begin + tok0 + row / GROUP);
-      const int head = kvh * GROUP + row % GROUP;
       bf16* dst = out + (token * nq + head) * D;
-      const bf16* gp = gate ? gate + token * gate_stride + (size_t)head * D : nullptr;
 #pragma unroll 1
       for (int c = 0; c < D; c += 32) {
+        uint4 g4[4];
+        if (live && gate_tma) {
+          // Row `row` of the 64-dim half c / 64, 128 bytes a row, its 16-byte pieces swizzled by the row.
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int piece = (c % 64) / 8 + i;
+            g4[i] = *reinterpret_cast<const uint4*>(q_s + (c / 64) * HALF_BYTES + row * 128 + ((piece ^ (row & 7)) << 4));
+          }
+        } else if (live && gate_wide) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) g4[i] = __ldg(reinterpret_cast<const uint4*>(gp + c) + i);
+        }
         uint32_t v[32];
         tmem_load32(tmem_base + lane_field + O_COL + c, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (!live) continue;
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
+          const uint4 g = g4[i / 8];
+          const uint32_t g2[4] = {g.x, g.y, g.z, g.w};
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 8; e += 2) {
             float a = __uint_as_float(v[i + e]) * inv, b = __uint_as_float(v[i + e + 1]) * inv;
             if (gp) {
-              a *= 1.f / (1.f + expf(-__bfloat162float(gp[c + i + e])));
-              b *= 1.f / (1.f + expf(-__bfloat162float(gp[c + i + e + 1])));
+              float ga, gb;
+              if (gate_tma || gate_wide) {
+                const float2 pair = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g2[e / 2]));
+                ga = pair.x, gb = pair.y;
+              } else {
+                ga = __bfloat162float(gp[c + i + e]), gb = __bfloat162float(gp[c + i + e + 1]);
+              }
+              a *= fast_sigmoid(ga);
+              b *= fast_sigmoid(gb);
             }
             w[e / 2] = pack_bf16(a, b);
           }
           *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
+    } else if (gate_issued) {
+      // Giving up: the gate's copy must land before the block's shared memory goes away.
+      for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(g_full, 0); ++i) {
+      }
     }
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  OMNIA_TRACE_BLOCK(4);
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
   }
@@ -575,6 +632,19 @@ extern "C" int omnia_attention_prefill_tcgen05(const void* q, int tokens, const 
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return (int)cudaErrorInvalidValue;
   }
+  // The gate's rows as Q's are, in the matrix they are columns of; only if TMA can address them.
+  CUtensorMap map_gate = map_q;
+  const int gate_tma = gate != nullptr && ((uintptr_t)gate & 15) == 0 && gate_stride % 8 == 0 && gate_stride >= nq * D;
+  if (gate_tma) {
+    const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)nq, (cuuint64_t)tokens};
+    const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)gate_stride * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)GROUP, (cuuint32_t)TOKENS};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    if (encode(&map_gate, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(gate), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return (int)cudaErrorInvalidValue;
+  }
   constexpr size_t smem = Q_BYTES + P_BYTES + KV_STAGES * STAGE_BYTES + 256;
   static bool configured = false;
   if (!configured) {
@@ -583,8 +653,8 @@ extern "C" int omnia_attention_prefill_tcgen05(const void* q, int tokens, const 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  attention_prefill_tcgen05_kernel<<<blocks, THREADS, smem, stream>>>(
-      map_q, map_kv, block_table, cu_seqlens, seq_lens, work, (const bf16*)gate, gate_stride, (bf16*)out,
-      max_pages, num_pages, nq, nkv, page_size, window, scale, err);
+  launch_pdl(attention_prefill_tcgen05_kernel, blocks, THREADS, smem, stream,
+             map_q, map_kv, map_gate, gate_tma, block_table, cu_seqlens, seq_lens, work, (const bf16*)gate, gate_stride, (bf16*)out,
+             max_pages, num_pages, nq, nkv, page_size, window, scale, err);
   return OMNIA_LAUNCH_RESULT();
 }

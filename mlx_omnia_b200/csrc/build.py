@@ -28,10 +28,11 @@ BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "--shared", "-Xcompiler", "-fPIC
 
 _loaded: dict[str, ctypes.CDLL] = {}
 
-TIMELINE = bool(os.environ.get("OMNIA_TIMELINE"))
-"""With OMNIA_TIMELINE set in the environment every library is the tracing build (see common.cuh):
+TIMELINE = int(os.environ.get("OMNIA_TIMELINE") or 0)
+"""With OMNIA_TIMELINE=1 in the environment every library is the tracing build (see common.cuh):
 kernels stamp the GPU's clock around their wait for the kernel before them, and `timeline()` reads
-the marks. A tracing build is a library of its own beside the ordinary one."""
+the marks. With 2, the kernels that carry block traces (OMNIA_TRACE_BLOCK) stamp from every block
+as well. A tracing build is a library of its own beside the ordinary one."""
 
 
 class KernelBuildError(RuntimeError):
@@ -72,7 +73,7 @@ def _digest(source: Path, defines: dict[str, object], extra: list[str]) -> str:
 def _with_mode(defines: dict[str, object] | None) -> dict[str, object]:
     defines = dict(defines or {})
     if TIMELINE:
-        defines["OMNIA_TIMELINE"] = 1
+        defines["OMNIA_TIMELINE"] = TIMELINE
     return defines
 
 

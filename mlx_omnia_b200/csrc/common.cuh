@@ -76,6 +76,7 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 #ifndef OMNIA_TIMELINE
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 #define OMNIA_TRACE_BLOCK(phase) do { } while (0)
+#define OMNIA_TRACE_IF(condition, phase) do { } while (0)
 #else
 // Tracing build (-DOMNIA_TIMELINE): thread 0 of block (0, 0, 0) of every kernel stamps the GPU's
 // nanosecond clock when it reaches its wait and when the wait is over, i.e. when the kernel
@@ -100,8 +101,14 @@ __device__ __forceinline__ void timeline_stamp(unsigned tag) {
 __device__ __forceinline__ void timeline_mark(unsigned tag) {
   if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) timeline_stamp(tag);
 }
-// For looking inside one kernel: thread 0 of every block stamps (phases 2.. of the line's tag).
+// For looking inside one kernel (-DOMNIA_TIMELINE=2): thread 0 of every block stamps (phases 2 to 7).
+#if OMNIA_TIMELINE >= 2
 #define OMNIA_TRACE_BLOCK(phase) do { if (threadIdx.x == 0) timeline_stamp(8 * __LINE__ + (phase)); } while (0)
+#define OMNIA_TRACE_IF(condition, phase) do { if (condition) timeline_stamp(8 * __LINE__ + (phase)); } while (0)
+#else
+#define OMNIA_TRACE_BLOCK(phase) do { } while (0)
+#define OMNIA_TRACE_IF(condition, phase) do { } while (0)
+#endif
 __device__ __forceinline__ void pdl_wait_at(unsigned line) {
   timeline_mark(8 * line);
   asm volatile("griddepcontrol.wait;" ::: "memory");

@@ -161,6 +161,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_holder;
+  // Everything so far needed nothing from the kernel before this one and ran while it finished
+  // (the launch is a programmatic dependent launch); from here on its results are read.
+  pdl_wait();
+  pdl_launch_dependents();
 
   // Tiles are dealt round-robin; consecutive tiles share the same columns of the output (the
   // same rows of w), so blocks running side by side read the same weight tile out of L2.
@@ -378,8 +382,8 @@ int launch(const void* a, const void* w, void* out, int m, int n, int k, int pai
   }
   const long long total = (long long)n_tiles * m_tiles;
   const int grid = (int)(total < sm_count ? total : sm_count);  // one persistent block per SM
-  gemm_tcgen05_kernel<BLOCK_N, STAGES, EPI><<<grid, THREADS, smem, stream>>>(
-      map_a, map_b, out, m, n, k, pair_offset, multiplier, cap, m_tiles, n_tiles, err);
+  launch_pdl(gemm_tcgen05_kernel<BLOCK_N, STAGES, EPI>, grid, THREADS, smem, stream,
+             map_a, map_b, out, m, n, k, pair_offset, multiplier, cap, m_tiles, n_tiles, err);
   return OMNIA_LAUNCH_RESULT();
 }
 

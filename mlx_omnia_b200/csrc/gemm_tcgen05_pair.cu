@@ -192,6 +192,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_holder;
+  // Everything so far needed nothing from the kernel before this one and ran while it finished
+  // (the launch is a programmatic dependent launch); from here on its results are read.
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ---- producer (both blocks) -------------------------------------------------------------
@@ -399,8 +403,8 @@ int launch(const void* a, const void* w, void* out, int m, int n, int k, int pai
   }
   const long long total = (long long)n_tiles * m_tiles;
   const int clusters = (int)(total < sm_count / 2 ? total : sm_count / 2);  // one persistent block per SM
-  gemm_tcgen05_pair_kernel<EPI><<<2 * clusters, THREADS, smem, stream>>>(
-      map_a, map_b, out, m, n, k, pair_offset, multiplier, cap, m_tiles, n_tiles, err);
+  launch_pdl(gemm_tcgen05_pair_kernel<EPI>, 2 * clusters, THREADS, smem, stream,
+             map_a, map_b, out, m, n, k, pair_offset, multiplier, cap, m_tiles, n_tiles, err);
   return OMNIA_LAUNCH_RESULT();
 }
 
