@@ -193,6 +193,31 @@ def run(args) -> dict:
         return {"value": tokens * 1000.0 / ms, "tokens": tokens, "ms": ms,
                 "frac": flops / (ms / 1000.0) / (measured["bf16_tflops"] * 1e12), "flops": flops}
 
+    if args.timeline:
+        # One step of a tracing build, kernel by kernel as it runs (set OMNIA_TIMELINE=1): the lines
+        # go to stderr, the record says how many kernels were seen.
+        from mlx_omnia_b200.kernels import timeline
+        if args.only == "prefill":
+            prefill(args.prefill_tokens, 1, 2)
+            torch.cuda.synchronize()
+            timeline.spans()
+            prefill(args.prefill_tokens, 1, 0)
+            anchor = "attention_tcgen05"
+        else:
+            length = args.context - 16
+            generator = Generator(engine, max_tokens_per_step=args.batch * length)
+            for p in prompts(args.batch, length):
+                generator.add(p, GenerationOptions(max_tokens=12, stop=()))
+            for _ in range(6):
+                generator.step()
+            torch.cuda.synchronize()
+            timeline.spans()
+            generator.step()
+            anchor = "attention_tc"
+        torch.cuda.synchronize()
+        kernels = timeline.spans()
+        print("\n".join(timeline.by_layer(kernels, anchor)), file=sys.stderr)
+        return {"only": args.only, "timeline": True, "kernels": len(kernels), "layers": layers}
     if args.only == "decode":  # a small case for profilers: one batch size, no prefill timing
         part = decode(args.batch, args.steps, args.warmup)
         return {"only": "decode", "batch": args.batch, "layers": layers, "ms_per_step": round(part["ms"], 4),
@@ -245,6 +270,9 @@ def main() -> int:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="run fewer layers than configs[2] has (named in config)")
+    parser.add_argument("--timeline", action="store_true",
+                        help="with --only decode|prefill and OMNIA_TIMELINE=1 in the environment: one step's "
+                             "kernels with the time each takes in the stream, on stderr")
     parser.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                         help="time one part only (small cases for profilers); prints a short record")
     parser.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds at the last timed step")

@@ -31,3 +31,16 @@ def test_decode_plan_grows_with_the_work():
     assert ops.decode_plan(8, 8, 5120) == (448, 1)
     assert ops.decode_plan(16, 8, 4096) == (704, 1)
     assert ops.decode_plan(64, 8, 8192) == (1024, 1)
+
+
+def test_timeline_groups_a_step_s_kernels_by_their_place_in_a_layer():
+    from mlx_omnia_b200.kernels import timeline
+
+    layer = [("gemv", 7, 10.0), ("attention", 9, 27.0), ("gemv", 7, 3.0), ("gemv", 7, 12.0), ("gemv", 7, 6.0)]
+    kernels = [("elementwise", 1, 5.0), ("elementwise", 2, 6.0)] + layer * 4 + [("elementwise", 3, 2.0)]
+    lines = timeline.by_layer(kernels, "attention")
+    assert len(lines) == 2 + 5 + 1 + 1
+    assert lines[0].startswith("before the layers") and lines[-1].startswith("after the layers")
+    assert "attention:9" in lines[3] and "27.00 us" in lines[3] and "4 layers" in lines[3]
+    assert lines[7].split()[2] == "58.00"
+    assert timeline.by_layer(layer, "attention") == [f"{lib}:{line} {us:8.2f} us" for lib, line, us in layer]

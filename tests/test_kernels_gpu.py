@@ -400,3 +400,33 @@ def test_sampling_keeps_exactly_the_filtered_set(ops):
         seen |= set(got.tolist())
     allowed = set(torch.nonzero(keep).flatten().tolist())
     assert seen <= allowed and len(seen) >= min(len(allowed), 3)
+
+
+def test_tracing_build_marks_every_kernel_s_wait():
+    """With OMNIA_TIMELINE=1 the libraries are built with clock stamps around each kernel's wait
+    for the kernel before it: three launches leave three pairs of marks, in order, the second of
+    a pair no earlier than the first, and reading the marks empties them."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    script = """
+import torch
+from mlx_omnia_b200.csrc import build
+from mlx_omnia_b200.kernels import ops
+x = torch.randn(5, 256, device="cuda")
+for _ in range(3):
+    ops.rmsnorm(x, None, 1e-6, torch.bfloat16)
+torch.cuda.synchronize()
+marks = build.timeline()
+assert [m[3] for m in marks if m[1] == "elementwise"] == [0, 1] * 3, marks
+times = [m[0] for m in marks]
+assert times == sorted(times) and len({m[2] for m in marks}) == 1
+assert build.timeline() == []
+print("marks ok")
+"""
+    root = Path(__file__).resolve().parent.parent
+    env = dict(os.environ, OMNIA_TIMELINE="1", PYTHONPATH=str(root))
+    done = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=env, timeout=600)
+    assert done.returncode == 0 and "marks ok" in done.stdout, done.stderr[-2000:]
