@@ -236,9 +236,34 @@ def tiled_attention_supported(dtype: torch.dtype, nq: int, nkv: int, d: int) -> 
     return dtype == torch.bfloat16 and d % 8 == 0 and d <= 256 and nq % nkv == 0 and nq // nkv <= 16
 
 
-# The small index lists below go to the device from ordinary host memory: the driver stages a few
-# kilobytes in microseconds, where pinning a fresh buffer for every list cost a prefill step 0.15 ms
-# with the GPU idle.
+# The small index lists below go to the device through a ring of pinned slots that is made once:
+# pinning a fresh buffer for every list cost a prefill step 0.15 ms with the GPU idle.
+_STAGING_SLOTS, _STAGING_INTS = 16, 16384
+_staging: dict[int, list] = {}
+
+
+def _ints_to_device(values: list, device: torch.device) -> torch.Tensor:
+    """`values` (ints, possibly nested evenly) as an int32 tensor on `device`, copied without
+    blocking from a pinned slot; a slot is written again only after its last copy has finished."""
+    host = torch.tensor(values, dtype=torch.int32)
+    if host.numel() > _STAGING_INTS:
+        return host.to(device, non_blocking=True)
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    ring = _staging.get(index)
+    if ring is None:
+        ring = _staging[index] = [torch.empty(_STAGING_SLOTS, _STAGING_INTS, dtype=torch.int32).pin_memory(),
+                                  [None] * _STAGING_SLOTS, 0]
+    slots, events, at = ring
+    ring[2] = (at + 1) % _STAGING_SLOTS
+    if events[at] is not None:
+        events[at].synchronize()
+    else:
+        events[at] = torch.cuda.Event()
+    pinned = slots[at, : host.numel()].view(host.shape)
+    pinned.copy_(host)
+    out = pinned.to(device, non_blocking=True)
+    events[at].record()
+    return out
 
 
 def _prefill_work(step: StepContext, tokens_per_block: int, device: torch.device) -> torch.Tensor:
@@ -253,7 +278,7 @@ def _prefill_work(step: StepContext, tokens_per_block: int, device: torch.device
         items = [(s, t0) for s, n in enumerate(step.q_lens) if n > 1 for t0 in range(0, n, tokens_per_block)]
         if step.seq_lens_host:
             items.sort(key=lambda item: -(step.seq_lens_host[item[0]] - step.q_lens[item[0]] + item[1]))
-        work = torch.tensor(items, dtype=torch.int32).to(device, non_blocking=True)
+        work = _ints_to_device(items, device)
         step.workspace[key] = work
     return work
 
@@ -283,7 +308,7 @@ def _prefill_work_flat(step: StepContext, tokens_per_block: int, tile: int, nkv:
                     tiles = last // tile - first // tile + 1
                 items += [(tiles, s, t0, h) for h in range(nkv)]
         items.sort(key=lambda item: -item[0])
-        work = torch.tensor([item[1:] for item in items], dtype=torch.int32).to(device, non_blocking=True)
+        work = _ints_to_device([item[1:] for item in items], device)
         step.workspace[key] = work
     return work
 
@@ -297,7 +322,7 @@ def _single_token_requests(step: StepContext, device: torch.device) -> tuple[tor
     if held is None:
         ids = [s for s, n in enumerate(step.q_lens) if n == 1]
         longest = max((step.seq_lens_host[s] for s in ids), default=0)
-        tensor = torch.tensor(ids, dtype=torch.int32).to(device, non_blocking=True) if ids else None
+        tensor = _ints_to_device(ids, device) if ids else None
         held = step.workspace["single_token_requests"] = (tensor, longest)
     return held
 
