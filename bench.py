@@ -166,7 +166,7 @@ def run(args) -> dict:
         wall = time.perf_counter() - wall
         ms = start.elapsed_time(stop) / steps
         assert len(outputs) == batch
-        context = generator.scheduler.running[0].computed if generator.scheduler.running else CONTEXT
+        context = generator.scheduler.running[0].computed if generator.scheduler.running else args.context
         generator.run()
         return {"ms": ms, "tokens_per_s": batch * 1000.0 / ms, "wall_tokens_per_s": batch * steps / wall,
                 "launches": (ops.launches - launches) // steps, "context": context}
