@@ -211,20 +211,24 @@ def decode_plan(requests: int, nkv: int, longest: int, sms: int = 148) -> tuple[
     the other, a chain of memory round trips; the GPU holds six such blocks per SM at a time, and
     measured inside whole decode steps the best plan is the one with the most blocks that still
     run in one wave: enough loads in flight to fill the memory's bandwidth, short chains, and SMs
-    that all get their share. Where even the shortest chunk leaves most SMs without a block (a
-    batch of one or two), a block has four warps that take the chunk's tiles in turn (three such
-    blocks per SM). The cost of a plan, in tile times: waves x (4 for a block's start and its
-    partial result + tiles per warp) + a round trip of the merge per eight chunks; the plan is the
-    cheapest chunk (a multiple of 64 keys, 128 to 1024), the shorter on a tie. At 4,096 positions
-    its pick was the best of the plans tried at batches 1, 2, 4, 8 and 16."""
+    that all get their share. With one or two requests (at most an eighth as many (request, head)
+    pairs as SMs) a block has four warps that take the chunk's tiles in turn, without a ring (a
+    tile counts one and a half); such blocks ran well two to an SM and badly three to an SM. The
+    cost of a plan, in tile times: waves x (4 for a block's start and its partial result + tiles
+    per warp), for four-warp blocks divided by the share of the SMs' places that they fill, + a
+    round trip of the merge per eight chunks; the plan is the cheapest chunk (a multiple of 64 keys, 128 to 1024), the shorter
+    on a tie. Its pick was the best or within 2 % of the best of the plans tried at 4,096
+    positions (batches 1 to 16) and at 16,000 and 32,000 (batches 1 and 2)."""
     pairs = (1 << max(requests - 1, 0).bit_length()) * max(nkv, 1)
     longest = max(longest, 1)
-    warps, per_sm = (4, 3) if pairs * -(-longest // DECODE_CHUNK) < 4.5 * sms else (1, 6)
+    warps, per_sm, tile = (4, 2, 1.5) if pairs * 8 <= sms else (1, 6, 1.0)
     best, best_cost = (DECODE_CHUNK, warps), None
     for chunk in range(DECODE_CHUNK, 1024 + 1, 64):
         chunks = -(-longest // chunk)
-        waves = -(-pairs * chunks // (per_sm * sms))
-        cost = waves * (4 + -(-(chunk // 32) // warps)) + -(-chunks // 8)
+        blocks = pairs * chunks
+        waves = -(-blocks // (per_sm * sms))
+        filled = blocks / (min(per_sm, -(-blocks // sms)) * sms) if waves == 1 and warps == 4 else 1.0
+        cost = waves * (4 + tile * -(-(chunk // 32) // warps)) / filled + -(-chunks // 8)
         if best_cost is None or cost < best_cost:
             best, best_cost = (chunk, warps), cost
     return best

@@ -31,6 +31,9 @@ def test_decode_plan_grows_with_the_work():
     assert ops.decode_plan(8, 8, 5120) == (448, 1)
     assert ops.decode_plan(16, 8, 4096) == (704, 1)
     assert ops.decode_plan(64, 8, 8192) == (1024, 1)
+    # One long request: four warps a block, chunks so long that two blocks an SM hold them all.
+    chunk, warps = ops.decode_plan(1, 8, 32768)
+    assert warps == 4 and 8 * -(-32768 // chunk) <= 2 * 148
 
 
 def test_timeline_groups_a_step_s_kernels_by_their_place_in_a_layer():
