@@ -66,6 +66,8 @@ class _Launched:
     plan: StepPlan
     sampling: list[Request]
     chosen: torch.Tensor | None
+    host_tokens: torch.Tensor | None = None  # pinned copy of `chosen`, on its way since the launch
+    copied: "torch.cuda.Event | None" = None  # recorded behind that copy
 
 
 class Generator:
@@ -77,6 +79,8 @@ class Generator:
         self._ids = itertools.count()
         self._seeds: dict[str, int] = {}
         self._in_flight: _Launched | None = None
+        self._token_slots: list[torch.Tensor] = []  # pinned buffers the chosen tokens come back in, used in turn
+        self._token_slot = 0
         self.pipelined = True  # launch the next decode step before reading this one's tokens
 
     def add(self, prompt: Sequence[int], options: GenerationOptions, request_id: str | None = None) -> Request:
@@ -131,12 +135,29 @@ class Generator:
                          for r in sampling]
             chosen = sample_rows(logits, [r.sampling for r in sampling], [self._seeds[r.request_id] for r in sampling],
                                  [len(r.generated) + ahead for r in sampling], histories)
-        return _Launched(plan, sampling, chosen)
+        launched = _Launched(plan, sampling, chosen)
+        if chosen is not None and chosen.is_cuda:
+            # The tokens start for the host at once, behind this step only. Read with a blocking copy
+            # when the host wants them, they would come behind everything launched since, the
+            # next step included, and the host would prepare the step after that with the GPU idle.
+            if not self._token_slots or self._token_slots[0].numel() < chosen.numel():
+                self._token_slots = [torch.empty(max(64, chosen.numel()), dtype=torch.int32).pin_memory()
+                                     for _ in range(4)]
+            self._token_slot = (self._token_slot + 1) % len(self._token_slots)
+            launched.host_tokens = self._token_slots[self._token_slot][: chosen.numel()]
+            launched.host_tokens.copy_(chosen, non_blocking=True)
+            launched.copied = torch.cuda.Event()
+            launched.copied.record()
+        return launched
 
     def _finalize(self, launched: "_Launched") -> list[StepOutput]:
         """Read the launched step's tokens (this waits for it) and commit them."""
         plan = launched.plan
-        tokens = launched.chosen.tolist() if launched.chosen is not None else []
+        if launched.copied is not None:
+            launched.copied.synchronize()
+            tokens = launched.host_tokens.tolist()
+        else:
+            tokens = launched.chosen.tolist() if launched.chosen is not None else []
         sampled = dict(zip((r.request_id for r in launched.sampling), tokens))
         # A request that ended (a stop token, an abort) after this step was launched is left out.
         live = [e for e in plan.entries if e.request.status == "running"]
