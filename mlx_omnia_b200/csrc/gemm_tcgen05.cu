@@ -258,7 +258,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 // Both halves are rounded to bfloat16 first, as a separate product would round them.
                 const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gate[j + e])));
                 const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[j + e])));
-                v[e] = g / (1.f + __expf(-g)) * u;
+                v[e] = __fdividef(g, 1.f + __expf(-g)) * u;
               }
               const int col = n0 + c + j;
               if (col + 1 < pair_offset && (pair_offset & 1) == 0) {

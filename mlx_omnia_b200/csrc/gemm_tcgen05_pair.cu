@@ -100,11 +100,13 @@ __device__ __forceinline__ void tmem_load32(uint32_t addr, uint32_t* v) {
 
 
 constexpr int STAGES = 6;
-constexpr uint32_t HALF_N = 128;                                    // rows of w a block stages
-constexpr uint32_t TILE_N = 256;                                    // columns of the accumulator
+// The accumulator's columns, TILE_N, are 256 or 192 (a template parameter): the narrower tile is for
+// shapes whose 256-wide tiles leave the last wave of clusters mostly idle (12,288 columns of
+// gate|up at 2,048 rows: 384 tiles on 74 clusters are six waves, the last with 14 tiles; 512 tiles of
+// 192 are seven waves of three quarters the length). Each block stages TILE_N / 2 rows of w.
 constexpr uint32_t A_BYTES = BLOCK_M * BLOCK_K * sizeof(bf16);
-constexpr uint32_t B_BYTES = HALF_N * BLOCK_K * sizeof(bf16);
-constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr uint32_t ACC_STRIDE = 256;                                // tensor-memory columns between the two accumulators
+constexpr uint32_t TMEM_COLS = 512;                                 // a power of two, as allocations must be
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -148,12 +150,16 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
 
 constexpr int ACC_BUFS = 2;                                         // the tile being multiplied, the tile being stored
 
-template <int EPI>
+template <int EPI, uint32_t TILE_N>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          void* __restrict__ out, int m, int n, int k, int pair_offset, float multiplier,
                          float cap, int m_tiles, int n_tiles, int* err) {
   constexpr int TILE_COLS = EPI == EPI_SWIGLU ? TILE_N / 2 : TILE_N;
+  constexpr uint32_t HALF_N = TILE_N / 2;                           // rows of w a block stages
+  constexpr uint32_t B_BYTES = HALF_N * BLOCK_K * sizeof(bf16);
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  static_assert(TILE_N % 32 == 0 && TILE_N <= ACC_STRIDE && STAGE_BYTES % 1024 == 0, "tile width");
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
@@ -185,7 +191,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
-                 "r"((uint32_t)(ACC_BUFS * TILE_N)));
+                 "r"(TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -228,7 +234,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         ok = mbar_wait(acc_empty0 + 8 * buf, (round & 1) ^ 1, abort_flag);  // both epilogues have drained it
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t acc = tmem_base + buf * TILE_N;
+        const uint32_t acc = tmem_base + buf * ACC_STRIDE;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1, abort_flag);
@@ -258,7 +264,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       ok = mbar_wait(acc_full0 + 8 * buf, round & 1, abort_flag);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t lane_base = tmem_base + buf * TILE_N + ((uint32_t)(quarter * 32) << 16);
+      const uint32_t lane_base = tmem_base + buf * ACC_STRIDE + ((uint32_t)(quarter * 32) << 16);
       if (EPI == EPI_SWIGLU) {
         bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)row * pair_offset + n0;
 #pragma unroll 1
@@ -276,7 +282,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 // Both halves are rounded to bfloat16 first, as a separate product would round them.
                 const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gate[j + e])));
                 const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[j + e])));
-                v[e] = g / (1.f + __expf(-g)) * u;
+                v[e] = __fdividef(g, 1.f + __expf(-g)) * u;
               }
               const int col = n0 + c + j;
               if (col + 1 < pair_offset && (pair_offset & 1) == 0) {
@@ -341,7 +347,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   cluster_sync_all();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(ACC_BUFS * TILE_N)));
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
   }
   if (threadIdx.x == 0 && *abort_flag) atomicOr(err, OMNIA_ERR_TIMEOUT);
 }
@@ -378,34 +384,61 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows)
 }
 
 
+int sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
+    if (count <= 0) count = 148;
+  }
+  return count;
+}
+
+// Tiles of the output for accumulators of `tile_n` columns.
 template <int EPI>
-int launch(const void* a, const void* w, void* out, int m, int n, int k, int pair_offset, float multiplier,
-           float cap, int* err, cudaStream_t stream) {
+long long tile_count(int m, int n, int pair_offset, int tile_n, int* m_tiles, int* n_tiles) {
+  const int cols = EPI == EPI_SWIGLU ? pair_offset : n;
+  const int tile_cols = EPI == EPI_SWIGLU ? tile_n / 2 : tile_n;
+  *n_tiles = (cols + tile_cols - 1) / tile_cols;
+  *m_tiles = (m + 2 * BLOCK_M - 1) / (2 * BLOCK_M);
+  return (long long)*n_tiles * *m_tiles;
+}
+
+template <int EPI, uint32_t TILE_N>
+int launch_width(const void* a, const void* w, void* out, int m, int n, int k, int pair_offset, float multiplier,
+                 float cap, int* err, cudaStream_t stream) {
+  constexpr uint32_t STAGE_BYTES = A_BYTES + (TILE_N / 2) * BLOCK_K * sizeof(bf16);
   CUtensorMap map_a, map_b;
-  if (!make_map(&map_a, a, m, k, BLOCK_M) || !make_map(&map_b, w, n, k, (int)HALF_N)) return (int)cudaErrorInvalidValue;
+  if (!make_map(&map_a, a, m, k, BLOCK_M) || !make_map(&map_b, w, n, k, (int)(TILE_N / 2)))
+    return (int)cudaErrorInvalidValue;
   constexpr size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<EPI>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<EPI, TILE_N>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int cols = EPI == EPI_SWIGLU ? pair_offset : n;
-  const int tile_cols = EPI == EPI_SWIGLU ? (int)TILE_N / 2 : (int)TILE_N;
-  const int n_tiles = (cols + tile_cols - 1) / tile_cols, m_tiles = (m + 2 * BLOCK_M - 1) / (2 * BLOCK_M);
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int device = 0;
-    cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-    if (sm_count <= 0) sm_count = 148;
-  }
-  const long long total = (long long)n_tiles * m_tiles;
-  const int clusters = (int)(total < sm_count / 2 ? total : sm_count / 2);  // one persistent block per SM
-  launch_pdl(gemm_tcgen05_pair_kernel<EPI>, 2 * clusters, THREADS, smem, stream,
+  int m_tiles, n_tiles;
+  const long long total = tile_count<EPI>(m, n, pair_offset, (int)TILE_N, &m_tiles, &n_tiles);
+  const int pairs = sm_count() / 2;
+  const int clusters = (int)(total < pairs ? total : pairs);  // one persistent block per SM
+  launch_pdl(gemm_tcgen05_pair_kernel<EPI, TILE_N>, 2 * clusters, THREADS, smem, stream,
              map_a, map_b, out, m, n, k, pair_offset, multiplier, cap, m_tiles, n_tiles, err);
   return OMNIA_LAUNCH_RESULT();
+}
+
+// The width whose waves of tiles take the least time: waves x width, 256 on a tie.
+template <int EPI>
+int launch(const void* a, const void* w, void* out, int m, int n, int k, int pair_offset, float multiplier,
+           float cap, int* err, cudaStream_t stream) {
+  const int pairs = sm_count() / 2;
+  int mt, nt;
+  const long long wide = (tile_count<EPI>(m, n, pair_offset, 256, &mt, &nt) + pairs - 1) / pairs * 256;
+  const long long narrow = (tile_count<EPI>(m, n, pair_offset, 192, &mt, &nt) + pairs - 1) / pairs * 192;
+  if (narrow < wide) return launch_width<EPI, 192>(a, w, out, m, n, k, pair_offset, multiplier, cap, err, stream);
+  return launch_width<EPI, 256>(a, w, out, m, n, k, pair_offset, multiplier, cap, err, stream);
 }
 
 }  // namespace

@@ -322,7 +322,7 @@ def test_product_runs_a_pending_residual_step(ops, m, n, k):
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 128, 128), (129, 1000, 96), (200, 300, 136), (300, 778, 160),
                                    (2048, 2048, 2048), (1000, 6144, 2048), (260, 2048, 6144), (130, 12288, 512),
-                                   (2048, 6144, 2048), (777, 1000, 520)])
+                                   (2048, 6144, 2048), (777, 1000, 520), (2048, 12288, 2048)])
 @pytest.mark.parametrize("kernel", ["one_sm", "two_sm", "dispatch"])
 def test_tcgen05_products(ops, kernel, m, n, k):
     """The tcgen05/TMA kernels (one SM to a tile; two SMs to a tile, cta_group::2) and their
