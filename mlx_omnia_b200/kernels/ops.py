@@ -15,6 +15,7 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 
 from dataclasses import dataclass
 
+import numpy as np
 import torch
 
 from mlx_omnia_b200.csrc.build import load_library
@@ -246,10 +247,11 @@ _STAGING_SLOTS, _STAGING_INTS = 16, 16384
 _staging: dict[int, list] = {}
 
 
-def _ints_to_device(values: list, device: torch.device) -> torch.Tensor:
+def _ints_to_device(values, device: torch.device) -> torch.Tensor:
     """`values` (ints, possibly nested evenly) as an int32 tensor on `device`, copied without
     blocking from a pinned slot; a slot is written again only after its last copy has finished."""
-    host = torch.tensor(values, dtype=torch.int32)
+    host = torch.from_numpy(np.ascontiguousarray(values, dtype=np.int32)) if isinstance(values, np.ndarray) \
+        else torch.tensor(values, dtype=torch.int32)
     if host.numel() > _STAGING_INTS:
         return host.to(device, non_blocking=True)
     index = device.index if device.index is not None else torch.cuda.current_device()
@@ -299,20 +301,23 @@ def _prefill_work_flat(step: StepContext, tokens_per_block: int, tile: int, nkv:
     key = ("prefill_work_flat", tokens_per_block, tile, nkv, window)
     work = step.workspace.get(key)
     if work is None:
-        items = []
+        parts = []
         for s, n in enumerate(step.q_lens):
             if n <= 1:
                 continue
-            for t0 in range(0, n, tokens_per_block):
-                tiles = 0
-                if step.seq_lens_host:
-                    pos0 = step.seq_lens_host[s] - n + t0
-                    last = pos0 + min(tokens_per_block, n - t0) - 1
-                    first = max(0, pos0 - window + 1) if window else 0
-                    tiles = last // tile - first // tile + 1
-                items += [(tiles, s, t0, h) for h in range(nkv)]
-        items.sort(key=lambda item: -item[0])
-        work = _ints_to_device([item[1:] for item in items], device)
+            t0 = np.arange(0, n, tokens_per_block, dtype=np.int64)
+            tiles = np.zeros_like(t0)
+            if step.seq_lens_host:
+                pos0 = step.seq_lens_host[s] - n + t0
+                last = pos0 + np.minimum(tokens_per_block, n - t0) - 1
+                first = np.maximum(0, pos0 - window + 1) if window else np.zeros_like(t0)
+                tiles = last // tile - first // tile + 1
+            # Every block of tokens once per key/value head, heads innermost.
+            parts.append(np.stack([np.repeat(tiles, nkv), np.full(t0.size * nkv, s), np.repeat(t0, nkv),
+                                   np.tile(np.arange(nkv), t0.size)], axis=1))
+        table = np.concatenate(parts) if parts else np.zeros((0, 4), dtype=np.int64)
+        order = np.argsort(-table[:, 0], kind="stable")
+        work = _ints_to_device(table[order, 1:], device)
         step.workspace[key] = work
     return work
 
