@@ -47,3 +47,28 @@ def test_timeline_groups_a_step_s_kernels_by_their_place_in_a_layer():
     assert "attention:9" in lines[3] and "27.00 us" in lines[3] and "4 layers" in lines[3]
     assert lines[7].split()[2] == "58.00"
     assert timeline.by_layer(layer, "attention") == [f"{lib}:{line} {us:8.2f} us" for lib, line, us in layer]
+
+
+def test_a_pending_residual_step_is_settled_once_and_says_when_it_was_consumed(cpu_ops):
+    """Without a GPU no product runs a pending step itself (the blocks then make none): settling one
+    runs the residual kernel (here its plain reference) in place; asking again gives the same
+    activations; a step that a product consumed keeps no activations and says so."""
+    import pytest
+    import torch
+
+    import kernel_refs
+
+    ops = cpu_ops
+    x, branch = torch.randn(3, 16), torch.randn(3, 16).bfloat16()
+    wb, wo = torch.rand(16) + 0.5, torch.rand(16) + 0.5
+    expect_x = x.clone()
+    expect_h = kernel_refs.add_rmsnorm(expect_x, branch, wb, 1e-6, wo, 1e-5)
+    step = ops.PendingStep(x, branch, wb, 1e-6, wo, 1e-5)
+    assert not ops.pending_supported(x, branch)
+    assert torch.equal(ops.settle(step), expect_h)
+    assert step.x_new is x and torch.equal(x, expect_x) and ops.residual_after(step, torch.zeros(1)) is x
+    assert torch.equal(ops.settle(step), expect_h) and ops.settle(expect_h) is expect_h
+    assert ops.residual_after(expect_h, x) is x
+    consumed = ops.PendingStep(x, branch, wb, 1e-6, wo, 1e-5, x_new=torch.zeros_like(x))
+    with pytest.raises(RuntimeError, match="already consumed"):
+        ops.settle(consumed)
