@@ -12,7 +12,6 @@ The vision tower, the DFlash drafter and quantised files are outside this engine
 
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 from typing import Any
 

@@ -36,7 +36,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
-from mlx_omnia_b200.parts.base import KVSpec, StateSpec
+from mlx_omnia_b200.parts.base import KVSpec
 from mlx_omnia_b200.parts.model import CacheNeed
 
 

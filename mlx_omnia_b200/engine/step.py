@@ -45,12 +45,6 @@ class StepRunner:
                 self.graphs = DecodeGraphs(self)
 
     # -- metadata ----------------------------------------------------------------------
-    def _device(self, array: np.ndarray) -> torch.Tensor:
-        tensor = torch.from_numpy(array)
-        if self.runtime.device.type == "cuda":
-            return tensor.pin_memory().to(self.runtime.device, non_blocking=True)
-        return tensor.to(self.runtime.device)
-
     def build_context(self, entries: list[StepEntry]) -> StepContext:
         """Take the pages the entries' tokens need and lay the batch out."""
         cache, page = self.cache, self.cache.page_size

@@ -19,7 +19,6 @@ import sys
 from pathlib import Path
 from typing import IO
 
-import numpy as np
 
 from mlx_omnia_b200.engine.engine import Engine, EngineArgs
 from mlx_omnia_b200.engine.step import StepEntry

@@ -18,7 +18,7 @@ from __future__ import annotations
 import torch
 
 from mlx_omnia_b200.kernels import ops
-from mlx_omnia_b200.parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Norm, PartSpec, TensorSpec,
+from mlx_omnia_b200.parts.base import (FEED_FORWARDS, MIXERS, NORMS, Block, Norm, PartSpec, TensorSpec,
                                        register_block)
 from mlx_omnia_b200.parts.norms import RMSNorm
 
