@@ -254,7 +254,7 @@ def run(args) -> dict:
                    "kv_heads": text["num_key_value_heads"], "head_dim": text["head_dim"],
                    "intermediate": text["intermediate_size"], "vocab": vocab, "tied": True, "global_batch": args.batch,
                    "seq_len": args.context, "context_at_timed_steps": main["context"], "page_size": 16,
-                   "params": params, "parallelism": "single-gpu", "l2": "weights (3.7 GB) exceed L2; no flush",
+                   "params": params, "parallelism": "single-gpu", "l2": f"weights ({weight_bytes / 1e9:.1f} GB) exceed L2; no flush",
                    "peaks": peak_source},
         "clocks": clocks,
         "e2e": {"value": round(main["wall_tokens_per_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
