@@ -214,12 +214,13 @@ def decode_plan(requests: int, nkv: int, longest: int, sms: int = 148) -> tuple[
     run in one wave: enough loads in flight to fill the memory's bandwidth, short chains, and SMs
     that all get their share. With one or two requests (at most an eighth as many (request, head)
     pairs as SMs) a block has four warps that take the chunk's tiles in turn, without a ring (a
-    tile counts one and a half); such blocks ran well two to an SM and badly three to an SM. The
-    cost of a plan, in tile times: waves x (4 for a block's start and its partial result + tiles
-    per warp), for four-warp blocks divided by the share of the SMs' places that they fill, + a
-    round trip of the merge per eight chunks; the plan is the cheapest chunk (a multiple of 64 keys, 128 to 1024), the shorter
-    on a tie. Its pick was the best or within 2 % of the best of the plans tried at 4,096
-    positions (batches 1 to 16) and at 16,000 and 32,000 (batches 1 and 2)."""
+    tile counts one and a half); at some 244 registers a thread two such blocks fit an SM (plans
+    made for three ran in one and a half waves, and badly). The cost of a plan, in tile times:
+    waves x (4 for a block's start and its partial result + tiles per warp), for four-warp blocks
+    divided by the share of the SMs' places that they fill, + a round trip of the merge per eight
+    chunks; the plan is the cheapest chunk (a multiple of 64 keys, 128 to 1024), the shorter on a
+    tie. Its pick was the best or within 2 % of the best of the plans tried at 4,096 positions
+    (batches 1 to 16) and at 16,000 and 32,000 (batches 1 and 2)."""
     pairs = (1 << max(requests - 1, 0).bit_length()) * max(nkv, 1)
     longest = max(longest, 1)
     warps, per_sm, tile = (4, 2, 1.5) if pairs * 8 <= sms else (1, 6, 1.0)
