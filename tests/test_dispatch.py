@@ -72,3 +72,32 @@ def test_a_pending_residual_step_is_settled_once_and_says_when_it_was_consumed(c
     consumed = ops.PendingStep(x, branch, wb, 1e-6, wo, 1e-5, x_new=torch.zeros_like(x))
     with pytest.raises(RuntimeError, match="already consumed"):
         ops.settle(consumed)
+
+
+def test_prefill_blocks_are_listed_longest_first_heads_innermost(monkeypatch):
+    """The tcgen05 prefill kernel's block list: every block of tokens of every multi-token request
+    once per key/value head, ordered by the key tiles it sees (most first), ties in the order
+    request, first token, head; requests that bring one token are left to the decode kernel."""
+    from types import SimpleNamespace
+
+    def expected(q_lens, seq_lens, tokens_per_block, tile, nkv, window):
+        items = []
+        for s, n in enumerate(q_lens):
+            if n <= 1:
+                continue
+            for t0 in range(0, n, tokens_per_block):
+                pos0 = seq_lens[s] - n + t0
+                last = pos0 + min(tokens_per_block, n - t0) - 1
+                first = max(0, pos0 - window + 1) if window else 0
+                items += [(last // tile - first // tile + 1, s, t0, h) for h in range(nkv)]
+        items.sort(key=lambda item: -item[0])
+        return [list(item[1:]) for item in items]
+
+    monkeypatch.setattr(ops, "_ints_to_device", lambda values, device: values)
+    for q_lens, seq_lens, per_block, tile, nkv, window in [([2048], [2048], 64, 64, 8, 0),
+                                                            ([7, 1, 300, 40], [7, 90, 1000, 45], 64, 64, 3, 0),
+                                                            ([500, 33], [900, 33], 32, 64, 2, 130), ([1, 1], [5, 9], 64, 64, 2, 0)]:
+        step = SimpleNamespace(workspace=None, q_lens=q_lens, seq_lens_host=seq_lens)
+        work = ops._prefill_work_flat(step, per_block, tile, nkv, window, None)
+        assert work.tolist() == expected(q_lens, seq_lens, per_block, tile, nkv, window)
+        assert ops._prefill_work_flat(step, per_block, tile, nkv, window, None) is work  # built once per step
