@@ -2,14 +2,18 @@
 
 Storage
 -------
-Every schedule entry that owns a cache stores, per token, `kv_heads` keys and values
-of `head_dim`. Entries whose needs are equal (same heads, head size and window) form a
-*group*; a group has its own pool of pages and, per request, its own block table. One
-tensor per group, `[entries, pages, 2, kv_heads, page_size, head_dim]`, holds the
-group's pages: page `p` of entry `e` is `tensor[e, p]`, keys at index 0 and values at
-index 1 of the next axis. A request's logical page `i` (positions `i * page_size` to
-`(i + 1) * page_size - 1`) maps to the same physical page number in every entry of
-the group.
+Every schedule entry that owns a cache says, as a `KVSpec`, what it stores per
+position: a list of rows `(heads, width)` (an attention mixer's keys and values are two
+equal rows; a latent cache is one), a window, and how many positions share a stored row.
+Entries whose specs are equal form a *group*; a group has its own pool of pages and, per
+request, its own block table. One tensor per group holds its pages: page `p` of entry
+`e` is `tensor[e, p]`, laid out row after row, each row `[heads, page_size, width]`; a
+group of equal rows is shaped `[entries, pages, rows, heads, page_size, width]` (keys at
+index 0 and values at index 1 of the rows' axis for attention), any other
+`[entries, pages, elements per page]`. A request's logical page `i` holds stored rows
+`i * page_size` to `(i + 1) * page_size - 1` and maps to the same physical page number
+in every entry of the group. Groups may differ in how many pages a request needs of
+them (`KVSpec.stride`), so every count below is per group.
 
 A group with a window gives a page back as soon as every position in it is behind
 the window of all tokens still to come; its block-table entry becomes -1. All pages
@@ -17,8 +21,10 @@ return when the request ends. Freed pages are handed out again, last freed first
 
 Beside the pages there are *state slots*: a request holds one slot number for its
 whole life, and every entry that declares a `StateSpec` has a tensor
-`[slots, *shape]` indexed by it. Muse-Glimmer declares none; the slots exist so a
-mixer with state of its own needs no change here.
+`[slots + 1, *shape]` indexed by it; the last row is a scratch slot that belongs to no
+request (the padding rows of a captured step point at it). A slot is set to the mixer's
+initial state when a request's first step runs. Muse-Glimmer declares no state; the
+slots exist so a mixer with state of its own needs no change here.
 
 The reference keeps one growing buffer per request and layer instead
 (src/mlx_omnia/engine/core/cache/kv.py:18-128) and says which rows a window makes
@@ -80,7 +86,7 @@ class Group:
     spec: KVSpec
     entries: list[int]  # schedule entries stored in this group, in tensor order
     pool: PagePool
-    pages: torch.Tensor | None  # [entries, pages, 2, kv_heads, page_size, head_dim]
+    pages: torch.Tensor | None  # [entries, pages, rows, heads, page_size, width] or [entries, pages, elements]
 
 
 @dataclass
@@ -129,25 +135,45 @@ class CacheManager:
         if allocate:
             for group in self.groups:
                 s = group.spec
-                group.pages = torch.zeros(len(group.entries), group.pool.count, 2, s.kv_heads, page_size, s.head_dim,
-                                          dtype=dtype, device=device)
+                shape = (len(s.rows), *s.rows[0][:1], page_size, s.rows[0][1]) if s.uniform else \
+                    (s.elements_per_position * page_size,)
+                group.pages = torch.zeros(len(group.entries), group.pool.count, *shape, dtype=dtype, device=device)
         self.slots = PagePool(max_requests)
+        self.scratch_slot = max_requests  # the state row that padding rows of a captured step point at
         self.state: dict[int, torch.Tensor] = {}
+        self.initial_state: dict[int, torch.Tensor] = {}  # entries whose state does not start as zeros
         for entry, need in enumerate(needs):
             if need.state is not None and allocate:
-                self.state[entry] = torch.zeros(max_requests, *need.state.shape, dtype=need.state.dtype, device=device)
+                self.state[entry] = torch.zeros(max_requests + 1, *need.state.shape, dtype=need.state.dtype,
+                                                device=device)
+                if need.initial_state is not None:
+                    self.initial_state[entry] = need.initial_state.to(need.state.dtype).to(device)
         self.requests: dict[str, RequestCache] = {}
 
     # -- sizes -----------------------------------------------------------------------
+    @staticmethod
+    def bytes_per_token(needs: list[CacheNeed], element_size: int) -> int:
+        """Cache bytes one position costs over all entries that own pages (what a pool is
+        sized by when the caller names no size)."""
+        return sum(-(-need.kv.elements_per_position // need.kv.stride) * element_size
+                   for need in needs if need.kv is not None)
+
     def bytes_per_page(self, group: int, element_size: int) -> int:
         g = self.groups[group]
-        return len(g.entries) * 2 * g.spec.kv_heads * self.page_size * g.spec.head_dim * element_size
+        return len(g.entries) * g.spec.elements_per_position * self.page_size * element_size
+
+    def pages_for(self, group: int, tokens: int) -> int:
+        """Pages of `group` that a request of `tokens` positions occupies (none given back)."""
+        return -(-self.groups[group].spec.stored(tokens) // self.page_size)
 
     def pages_needed(self, request: RequestCache, new_tokens: int) -> list[int]:
         """Pages each group must take for `request` to grow by `new_tokens`."""
-        have = -(-request.tokens // self.page_size)
-        want = -(-(request.tokens + new_tokens) // self.page_size)
-        return [want - have for _ in self.groups]
+        return [self.pages_for(g, request.tokens + new_tokens) - self.pages_for(g, request.tokens)
+                for g in range(len(self.groups))]
+
+    def capacity_tokens(self) -> int:
+        """The longest request the pools can hold (the tightest group decides)."""
+        return min((g.pool.count * self.page_size * g.spec.stride for g in self.groups), default=1 << 30)
 
     def can_grow(self, request: RequestCache, new_tokens: int, reserve: list[int] | None = None) -> bool:
         need = self.pages_needed(request, new_tokens)
@@ -185,10 +211,11 @@ class CacheManager:
         request.tokens += new_tokens
 
     def slot_of(self, request: RequestCache, group: int, position: int) -> int:
-        page = request.tables[group][position // self.page_size]
+        row = position // self.groups[group].spec.stride
+        page = request.tables[group][row // self.page_size]
         if page < 0:
             raise CacheError(f"position {position} of {request.request_id!r} lies in a page already given back")
-        return page * self.page_size + position % self.page_size
+        return page * self.page_size + row % self.page_size
 
     def release_behind_window(self, request: RequestCache) -> int:
         """Give back pages of windowed groups that no later token can read. With
@@ -200,7 +227,8 @@ class CacheManager:
             if window is None:
                 continue
             dead_below = request.tokens - window + 1  # positions < this are never read again
-            for index in range(min(len(table), max(dead_below, 0) // self.page_size) - 1, -1, -1):
+            dead_rows = max(dead_below, 0) // group.spec.stride  # stored rows wholly below it
+            for index in range(min(len(table), dead_rows // self.page_size) - 1, -1, -1):
                 if table[index] < 0:
                     break  # everything below was given back earlier
                 group.pool.give(table[index])

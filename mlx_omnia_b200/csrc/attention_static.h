@@ -5,10 +5,9 @@
 //
 // Who needs it: a host program that has already handed every free byte of the GPU to a
 // pool of its own (an inference server that embeds this library, for instance) has nothing
-// left for cudaMalloc to give; a caller on a latency-critical path cannot accept the
-// device-wide synchronisation that cudaMalloc and cudaFree imply; and code that runs while
-// a stream is being captured must not allocate at all. `omnia_attention_decode_tc` asks such
-// callers to bring three scratch buffers (partial accumulators, partial softmax statistics
+// left for cudaMalloc to give, and a caller on a latency-critical path cannot accept the
+// device-wide synchronisation that cudaMalloc and cudaFree imply. `omnia_attention_decode_tc`
+// asks such callers to bring three scratch buffers (partial accumulators, partial softmax statistics
 // and a ticket per head group). This variant brings its own: a fixed array that lives in the
 // library's device image. The caller still passes every input and the output.
 //
@@ -28,8 +27,10 @@
 //
 // The first call on each device looks the array's device address up
 // (cudaGetSymbolAddress, with that device current) and raises the kernel's shared-memory
-// limit; later calls on that device only launch. Make that first call outside any stream
-// capture. No call allocates: there is no cudaMalloc, cudaFree or allocating library
+// limit; later calls on that device only launch. That set-up is done under a lock, so host
+// threads may make a device's first call at the same time (their launches still share the
+// scratch, as said above). Make that first call before any stream capture begins. No call
+// allocates: there is no cudaMalloc, cudaFree or allocating library
 // routine on this path.
 #pragma once
 
@@ -46,8 +47,10 @@ extern "C" {
 #endif
 
 // Same arguments and meaning as omnia_attention_decode_tc, without part_o, part_ml and tickets.
-// Returns 0 when the kernel was launched, a cudaError_t value when CUDA refused something, or
-// one of the negative codes above.
+// Returns 0 when the kernel was launched, a cudaError_t value when CUDA refused something or an
+// argument is out of range (requests < 0; nkv, max_chunks, max_pages, num_pages or page_size
+// < 1; chunk_keys not a positive multiple of 32; nq != nkv * GROUP), or one of the negative
+// codes above. Nothing is launched unless 0 is returned.
 int omnia_attention_decode_tc_static(const void* q, const void* pages, const int* block_table,
                                      const int* cu_seqlens, const int* seq_lens, const int* seq_ids,
                                      int requests, int chunk_keys, int max_chunks, const void* gate,

@@ -809,7 +809,8 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
                                          float eps, const float* inv_freq, const long long* slot_mapping,
                                          int spread, int* err, cudaStream_t stream) {
   if (requests == 0) return 0;
-  if (nq != nkv * GROUP || chunk_keys % DECODE_BN != 0 || max_chunks < 1 || (warps != 1 && warps != 4))
+  if (requests < 0 || nkv < 1 || nq != nkv * GROUP || chunk_keys <= 0 || chunk_keys % DECODE_BN != 0 ||
+      max_chunks < 1 || max_pages < 1 || num_pages < 1 || page_size < 1 || (warps != 1 && warps != 4))
     return (int)cudaErrorInvalidValue;
   if (proj != nullptr && (D % 32 != 0 || slot_mapping == nullptr || proj_stride % 2 || q_col % 2 || k_col % 2 || v_col % 2))
     return (int)cudaErrorInvalidValue;
@@ -817,21 +818,18 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
                       (bf16*)const_cast<void*>(pages), (long long)num_pages * page_size};
   // One warp: a two-stage ring. Four warps: one stage each (a warp has few tiles), and the merge area fits in it.
   size_t smem = (size_t)((warps == 1 ? DECODE_STAGES : 4) * 2 * DECODE_BN) * ROW * sizeof(bf16);
-  static int sms = 0;
-  if (sms == 0) {
-    int device = 0;
-    cudaError_t e = cudaGetDevice(&device);
-    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attention_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               (int)(BLOCK_MOST - BLOCK_OVERHEAD));
+  const int sms = omnia_sm_count();
+  static bool configured[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
+  if (!configured[device]) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)(BLOCK_MOST - BLOCK_OVERHEAD));
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(attention_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                (int)(BLOCK_MOST - BLOCK_OVERHEAD));
-    if (e != cudaSuccess) {
-      sms = 0;
-      return (int)e;
-    }
+    if (e != cudaSuccess) return (int)e;
+    configured[device] = true;
   }
   if (spread) {
     // The blocks are handed to SMs as these become free, as many to an SM as fit, and the kernel
@@ -863,6 +861,8 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
 
 #include <stdio.h>
 
+#include <mutex>
+
 static __device__ __align__(256) unsigned char static_scratch[OMNIA_STATIC_SCRATCH_BYTES];
 
 static thread_local char static_error[256] = "";
@@ -879,10 +879,17 @@ extern "C" int omnia_attention_decode_tc_static(const void* q, const void* pages
                                                 cudaStream_t stream) {
   static_error[0] = 0;
   if (requests == 0) return 0;
-  if (nq != nkv * GROUP || chunk_keys % DECODE_BN != 0 || max_chunks < 1) {
+  if (requests < 0 || nkv < 1 || max_chunks < 1 || max_pages < 1 || num_pages < 1 || page_size < 1) {
+    snprintf(static_error, sizeof static_error,
+             "requests (%d) must not be negative; nkv (%d), max_chunks (%d), max_pages (%d), num_pages (%d) "
+             "and page_size (%d) must be at least 1", requests, nkv, max_chunks, max_pages, num_pages, page_size);
+    return (int)cudaErrorInvalidValue;
+  }
+  if (nq != nkv * GROUP || chunk_keys <= 0 || chunk_keys % DECODE_BN != 0) {
     snprintf(static_error, sizeof static_error,
              "this library is compiled for %d query heads per key/value head and chunks that are a "
-             "multiple of %d keys", GROUP, DECODE_BN);
+             "positive multiple of %d keys (given: nq %d, nkv %d, chunk_keys %d)", GROUP, DECODE_BN, nq, nkv,
+             chunk_keys);
     return (int)cudaErrorInvalidValue;
   }
   const long long slots = (long long)requests * nq * max_chunks;
@@ -905,6 +912,9 @@ extern "C" int omnia_attention_decode_tc_static(const void* q, const void* pages
              MAX_DEVICES);
     return e != cudaSuccess ? (int)e : OMNIA_STATIC_NO_DEVICE;
   }
+  {
+  static std::mutex setup;  // two host threads may make a device's first call at once
+  std::lock_guard<std::mutex> held(setup);
   if (device_address[device] == nullptr) {
     unsigned char* address = nullptr;
     e = cudaGetSymbolAddress((void**)&address, static_scratch);
@@ -919,6 +929,7 @@ extern "C" int omnia_attention_decode_tc_static(const void* q, const void* pages
       return (int)e;
     }
     device_address[device] = address;
+  }
   }
   float* part_o = reinterpret_cast<float*>(device_address[device]);
   float* part_ml = part_o + slots * D;

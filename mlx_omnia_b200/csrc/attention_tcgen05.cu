@@ -15,7 +15,10 @@
 // MMAs; warps 2-5 are the softmax and the epilogue (normalise, optional sigmoid gate, store). The score
 // accumulator is double-buffered, so S of the next tile is computed while this tile's softmax runs.
 // Key groups whose page is not loaded (beyond the request, or given back behind a window) are
-// masked in S and skipped in P V, so stale shared memory never reaches the arithmetic.
+// masked in S and skipped in P V, so stale shared memory never reaches the arithmetic; the rows
+// of the last loaded group that lie past the block's last key (the unwritten tail of the
+// request's last page) are cleared in the V tile, so whatever a page's previous owner left
+// there (a NaN included) meets its zero weight as a zero.
 //
 // Every wait on a barrier is bounded: when the bound is hit the block raises OMNIA_ERR_TIMEOUT
 // in the error word, every role leaves its loop, the producer waits (bounded) for loads in
@@ -486,6 +489,21 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
       }
       l += sum;
+      if (j == n_tiles - 1 && ((last + 1) & 15)) {
+        // The last group of 16 keys reaches past the block's last key. Those rows of V get a
+        // zero weight, but what they hold need not be a number: past the request's last token
+        // the page still holds whatever its previous owner left (0 x NaN is NaN). Clear them in
+        // the tile once it has landed; the fence below orders the stores before the P V product.
+        const int s = j % KV_STAGES;
+        ok = mbar_wait(v_full0 + 8 * s, (j / KV_STAGES) & 1, abort_flag);
+        if (!ok) break;
+        const int r0 = last - key0 + 1, r1 = (r0 + 15) & ~15;  // rows [r0, r1) of the tile
+        unsigned char* v_s = kv_s + s * STAGE_BYTES + K_BYTES;
+        for (int i = row; i < (r1 - r0) * DH * 8; i += 128) {
+          const int piece = i & 7, h = (i >> 3) % DH, r = r0 + (i >> 3) / DH;
+          *reinterpret_cast<uint4*>(v_s + h * TILE_HALF + r * 128 + piece * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core (async proxy)
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(p_full);

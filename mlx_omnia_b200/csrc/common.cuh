@@ -148,6 +148,20 @@ inline cudaError_t launch_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 blo
 
 #define OMNIA_LAUNCH_RESULT() ((int)cudaGetLastError())
 
+// How many SMs the current device has (asked once per device, then remembered). Grid sizes and
+// tilings are made from this, never from a number written into the source.
+inline int omnia_sm_count() {
+  static int counts[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) device = 0;
+  if (counts[device] == 0) {
+    int count = 0;
+    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
+    counts[device] = count > 0 ? count : 1;
+  }
+  return counts[device];
+}
+
 #define OMNIA_DISPATCH_DTYPE(code, ...)                    \
   do {                                                     \
     if ((code) == OMNIA_F32) {                             \

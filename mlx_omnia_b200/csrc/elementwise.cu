@@ -422,7 +422,8 @@ extern "C" int omnia_swiglu(const void* gu, void* act, int rows, int inner, int 
                             cudaStream_t stream) {
   const long long total = (long long)rows * inner;
   if (total == 0) return 0;
-  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  const long long most = 16LL * omnia_sm_count();
+  const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
   OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(swiglu_kernel<T>, blocks, 256, 0, stream, 
                                   (const T*)gu, (T*)act, total, inner)));
   return OMNIA_LAUNCH_RESULT();
@@ -446,7 +447,8 @@ __global__ void softcap_kernel(const T* __restrict__ z, float* __restrict__ out,
 extern "C" int omnia_softcap(const void* z, float* out, long long total, float multiplier,
                              float cap, int dtype, cudaStream_t stream) {
   if (total == 0) return 0;
-  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  const long long most = 16LL * omnia_sm_count();
+  const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
   OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(softcap_kernel<T>, blocks, 256, 0, stream, (const T*)z, out,
                                                                             total, multiplier, cap)));
   return OMNIA_LAUNCH_RESULT();

@@ -183,7 +183,7 @@ template <int NT, int RG, int EPI>
 int launch_variant(int blocks, const bf16* a, const bf16* w, void* out, int m, int n, int k, int pair_offset,
                    float multiplier, float cap, cudaStream_t stream) {
   // A grid of at most one wave leaves every block a long slice of k: sixteen warps halve it.
-  if (NT <= 2 && blocks <= 148)
+  if (NT <= 2 && blocks <= omnia_sm_count())
     return launch_warps<NT, RG, EPI, 16>(blocks, a, w, out, m, n, k, pair_offset, multiplier, cap, stream);
   return launch_warps<NT, RG, EPI, 8>(blocks, a, w, out, m, n, k, pair_offset, multiplier, cap, stream);
 }
@@ -193,7 +193,7 @@ int launch(const bf16* a, const bf16* w, void* out, int m, int n, int k, int pai
            float multiplier, float cap, cudaStream_t stream) {
   if (EPI == EPI_SWIGLU)
     return launch_variant<NT, 2, EPI>((pair_offset + 15) / 16, a, w, out, m, n, k, pair_offset, multiplier, cap, stream);
-  if (NT <= 2 && n >= 32 * 148)
+  if (NT <= 2 && n >= 32 * omnia_sm_count())
     return launch_variant<NT, 2, EPI>((n + 31) / 32, a, w, out, m, n, k, 0, multiplier, cap, stream);
   return launch_variant<NT, 1, EPI>((n + 15) / 16, a, w, out, m, n, k, 0, multiplier, cap, stream);
 }

@@ -373,13 +373,7 @@ int launch(const void* a, const void* w, void* out, int m, int n, int k, int pai
   const int cols = EPI == EPI_SWIGLU ? pair_offset : n;
   const int tile_cols = EPI == EPI_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
   const int n_tiles = (cols + tile_cols - 1) / tile_cols, m_tiles = (m + BLOCK_M - 1) / BLOCK_M;
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int device = 0;
-    cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-    if (sm_count <= 0) sm_count = 148;
-  }
+  const int sm_count = omnia_sm_count();
   const long long total = (long long)n_tiles * m_tiles;
   const int grid = (int)(total < sm_count ? total : sm_count);  // one persistent block per SM
   launch_pdl(gemm_tcgen05_kernel<BLOCK_N, STAGES, EPI>, grid, THREADS, smem, stream,
@@ -403,10 +397,10 @@ extern "C" int omnia_gemm_tcgen05(const void* a, const void* w, void* out, int m
   if (epilogue == EPI_SOFTCAP) return launch<256, 4, EPI_SOFTCAP>(a, w, out, m, n, k, 0, multiplier, cap, err, stream);
   if (epilogue != EPI_STORE) return (int)cudaErrorInvalidValue;
   // 256-wide tiles do twice the work per byte staged; 128-wide tiles win only when they fill
-  // SMs that the wide tiling would leave idle. Cost in units of one wide tile per round of 148.
-  const long long m_tiles = (m + 127) / 128;
-  const long long wide_rounds = (((n + 255) / 256) * m_tiles + 147) / 148;
-  const long long narrow_rounds = (((n + 127) / 128) * m_tiles + 147) / 148;
+  // SMs that the wide tiling would leave idle. Cost in units of one wide tile per round of all SMs.
+  const long long m_tiles = (m + 127) / 128, sms = omnia_sm_count();
+  const long long wide_rounds = (((n + 255) / 256) * m_tiles + sms - 1) / sms;
+  const long long narrow_rounds = (((n + 127) / 128) * m_tiles + sms - 1) / sms;
   if (wide_rounds * 100 <= narrow_rounds * 65) return launch<256, 4, EPI_STORE>(a, w, out, m, n, k, 0, 1.f, 0.f, err, stream);
   return launch<128, 6, EPI_STORE>(a, w, out, m, n, k, 0, 1.f, 0.f, err, stream);
 }

@@ -384,16 +384,7 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows)
 }
 
 
-int sm_count() {
-  static int count = 0;
-  if (count == 0) {
-    int device = 0;
-    cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
-    if (count <= 0) count = 148;
-  }
-  return count;
-}
+int sm_count() { return omnia_sm_count(); }
 
 // Tiles of the output for accumulators of `tile_n` columns.
 template <int EPI>

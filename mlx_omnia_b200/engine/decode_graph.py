@@ -6,8 +6,13 @@ run them. Such steps are therefore captured once per *bucket* (requests rounded 
 a power of two, block-table width rounded up to three significant bits) and replayed: the
 host writes the step's metadata into one pinned buffer, one copy brings it to the
 device buffer the captured kernels read, and the graph runs. Rows beyond the live
-requests are padding: sequence length 0, slot -1, position -1, which every kernel
-treats as "nothing to do".
+requests are padding: sequence length 0, cache slot -1, position -1, which every kernel
+treats as "nothing to do", and the scratch state slot, which belongs to no request (so
+a mixer with state of its own may read and write it freely). The metadata is laid out
+and filled by the same `StepLayout` as an uncaptured step's.
+
+At most `MAX_GRAPHS` captured graphs are kept; the one replayed longest ago is dropped
+for a new bucket (each holds its own logits, activations and scratch buffers).
 
 The kernels and the model code are the same as in an uncaptured step; only the way
 they are launched differs, so logits agree bit for bit with an eager step of the same
@@ -27,8 +32,11 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
+from mlx_omnia_b200.engine.step import StepLayout
 from mlx_omnia_b200.kernels import ops
 from mlx_omnia_b200.parts.base import StepContext
+
+MAX_GRAPHS = 24
 
 
 def _bucket(n: int) -> int:
@@ -42,13 +50,10 @@ def _bucket(n: int) -> int:
 class _Captured:
     graph: torch.cuda.CUDAGraph
     step: StepContext
-    host: np.ndarray  # pinned int32 mirror of `device`
-    host_tensor: torch.Tensor
+    layout: StepLayout
+    host_tensor: torch.Tensor  # pinned int32 mirror of `device`
     device: torch.Tensor
-    fields: dict[str, tuple[int, int]]  # name -> (offset, length) in int32 units
     logits: torch.Tensor
-    batch: int
-    width: int
     launches: int = 0  # this package's kernels inside the graph (counted at capture)
     copied: torch.cuda.Event | None = None  # the last host-to-device copy of the metadata
 
@@ -56,55 +61,25 @@ class _Captured:
 class DecodeGraphs:
     def __init__(self, runner) -> None:
         self.runner = runner
-        self.captured: dict[tuple[int, int], _Captured] = {}
+        self.captured: dict[tuple[int, int], _Captured] = {}  # in order of last use, oldest first
         self.replays = 0
 
     @staticmethod
     def supported(model) -> bool:
         return all(getattr(block.mixer, "graph_safe", False) for block in model.blocks)
 
-    # -- layout of the metadata buffer -------------------------------------------------
-    def _layout(self, batch: int, width: int) -> tuple[dict[str, tuple[int, int]], int]:
-        fields, at = {}, 0
-        for name, length in [("token_ids", batch), ("positions", batch), ("cu_seqlens", batch + 1),
-                             ("seq_lens", batch), ("state_slots", batch), ("fresh", batch), ("logit_rows", batch)]:
-            fields[name] = (at, length)
-            at += length
-        for g in range(len(self.runner.cache.groups)):
-            fields[f"table{g}"] = (at, batch * width)
-            at += batch * width
-        at += at % 2  # int64 fields start on 8 bytes
-        for g in range(len(self.runner.cache.groups)):
-            fields[f"slots{g}"] = (at, 2 * batch)
-            at += 2 * batch
-        return fields, at
-
     def _capture(self, batch: int, width: int) -> _Captured:
         runner = self.runner
         device = runner.runtime.device
-        fields, total = self._layout(batch, width)
-        host_tensor = torch.zeros(total, dtype=torch.int32).pin_memory()
-        host = host_tensor.numpy()
-        dev = torch.zeros(total, dtype=torch.int32, device=device)
-
-        def view(name: str) -> torch.Tensor:
-            offset, length = fields[name]
-            return dev[offset: offset + length]
-
-        groups = {}
-        for g in range(len(runner.cache.groups)):
-            slots = view(f"slots{g}").view(torch.int64)
-            groups[g] = (view(f"table{g}").view(batch, width), slots)
-        context_bound = width * runner.cache.page_size
-        # Kernels that need scratch memory keep it here, for as long as the graph lives.
-        workspace = {"private": True}
-        step = StepContext(
-            num_tokens=batch, num_seqs=batch, token_ids=view("token_ids"), positions=view("positions"),
-            cu_seqlens=view("cu_seqlens"), seq_lens=view("seq_lens"), state_slots=view("state_slots"),
-            fresh=view("fresh"), logit_rows=view("logit_rows"), q_lens=[1] * batch, seq_lens_host=[], max_q_len=1,
-            max_seq_len=context_bound, decode_only=True, groups=groups, workspace=workspace)
+        layout = StepLayout(batch, batch, batch, [width] * len(runner.cache.groups))
+        host_tensor = torch.zeros(layout.words, dtype=torch.int32).pin_memory()
+        dev = torch.zeros(layout.words, dtype=torch.int32, device=device)
+        # Kernels that need scratch memory keep it in the workspace, for as long as the graph lives.
+        step = layout.context(dev, q_lens=[1] * batch, seq_lens_host=[], max_q_len=1,
+                              max_seq_len=width * runner.cache.page_size, decode_only=True,
+                              workspace={"private": True})
         # Padding everywhere, so the warm-up and the capture touch no page.
-        self._fill(host, fields, batch, width, [], [])
+        layout.fill(host_tensor.numpy(), runner.cache, [], [], np.arange(batch, dtype=np.int32))
         dev.copy_(host_tensor)
         layers = runner.layer_contexts(step)
         side = torch.cuda.Stream(device=device)
@@ -117,65 +92,34 @@ class DecodeGraphs:
         before = ops.launches
         with torch.cuda.graph(graph):
             logits = runner.model.forward(step, layers)
-        return _Captured(graph, step, host, host_tensor, dev, fields, logits, batch, width, ops.launches - before)
+        return _Captured(graph, step, layout, host_tensor, dev, logits, ops.launches - before)
 
-    def _fill(self, host: np.ndarray, fields, batch: int, width: int, entries, starts) -> None:
-        cache = self.runner.cache
-        n = len(entries)
-
-        def put(name: str, values, pad: int) -> None:
-            offset, length = fields[name]
-            host[offset: offset + length] = pad
-            if len(values):
-                host[offset: offset + len(values)] = values
-
-        put("token_ids", [e.tokens[0] for e in entries], 0)
-        put("positions", starts, -1)
-        offset, length = fields["cu_seqlens"]
-        host[offset: offset + length] = np.arange(length, dtype=np.int32)
-        put("seq_lens", [s + 1 for s in starts], 0)
-        put("state_slots", [e.request.slot for e in entries], 0)
-        put("fresh", [int(e.request.fresh) for e in entries], 0)
-        offset, length = fields["logit_rows"]
-        host[offset: offset + length] = np.arange(length, dtype=np.int32)
-        page = cache.page_size
-        for g in range(len(cache.groups)):
-            offset, length = fields[f"table{g}"]
-            table = host[offset: offset + length].reshape(batch, width)
-            table[:] = -1
-            slots = np.full(batch, -1, dtype=np.int64)
-            for i, (e, start) in enumerate(zip(entries, starts)):
-                pages = e.request.table_array(g)
-                table[i, : len(pages)] = pages
-                slots[i] = int(pages[start // page]) * page + start % page
-            offset, length = fields[f"slots{g}"]
-            host[offset: offset + length].view(np.int64)[:] = slots
+    def _graph_for(self, batch: int, width: int) -> _Captured:
+        key = (batch, width)
+        captured = self.captured.pop(key, None)
+        if captured is None:
+            while len(self.captured) >= MAX_GRAPHS:
+                oldest = next(iter(self.captured))
+                torch.cuda.synchronize(self.runner.runtime.device)  # nothing of it is still running
+                del self.captured[oldest]
+            captured = self._capture(batch, width)
+        self.captured[key] = captured  # most recently used last
+        return captured
 
     # -- one step ----------------------------------------------------------------------
     def run(self, entries, copy: bool = True, device_tokens: torch.Tensor | None = None) -> torch.Tensor:
         """Run a step whose entries all bring one token. -> logits [wanted, vocab].
         With `copy` False the result is the graph's own buffer, valid until the next step.
         `device_tokens` (int32 [entries], on the device) replace the entries' token ids."""
-        runner, cache = self.runner, self.runner.cache
-        starts = [e.request.tokens for e in entries]
-        grown = []
-        try:
-            for e in entries:
-                cache.grow(e.request, 1)
-                grown.append(e.request)
-        except Exception:
-            for request in grown:
-                runner._shrink(request, 1)
-            raise
+        runner = self.runner
+        starts = runner.take_pages(entries)
         batch = _bucket(len(entries))
         width = ops.width_bucket(max(max(len(t) for t in e.request.tables) for e in entries))
-        key = (batch, width)
-        captured = self.captured.get(key)
-        if captured is None:
-            captured = self.captured[key] = self._capture(batch, width)
+        captured = self._graph_for(batch, width)
         if captured.copied is not None:
             captured.copied.synchronize()  # the pinned buffer is free to be written again
-        self._fill(captured.host, captured.fields, batch, width, entries, starts)
+        captured.layout.fill(captured.host_tensor.numpy(), runner.cache, entries, starts,
+                             np.arange(batch, dtype=np.int32))
         captured.device.copy_(captured.host_tensor, non_blocking=True)
         if device_tokens is not None:
             captured.step.token_ids[: len(entries)].copy_(device_tokens[: len(entries)])

@@ -12,10 +12,10 @@ from mlx_omnia_b200.cache.manager import CacheManager
 from mlx_omnia_b200.config.hydrate import read_json
 from mlx_omnia_b200.engine.step import StepRunner
 from mlx_omnia_b200.kernels import ops
-from mlx_omnia_b200.parts.base import Runtime, TensorSpec
-from mlx_omnia_b200.parts.model import DecoderModel
+from mlx_omnia_b200.parts.base import Runtime
+from mlx_omnia_b200.parts.model import DecoderModel, ModelSpec
 from mlx_omnia_b200.registry import Architecture, resolve_architecture
-from mlx_omnia_b200.weights.loader import WeightError, load_tensors
+from mlx_omnia_b200.weights.loader import load_tensors
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
@@ -26,18 +26,32 @@ class EngineArgs:
 
     dtype:          "bfloat16" (what serving uses) or "float32" (everything in true 32-bit)
     page_size:      tokens per cache page
-    cache_tokens:   how many tokens the page pool of each group can hold
+    cache_tokens:   how many tokens the page pool of each group can hold; None sizes the pool
+                    from the device memory that is free once the weights are placed
+                    (`memory_fraction` of it, divided by the cache bytes a token costs)
     max_requests:   live requests (state slots) at most
     device:         the CUDA device
     cuda_graphs:    replay single-token steps from captured CUDA graphs
+    memory_fraction: the share of free device memory that a pool sized by the engine takes
     """
 
     dtype: str = "bfloat16"
     page_size: int = 16
-    cache_tokens: int = 8192
+    cache_tokens: int | None = 8192
     max_requests: int = 64
     device: str = "cuda:0"
     cuda_graphs: bool = True
+    memory_fraction: float = 0.8
+
+
+def pool_tokens(free_bytes: int, bytes_per_token: int, page_size: int, fraction: float) -> int:
+    """Tokens a pool may hold when it is given `fraction` of `free_bytes`: whole pages, at
+    least one. The reference counts its cache's bytes per layer for admission
+    (src/mlx_omnia/engine/core/cache/layer.py:123-127); a paged pool is sized once instead."""
+    if bytes_per_token <= 0:
+        return page_size
+    pages = int(free_bytes * fraction) // (bytes_per_token * page_size)
+    return max(pages, 1) * page_size
 
 
 def _runtime(args: EngineArgs) -> Runtime:
@@ -53,41 +67,24 @@ def _runtime(args: EngineArgs) -> Runtime:
     return Runtime(DTYPES[args.dtype], device)
 
 
-def place_tensors(tensors: dict[str, torch.Tensor], expected: dict[str, TensorSpec], runtime: Runtime,
-                  architecture: Architecture, config) -> dict[str, torch.Tensor]:
-    """In-memory counterpart of `load_tensors`: same strictness, no files."""
-    dropped = set(architecture.dropped_tensors(config))
-    named = {}
-    unexpected = []
-    for file_name, tensor in tensors.items():
-        name = architecture.tensor_name(file_name)
-        if name is None or name in dropped:
-            continue
-        if name in expected:
-            named[name] = tensor
-        else:
-            unexpected.append(file_name)
-    missing = sorted(set(expected) - set(named))
-    wrong = [f"{n}: given {list(t.shape)}, model wants {list(expected[n].shape)}"
-             for n, t in named.items() if tuple(t.shape) != tuple(expected[n].shape)]
-    if missing or unexpected or wrong:
-        raise WeightError(missing, sorted(unexpected), sorted(wrong))
-    out = {}
-    for name, tensor in named.items():
-        kind = expected[name].kind
-        dtype = torch.float32 if kind == "vector" else torch.int32 if kind == "table_i32" else runtime.dtype
-        out[name] = tensor.to(dtype).to(runtime.device)
-    return out
-
-
 class Engine:
     """A loaded model with its cache and step function."""
 
     def __init__(self, architecture: Architecture, config: Any, model: DecoderModel, runtime: Runtime,
                  args: EngineArgs) -> None:
         self.architecture, self.config, self.model, self.runtime, self.args = architecture, config, model, runtime, args
-        pages = -(-args.cache_tokens // args.page_size)
-        self.cache = CacheManager(model.cache_needs(), page_size=args.page_size, pages_per_group=pages,
+        needs = model.cache_needs()
+        tokens = args.cache_tokens
+        if tokens is None:
+            if runtime.device.type != "cuda":
+                raise ValueError("cache_tokens must be given when the engine does not run on a CUDA device")
+            element = torch.empty(0, dtype=runtime.dtype).element_size()
+            free, _ = torch.cuda.mem_get_info(runtime.device)
+            tokens = pool_tokens(free, CacheManager.bytes_per_token(needs, element), args.page_size,
+                                 args.memory_fraction)
+        self.cache_tokens = tokens
+        pages = -(-tokens // args.page_size)
+        self.cache = CacheManager(needs, page_size=args.page_size, pages_per_group=pages,
                                   max_requests=args.max_requests, dtype=runtime.dtype, device=runtime.device)
         self.runner = StepRunner(model, self.cache, runtime, cuda_graphs=args.cuda_graphs)
 
@@ -96,29 +93,30 @@ class Engine:
         return self.model.head.vocab
 
     @classmethod
-    def from_folder(cls, folder: str | Path, args: EngineArgs | None = None) -> "Engine":
-        """Load `folder` (config.json + model*.safetensors); the model class is the one
-        config.json names."""
-        args = args or EngineArgs()
-        raw = read_json(Path(folder))
-        architecture = resolve_architecture(raw)
-        config = architecture.parse(raw)
-        runtime = _runtime(args)
-        model = DecoderModel(architecture.model_spec(config))
-        model.load(load_tensors(folder, architecture, config, model.tensors(), runtime), runtime)
-        return cls(architecture, config, model, runtime, args)
-
-    @classmethod
-    def from_tensors(cls, raw_config: dict[str, Any], tensors: dict[str, torch.Tensor],
-                     args: EngineArgs | None = None) -> "Engine":
-        """Build from a config.json object and tensors under the checkpoint's names."""
+    def build(cls, raw_config: dict[str, Any], source, args: EngineArgs | None = None,
+              spec: ModelSpec | None = None) -> "Engine":
+        """The one way an engine is put together. `source` is whatever `load_tensors` reads
+        (a model folder, or a dict of tensors under the checkpoint's names); the model class
+        is the one `raw_config` names. `spec` replaces the architecture's own list of parts
+        (for a model put together by hand from registered parts)."""
         args = args or EngineArgs()
         architecture = resolve_architecture(raw_config)
         config = architecture.parse(raw_config)
         runtime = _runtime(args)
-        model = DecoderModel(architecture.model_spec(config))
-        model.load(place_tensors(tensors, model.tensors(), runtime, architecture, config), runtime)
+        model = DecoderModel(spec if spec is not None else architecture.model_spec(config))
+        model.load(load_tensors(source, architecture, config, model.tensors(), runtime), runtime)
         return cls(architecture, config, model, runtime, args)
+
+    @classmethod
+    def from_folder(cls, folder: str | Path, args: EngineArgs | None = None) -> "Engine":
+        """Load `folder` (config.json + model*.safetensors)."""
+        return cls.build(read_json(Path(folder)), Path(folder), args)
+
+    @classmethod
+    def from_tensors(cls, raw_config: dict[str, Any], tensors: dict[str, torch.Tensor],
+                     args: EngineArgs | None = None, spec: ModelSpec | None = None) -> "Engine":
+        """Build from a config.json object and tensors under the checkpoint's names."""
+        return cls.build(raw_config, tensors, args, spec)
 
     @classmethod
     def from_random(cls, raw_config: dict[str, Any], seed: int, args: EngineArgs | None = None,

@@ -109,7 +109,7 @@ class Scheduler:
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []
         self._order = itertools.count()
-        self.capacity = min((g.pool.count for g in cache.groups), default=1 << 30) * cache.page_size
+        self.capacity = cache.capacity_tokens()
 
     # -- requests ------------------------------------------------------------------------
     def add(self, request: Request) -> None:
@@ -160,18 +160,17 @@ class Scheduler:
     def _affordable(self, request: Request, wanted: int, reserved: list[int]) -> int:
         """The largest portion <= wanted whose pages are free in every group, `reserved`
         pages per group being already promised to earlier entries of this plan."""
-        page = self.cache.page_size
+        cache = self.cache
         held = request.cache.tokens if request.cache is not None else 0
-        room = held % page and page - held % page  # free positions in the last page
-        free_pages = min((g.pool.free - r for g, r in zip(self.cache.groups, reserved)), default=1 << 30)
-        return max(0, min(wanted, room + max(free_pages, 0) * page))
+        for g, group in enumerate(cache.groups):
+            pages = cache.pages_for(g, held) + max(group.pool.free - reserved[g], 0)
+            wanted = min(wanted, pages * cache.page_size * group.spec.stride - held)
+        return max(0, wanted)
 
     def _reserve(self, request: Request, count: int, reserved: list[int]) -> None:
         held = request.cache.tokens if request.cache is not None else 0
-        page = self.cache.page_size
-        need = -(-(held + count) // page) - -(-held // page)
         for g in range(len(reserved)):
-            reserved[g] += need
+            reserved[g] += self.cache.pages_for(g, held + count) - self.cache.pages_for(g, held)
 
     def plan(self) -> StepPlan:
         reserved = [0] * len(self.cache.groups)

@@ -28,8 +28,18 @@ MAX_LIVE_REQUESTS = 4
 TOKEN_ROUNDING = 64
 
 
-def replay(engine: Engine, lines: IO[str], out_dir: Path, done: IO[str] = sys.stdout) -> int:
-    """Run every step read from `lines`; returns how many steps ran."""
+def poison_free_pages(engine: Engine, value: float = float("nan")) -> None:
+    """Fill every cache page that no request holds with `value`: a step that reads a page it
+    was not given then shows it in its logits. (A debugging aid of the replay program.)"""
+    for group in engine.cache.groups:
+        free = [page for page in range(group.pool.count) if page not in set(group.pool.held())]
+        if free and group.pages is not None:
+            group.pages[:, free] = value
+
+
+def replay(engine: Engine, lines: IO[str], out_dir: Path, done: IO[str] = sys.stdout, before_step=None) -> int:
+    """Run every step read from `lines`; returns how many steps ran. `before_step(engine,
+    record)`, when given, runs ahead of each step."""
     out_dir.mkdir(parents=True, exist_ok=True)
     count = 0
     for line in lines:
@@ -37,6 +47,8 @@ def replay(engine: Engine, lines: IO[str], out_dir: Path, done: IO[str] = sys.st
         if not line:
             continue
         record = json.loads(line)
+        if before_step is not None:
+            before_step(engine, record)
         entries = []
         for item in record.get("entries", []):
             request_id = str(item["id"])
@@ -65,6 +77,8 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at any time, each request rounded up to 64")
     parser.add_argument("--page-size", type=int, default=16, help="tokens per cache page (a divisor of 64)")
+    parser.add_argument("--poison-free-pages", action="store_true",
+                        help="before every step fill the cache pages that no request holds with NaN")
     args = parser.parse_args(argv)
     if TOKEN_ROUNDING % args.page_size:
         parser.error("--page-size must divide 64")
@@ -72,5 +86,6 @@ def main(argv: list[str] | None = None) -> int:
     engine = Engine.from_folder(args.model, EngineArgs(dtype=args.dtype, page_size=args.page_size,
                                                        cache_tokens=max(args.max_tokens, TOKEN_ROUNDING),
                                                        max_requests=MAX_LIVE_REQUESTS))
-    replay(engine, sys.stdin, Path(args.out))
+    replay(engine, sys.stdin, Path(args.out),
+           before_step=(lambda e, record: poison_free_pages(e)) if args.poison_free_pages else None)
     return 0

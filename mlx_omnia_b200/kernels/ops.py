@@ -99,6 +99,19 @@ def require_cuda() -> None:
         raise KernelError("mlx_omnia_b200 runs on a CUDA device (sm_100a) only; none is visible")
 
 
+_sm_counts: dict[int, int] = {}
+
+
+def sm_count(device: torch.device | None = None) -> int:
+    """How many SMs `device` (the current one when None) has; asked once per device. Plans that
+    count waves or shares of the GPU are made from this."""
+    index = torch.cuda.current_device() if device is None or device.index is None else device.index
+    count = _sm_counts.get(index)
+    if count is None:
+        count = _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return count
+
+
 # ------------------------------------------------------------------------------------
 
 
@@ -205,7 +218,7 @@ def width_bucket(pages: int) -> int:
     return -(-pages // step) * step
 
 
-def decode_plan(requests: int, nkv: int, longest: int, sms: int = 148) -> tuple[int, int]:
+def decode_plan(requests: int, nkv: int, longest: int, sms: int) -> tuple[int, int]:
     """(keys per block, warps per block) of the decode attention kernel for `requests` requests
     (rounded up to a power of two, as a captured graph's batch is) of `nkv` key/value heads whose
     longest holds `longest` positions. A block of one warp walks its chunk's 32-key tiles one after
@@ -220,7 +233,7 @@ def decode_plan(requests: int, nkv: int, longest: int, sms: int = 148) -> tuple[
     divided by the share of the SMs' places that they fill, + a round trip of the merge per eight
     chunks; the plan is the cheapest chunk (a multiple of 64 keys, 128 to 1024), the shorter on a
     tie. Its pick was the best or within 2 % of the best of the plans tried at 4,096 positions
-    (batches 1 to 16) and at 16,000 and 32,000 (batches 1 and 2)."""
+    (batches 1 to 16) and at 16,000 and 32,000 (batches 1 and 2), on a GPU of 148 SMs (`sms`)."""
     pairs = (1 << max(requests - 1, 0).bit_length()) * max(nkv, 1)
     longest = max(longest, 1)
     warps, per_sm, tile = (4, 2, 1.5) if pairs * 8 <= sms else (1, 6, 1.0)
@@ -415,7 +428,7 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
     if step.decode_only or single is not None:
         count = step.num_seqs if step.decode_only else single.shape[0]
         longest = width_bucket(-(-longest // kv.page_size)) * kv.page_size
-        chunk, warps = decode_plan(count, nkv, longest)
+        chunk, warps = decode_plan(count, nkv, longest, sm_count(q.device))
         max_chunks = -(-longest // chunk)
         part_o, part_ml, tickets = _step_buffers(step, q.device, {
             "attention_part_o": (count * nq * max_chunks * d, torch.float32, False),
@@ -544,7 +557,7 @@ USE_TCGEN05_PAIR = True
 """Large bfloat16 products run two SMs to a tile (gemm_tcgen05_pair.cu); off, one SM to a tile."""
 
 
-def _pair_pays(rows: int, n: int, k: int, epilogue: int, sms: int = 148) -> bool:
+def _pair_pays(rows: int, n: int, k: int, epilogue: int, sms: int) -> bool:
     """Whether the two-SM kernel is the faster one: it brings in a third less per step of k, but
     has half as many (twice as large) tiles to hand out and a longer start. Measured at the
     benchmark's shapes it wins by 4 to 13 % where a pair of SMs gets at least 64 steps of k of
@@ -559,7 +572,7 @@ def _pair_pays(rows: int, n: int, k: int, epilogue: int, sms: int = 148) -> bool
 
 def _gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, multiplier: float = 1.0,
                   cap: float = 0.0) -> torch.Tensor:
-    if USE_TCGEN05_PAIR and _pair_pays(a.shape[0], weight.shape[0], a.shape[1], epilogue):
+    if USE_TCGEN05_PAIR and _pair_pays(a.shape[0], weight.shape[0], a.shape[1], epilogue, sm_count(a.device)):
         return _gemm_tcgen05_pair(a, weight, out, epilogue, multiplier, cap)
     fn = _function("gemm_tcgen05", "omnia_gemm_tcgen05",
                    [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p])

@@ -43,7 +43,7 @@ class GQAAttention(Mixer):
         self.position = POSITIONS.build(position or PartSpec("none"))
 
     def kv_spec(self) -> KVSpec:
-        return KVSpec(self.kv_heads, self.head_dim, self.window)
+        return KVSpec.keys_and_values(self.kv_heads, self.head_dim, self.window)
 
     def tensors(self) -> dict[str, TensorSpec]:
         q, kv = self.heads * self.head_dim, self.kv_heads * self.head_dim

@@ -13,8 +13,9 @@ Every part:
     ``tensors() -> {local_name: TensorSpec}``   what it loads
     ``load(tensors, runtime)``                  receives exactly those, on the device
 Mixer additionally:
-    ``kv_spec() -> KVSpec | None``              rows it keeps per token, in pages
+    ``kv_spec() -> KVSpec | None``              rows it keeps per position, in pages
     ``state_spec() -> StateSpec | None``        fixed-size state it keeps per request
+    ``initial_state() -> Tensor | None``        what that state starts as (None: zeros)
     ``forward(h, ctx: LayerContext) -> branch`` h, branch: [tokens, hidden] engine dtype
 FeedForward:  ``forward(h, ctx) -> branch``
               A mixer or feed-forward whose `forward` gives `h` to one ``ops.linear`` or
@@ -23,6 +24,7 @@ FeedForward:  ``forward(h, ctx) -> branch``
 Norm:         ``forward(x) -> h`` and the attributes ``weight``, ``eps`` that the
               fused residual kernel reads (``weight is None`` means weightless)
 Position:     ``table() -> float32[rotary_dims / 2] | None`` of inverse frequencies
+Embedding:    ``forward(token_ids, positions) -> x`` float32 [tokens, hidden]
 Block:        ``entry_norm`` and ``forward(x, h, ctx, exit_norm) -> (x, h_next)``
 """
 
@@ -47,18 +49,48 @@ class TensorSpec:
 
 @dataclass(frozen=True)
 class KVSpec:
-    """Per-token rows a mixer keeps in the paged cache: `kv_heads` keys and values of
-    `head_dim` each. `window` is how many of the latest positions can still be read
-    (None: all of them). Layers with equal specs share one group of pages."""
+    """What a mixer keeps in the paged cache for every position.
 
-    kv_heads: int
-    head_dim: int
+    rows:    the tensors of one position, each `(heads, width)`: an attention mixer keeps two
+             equal ones (its keys and its values), a mixer with a latent cache one, a mixer
+             whose keys and values differ in width two unequal ones.
+    window:  how many of the latest positions can still be read (None: all of them).
+    stride:  positions per stored row (1: one row for every position; n: one row for every
+             n positions, as a mixer that keeps a compressed history would want).
+    Layers with equal specs share one group of pages."""
+
+    rows: tuple[tuple[int, int], ...]
     window: int | None = None
+    stride: int = 1
+
+    def __post_init__(self) -> None:
+        if not self.rows or any(h < 1 or w < 1 for h, w in self.rows):
+            raise ValueError(f"a cache row needs positive (heads, width) entries, got {self.rows}")
+        if self.stride < 1 or (self.window is not None and self.window < 1):
+            raise ValueError("stride and window must be at least 1")
+
+    @classmethod
+    def keys_and_values(cls, kv_heads: int, head_dim: int, window: int | None = None) -> "KVSpec":
+        """`kv_heads` keys and as many values of `head_dim` each per position."""
+        return cls(((kv_heads, head_dim), (kv_heads, head_dim)), window)
+
+    @property
+    def uniform(self) -> bool:
+        return all(row == self.rows[0] for row in self.rows)
+
+    @property
+    def elements_per_position(self) -> int:
+        return sum(h * w for h, w in self.rows)
+
+    def stored(self, positions: int) -> int:
+        """Rows that `positions` positions occupy."""
+        return -(-positions // self.stride)
 
 
 @dataclass(frozen=True)
 class StateSpec:
-    """Fixed-size state a mixer keeps per request (one slot per live request)."""
+    """Fixed-size state a mixer keeps per request (one slot per live request). A request's
+    state starts as `Mixer.initial_state()` says (zeros unless overridden)."""
 
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32
@@ -96,6 +128,11 @@ class Mixer(Part):
     def state_spec(self) -> StateSpec | None:
         return None
 
+    def initial_state(self) -> torch.Tensor | None:
+        """What a request's state slot holds before its first step: a tensor of the
+        `StateSpec`'s shape, or None for zeros."""
+        return None
+
     def forward(self, h: torch.Tensor, ctx: "LayerContext") -> torch.Tensor:  # pragma: no cover
         raise NotImplementedError
 
@@ -117,6 +154,15 @@ class Norm(Part):
 
 class Position(Part):
     def table(self) -> torch.Tensor | None:  # pragma: no cover
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    """Turns the step's tokens into the float32 residual stream. It is told where each
+    token stands, so an encoding that is added to the embeddings (learned absolute
+    positions, say) is a part like any other."""
+
+    def forward(self, token_ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:  # pragma: no cover
         raise NotImplementedError
 
 
@@ -189,11 +235,16 @@ register_head = HEADS.register
 class KVView:
     """One cache entry's pages as a mixer sees them in a step.
 
-    pages:        [num_pages, 2, kv_heads, page_size, head_dim]; index 1 of axis 1 is V
+    pages:        a group whose rows are all `(heads, width)` (keys and values of equal
+                  shape, or a single latent row): [num_pages, len(rows), heads, page_size,
+                  width], so index 1 of axis 1 is an attention mixer's V; a group of
+                  unequal rows: [num_pages, elements per page], row i of a page being the
+                  `[heads_i, page_size, width_i]` block that `row(i)` views
     block_table:  int32 [num_seqs, max_pages]; physical page of each logical page of
                   each request, -1 where a page was given back (behind a window)
     slot_mapping: int64 [tokens]; page * page_size + offset where this step's token goes
     writes:       False when this entry reads another entry's cache
+    spec:         the `KVSpec` the pages were made for
     """
 
     pages: torch.Tensor
@@ -202,7 +253,16 @@ class KVView:
     page_size: int
     window: int | None
     writes: bool = True
+    spec: KVSpec | None = None
 
+    def row(self, index: int) -> torch.Tensor:
+        """Row `index` of every page: [num_pages, heads, page_size, width]."""
+        if self.pages.dim() == 5:
+            return self.pages[:, index]
+        rows = self.spec.rows
+        start = sum(h * w for h, w in rows[:index]) * self.page_size
+        heads, width = rows[index]
+        return self.pages[:, start: start + heads * width * self.page_size].view(-1, heads, self.page_size, width)
 
 @dataclass
 class StepContext:
@@ -219,7 +279,7 @@ class StepContext:
     positions: torch.Tensor  # [tokens] absolute position of each token in its request
     cu_seqlens: torch.Tensor  # [num_seqs + 1] offsets of each request's tokens in the batch
     seq_lens: torch.Tensor  # [num_seqs] tokens of the request held after this step
-    state_slots: torch.Tensor  # [num_seqs] slot of per-request state
+    state_slots: torch.Tensor  # [num_seqs] slot of per-request state (padding rows: the scratch slot)
     fresh: torch.Tensor  # [num_seqs] 1 where this is the request's first portion
     logit_rows: torch.Tensor  # [wanted] rows of the batch whose logits are wanted
     q_lens: list[int]

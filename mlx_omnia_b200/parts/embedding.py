@@ -13,11 +13,11 @@ from __future__ import annotations
 import torch
 
 from mlx_omnia_b200.kernels import ops
-from mlx_omnia_b200.parts.base import Part, TensorSpec, register_embedding, register_head
+from mlx_omnia_b200.parts.base import Embedding, Part, TensorSpec, register_embedding, register_head
 
 
 @register_embedding("token_embedding")
-class TokenEmbedding(Part):
+class TokenEmbedding(Embedding):
     """x = table[ids], RMS-normalised without a weight when `norm_eps` is given.
     The output is the float32 residual stream."""
 
@@ -31,8 +31,8 @@ class TokenEmbedding(Part):
         super().load(tensors, runtime)
         self.weight = tensors["weight"].contiguous()
 
-    def forward(self, ids: torch.Tensor) -> torch.Tensor:
-        return ops.embed_rmsnorm(ids, self.weight, self.norm_eps)
+    def forward(self, token_ids: torch.Tensor, positions: torch.Tensor | None = None) -> torch.Tensor:
+        return ops.embed_rmsnorm(token_ids, self.weight, self.norm_eps)
 
 
 @register_head("lm_head")

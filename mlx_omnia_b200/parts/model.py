@@ -62,6 +62,7 @@ class CacheNeed:
     kv: KVSpec | None  # pages it owns (None: none, or it reads another entry's)
     state: StateSpec | None
     reads: int | None
+    initial_state: torch.Tensor | None = None  # what a request's state starts as (None: zeros)
 
 
 class DecoderModel:
@@ -105,14 +106,14 @@ class DecoderModel:
                 if kv != owner:
                     raise ValueError(f"a schedule entry reads a cache of {owner} but its mixer keeps {kv}")
                 kv = None
-            needs.append(CacheNeed(kv, state, entry.reads))
+            needs.append(CacheNeed(kv, state, entry.reads, mixer.initial_state() if state is not None else None))
         return needs
 
     # -- the step --------------------------------------------------------------------
     def forward(self, step: StepContext, layers: list[LayerContext]) -> torch.Tensor:
         """Run this step's tokens through the schedule. -> float32 logits [wanted, vocab]"""
         schedule = self.spec.schedule
-        x = self.embedding.forward(step.token_ids)
+        x = self.embedding.forward(step.token_ids, step.positions)
         h = self.blocks[schedule[0].layer].entry_norm.forward(x)
         for e, entry in enumerate(schedule):
             after = self.blocks[schedule[e + 1].layer] if e + 1 < len(schedule) else None

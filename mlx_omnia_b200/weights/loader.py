@@ -54,45 +54,83 @@ def _target_dtype(spec: TensorSpec, runtime: Runtime) -> torch.dtype:
     return runtime.dtype
 
 
-def load_tensors(folder: str | Path, architecture: Architecture, config, expected: dict[str, TensorSpec],
+class FolderSource:
+    """The tensors of every `model*.safetensors` of a folder, read one at a time."""
+
+    def __init__(self, folder: str | Path) -> None:
+        self.where: dict[str, Path] = {}
+        for path in checkpoint_files(Path(folder)):
+            with safe_open(str(path), framework="pt", device="cpu") as handle:
+                for name in handle.keys():
+                    self.where[name] = path
+        self._open: tuple[Path, object] | None = None
+
+    def names(self) -> list[str]:
+        return list(self.where)
+
+    def _handle(self, name: str):
+        path = self.where[name]
+        if self._open is None or self._open[0] != path:
+            self._open = (path, safe_open(str(path), framework="pt", device="cpu"))
+        return self._open[1]
+
+    def shape(self, name: str) -> tuple[int, ...]:
+        return tuple(self._handle(name).get_slice(name).get_shape())
+
+    def tensor(self, name: str) -> torch.Tensor:
+        return self._handle(name).get_tensor(name)
+
+
+class DictSource:
+    """Tensors already in memory, under the checkpoint's names."""
+
+    def __init__(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.tensors = tensors
+
+    def names(self) -> list[str]:
+        return list(self.tensors)
+
+    def shape(self, name: str) -> tuple[int, ...]:
+        return tuple(self.tensors[name].shape)
+
+    def tensor(self, name: str) -> torch.Tensor:
+        return self.tensors[name]
+
+
+def load_tensors(source, architecture: Architecture, config, expected: dict[str, TensorSpec],
                  runtime: Runtime) -> dict[str, torch.Tensor]:
-    """Read, check and place on the device every tensor in `expected`."""
-    folder = Path(folder)
+    """Check and place on the device every tensor in `expected`. `source` is a model folder
+    (a path), a dict of tensors under the checkpoint's names, or anything with `names()`,
+    `shape(name)` and `tensor(name)`; whichever it is, the same check runs."""
+    if isinstance(source, (str, Path)):
+        source = FolderSource(source)
+    elif isinstance(source, dict):
+        source = DictSource(source)
     dropped = set(architecture.dropped_tensors(config))
-    found: dict[str, tuple[Path, str]] = {}
+    found: dict[str, str] = {}
     unexpected: list[str] = []
-    for path in checkpoint_files(folder):
-        with safe_open(str(path), framework="pt", device="cpu") as handle:
-            for file_name in handle.keys():
-                name = architecture.tensor_name(file_name)
-                if name is None or name in dropped:
-                    continue
-                if name in expected:
-                    found[name] = (path, file_name)
-                else:
-                    unexpected.append(file_name)
+    for file_name in source.names():
+        name = architecture.tensor_name(file_name)
+        if name is None or name in dropped:
+            continue
+        if name in expected:
+            found[name] = file_name
+        else:
+            unexpected.append(file_name)
     missing = sorted(set(expected) - set(found))
     wrong: list[str] = []
+    for name, file_name in found.items():
+        shape = source.shape(file_name)
+        if shape != tuple(expected[name].shape):
+            wrong.append(f"{file_name}: file has {list(shape)}, model wants {list(expected[name].shape)}")
     tensors: dict[str, torch.Tensor] = {}
-    by_file: dict[Path, list[tuple[str, str]]] = {}
-    for name, (path, file_name) in found.items():
-        by_file.setdefault(path, []).append((name, file_name))
-    for path, names in by_file.items():
-        with safe_open(str(path), framework="pt", device="cpu") as handle:
-            for name, file_name in names:
-                spec = expected[name]
-                shape = tuple(handle.get_slice(file_name).get_shape())
-                if shape != tuple(spec.shape):
-                    wrong.append(f"{file_name}: file has {list(shape)}, model wants {list(spec.shape)}")
-                    continue
-                if missing or unexpected or wrong:
-                    continue  # an error is coming; do not spend time reading
-                tensor = handle.get_tensor(file_name)
-                floating = tensor.dtype.is_floating_point
-                if (spec.kind == "table_i32") == floating:
-                    wrong.append(f"{file_name}: file has dtype {tensor.dtype}, model wants a {spec.kind}")
-                    continue
-                tensors[name] = tensor.to(_target_dtype(spec, runtime)).to(runtime.device)
+    if not (missing or unexpected or wrong):  # with an error coming, no time is spent reading
+        for name, file_name in sorted(found.items(), key=lambda item: item[1]):
+            spec, tensor = expected[name], source.tensor(file_name)
+            if (spec.kind == "table_i32") == tensor.dtype.is_floating_point:
+                wrong.append(f"{file_name}: file has dtype {tensor.dtype}, model wants a {spec.kind}")
+                continue
+            tensors[name] = tensor.to(_target_dtype(spec, runtime)).to(runtime.device)
     if missing or unexpected or wrong:
         raise WeightError(missing, sorted(unexpected), sorted(wrong))
     return tensors

@@ -22,19 +22,40 @@ FULL = "full_attention"  # src/mlx_omnia/engine/core/masks.py:6
 PREFIX = "model.language_model."  # src/mlx_omnia/engine/models/muse_glimmer/checkpoint.py:48-53
 
 
+class Rounding:
+    """Where a reduced-precision run of the reference rounds: every tensor an op hands to the
+    next op is stored in `dtype` (MLX keeps activations in the checkpoint's dtype), while
+    norms, softmax, rotation angles and the gate's sigmoid work in 32-bit inside the op
+    (src/mlx_omnia/engine/core/kernels/add_norm/fused.py:33-46,
+    src/mlx_omnia/engine/core/kernels/attention/sink.py:11-25,
+    src/mlx_omnia/engine/core/attention.py:673-681). `None` rounds nothing. It exists to measure
+    how far a faithful bfloat16 run may drift from the exact result: the tolerance of the
+    bfloat16 tests is a multiple of that, not a guess."""
+
+    def __init__(self, dtype: torch.dtype | None = None) -> None:
+        self.dtype = dtype
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        return x if self.dtype is None else x.to(self.dtype).to(x.dtype)
+
+
+EXACT = Rounding(None)
+
+
 def text_config(config: dict) -> dict:
     """The text trunk's keys live under ``text_config``.
     src/mlx_omnia/engine/models/muse_glimmer/config.py:79-85"""
     return config["text_config"] if "text_config" in config else config
 
 
-def rms_norm(x: torch.Tensor, weight: torch.Tensor | None, eps: float) -> torch.Tensor:
-    """``x * rsqrt(mean(x^2) + eps) * weight``; weightless when ``weight`` is None.
+def rms_norm(x: torch.Tensor, weight: torch.Tensor | None, eps: float, r: Rounding = EXACT) -> torch.Tensor:
+    """``x * rsqrt(mean(x^2) + eps) * weight``; weightless when ``weight`` is None. The
+    normalised value is rounded before the weight multiplies it.
     src/mlx_omnia/engine/models/muse_glimmer/layers/attention.py:8-17 (weightless),
     src/mlx_omnia/engine/core/kernels/add_norm/fused.py:33-46 (the arithmetic)."""
     scale = torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + eps)
-    y = x * scale
-    return y if weight is None else y * weight
+    y = r(x * scale)
+    return y if weight is None else r(y * weight)
 
 
 def centred(weight: torch.Tensor) -> torch.Tensor:
@@ -43,13 +64,13 @@ def centred(weight: torch.Tensor) -> torch.Tensor:
     return weight + 1.0
 
 
-def embed(ids: torch.Tensor, table: torch.Tensor, eps: float) -> torch.Tensor:
+def embed(ids: torch.Tensor, table: torch.Tensor, eps: float, r: Rounding = EXACT) -> torch.Tensor:
     """Lookup, then a weightless RMS norm over the hidden axis.
     src/mlx_omnia/engine/models/muse_glimmer/model.py:62-63"""
-    return rms_norm(table[ids], None, eps)
+    return rms_norm(table[ids], None, eps, r)
 
 
-def rope(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor:
+def rope(x: torch.Tensor, positions: torch.Tensor, theta: float, r: Rounding = EXACT) -> torch.Tensor:
     """Half-split rotation of the whole head: pair (i, i + d/2), angle
     ``pos * theta^(-2i/d)``; ``theta == 0`` leaves the head as it is (NoPE).
     x: [tokens, heads, d].
@@ -66,10 +87,10 @@ def rope(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor
     # unless the whole run is in float64.
     work = torch.float64 if x.dtype == torch.float64 else torch.float32
     angle = positions.to(work)[:, None] * inv_freq.to(work)[None, :]
-    cos = torch.cos(angle)[:, None, :].to(x.dtype)
+    cos = torch.cos(angle)[:, None, :].to(x.dtype)  # the rotation itself is 32-bit; its result is rounded
     sin = torch.sin(angle)[:, None, :].to(x.dtype)
     lo, hi = x[..., :half], x[..., half:]
-    return torch.cat([lo * cos - hi * sin, lo * sin + hi * cos], dim=-1)
+    return r(torch.cat([lo * cos - hi * sin, lo * sin + hi * cos], dim=-1))
 
 
 def visible(queries: torch.Tensor, keys: torch.Tensor, window: int | None) -> torch.Tensor:
@@ -85,7 +106,7 @@ def visible(queries: torch.Tensor, keys: torch.Tensor, window: int | None) -> to
 
 
 def attention_core(
-    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor, scale: float
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor, scale: float, r: Rounding = EXACT
 ) -> torch.Tensor:
     """Grouped-query softmax attention. q: [T, nq, d]; k, v: [S, nkv, d]; query head h
     reads KV head ``h // (nq / nkv)``.  -> [T, nq * d]
@@ -99,8 +120,8 @@ def attention_core(
     scores = torch.einsum("thd,shd->hts", q, k) * scale
     scores = scores.masked_fill(~mask[None], float("-inf"))
     probs = torch.softmax(scores, dim=-1)
-    out = torch.einsum("hts,shd->thd", probs, v)
-    return out.reshape(tokens, heads * d)
+    out = torch.einsum("hts,shd->thd", probs, v)  # scores, softmax and the sum stay 32-bit; the context is rounded
+    return r(out.reshape(tokens, heads * d))
 
 
 def attention(
@@ -116,35 +137,36 @@ def attention(
     scale: float,
     eps: float,
     shared_kv: tuple[torch.Tensor, torch.Tensor] | None = None,
+    r: Rounding = EXACT,
 ) -> tuple[torch.Tensor, tuple[torch.Tensor, torch.Tensor]]:
     """Project, weightless per-head RMS on q and k, rotate, attend, gate, project out.
     Returns the branch and the (k, v) that a cache would hold.
     src/mlx_omnia/engine/core/attention.py:618-682;
     src/mlx_omnia/engine/models/muse_glimmer/layers/attention.py:20-47."""
     tokens = h.shape[0]
-    q = (h @ w["q_proj.weight"].T).reshape(tokens, heads, head_dim)
-    q = rope(rms_norm(q, None, eps), positions, theta)
+    q = r(h @ w["q_proj.weight"].T).reshape(tokens, heads, head_dim)
+    q = rope(rms_norm(q, None, eps, r), positions, theta, r)
     if shared_kv is None:
-        k = (h @ w["k_proj.weight"].T).reshape(tokens, kv_heads, head_dim)
-        v = (h @ w["v_proj.weight"].T).reshape(tokens, kv_heads, head_dim)
-        k = rope(rms_norm(k, None, eps), positions, theta)
+        k = r(h @ w["k_proj.weight"].T).reshape(tokens, kv_heads, head_dim)
+        v = r(h @ w["v_proj.weight"].T).reshape(tokens, kv_heads, head_dim)
+        k = rope(rms_norm(k, None, eps, r), positions, theta, r)
     else:
         k, v = shared_kv
     mask = visible(positions, positions, window)
-    out = attention_core(q, k, v, mask, scale)
+    out = attention_core(q, k, v, mask, scale, r)
     # The gate reads the same normed input as q; sigmoid in 32-bit, full width.
     # src/mlx_omnia/engine/core/attention.py:673-681
-    gate = torch.sigmoid(h @ w["gate_proj.weight"].T)
-    out = out * gate
-    return out @ w["o_proj.weight"].T, (k, v)
+    gate = r(torch.sigmoid(r(h @ w["gate_proj.weight"].T)))
+    out = r(out * gate)
+    return r(out @ w["o_proj.weight"].T), (k, v)
 
 
-def swiglu(h: torch.Tensor, w: dict[str, torch.Tensor]) -> torch.Tensor:
+def swiglu(h: torch.Tensor, w: dict[str, torch.Tensor], r: Rounding = EXACT) -> torch.Tensor:
     """``down(silu(gate(h)) * up(h))``.
     src/mlx_omnia/engine/core/layers.py:249-250,253-272"""
-    gate = h @ w["gate_proj.weight"].T
-    up = h @ w["up_proj.weight"].T
-    return (gate * torch.sigmoid(gate) * up) @ w["down_proj.weight"].T
+    gate = r(h @ w["gate_proj.weight"].T)
+    up = r(h @ w["up_proj.weight"].T)
+    return r(r(r(gate * torch.sigmoid(gate)) * up) @ w["down_proj.weight"].T)
 
 
 def trunk_name(name: str) -> str:
@@ -168,13 +190,14 @@ def block(
     layer_type: str,
     theta: float,
     shared_kv=None,
+    r: Rounding = EXACT,
 ):
     """Sandwich norms: ``x + post_attn(attn(input_ln(x)))`` then
     ``+ post_ff(mlp(pre_ff(.)))``.
     src/mlx_omnia/engine/models/muse_glimmer/layers/block.py:11-26"""
     eps, post_eps = cfg["rms_norm_eps"], cfg["post_norm_eps"]
     d = cfg["head_dim"]
-    h1 = rms_norm(x, centred(w["input_layernorm.weight"]), eps)
+    h1 = rms_norm(x, centred(w["input_layernorm.weight"]), eps, r)
     a, kv = attention(
         h1,
         positions,
@@ -187,11 +210,12 @@ def block(
         scale=cfg["qk_scale_factor"] * d**-0.5,
         eps=eps,
         shared_kv=shared_kv,
+        r=r,
     )
-    x = x + rms_norm(a, centred(w["post_attention_layernorm.weight"]), post_eps)
-    h2 = rms_norm(x, centred(w["pre_feedforward_layernorm.weight"]), eps)
-    m = swiglu(h2, sub(w, "mlp."))
-    x = x + rms_norm(m, centred(w["post_feedforward_layernorm.weight"]), post_eps)
+    x = r(x + rms_norm(a, centred(w["post_attention_layernorm.weight"]), post_eps, r))
+    h2 = rms_norm(x, centred(w["pre_feedforward_layernorm.weight"]), eps, r)
+    m = swiglu(h2, sub(w, "mlp."), r)
+    x = r(x + rms_norm(m, centred(w["post_feedforward_layernorm.weight"]), post_eps, r))
     return x, kv
 
 
@@ -209,8 +233,15 @@ def forward(
     dtype: torch.dtype = torch.float32,
     schedule: list[tuple[int, int | None]] | None = None,
     taps: dict | None = None,
+    activations: torch.dtype | None = None,
+    rows=None,
 ) -> torch.Tensor:
-    """Logits at every position of one whole sequence.  -> [T, vocab]
+    """Logits at every position of one whole sequence (or at the positions ``rows``, so that a
+    wide head need not be applied everywhere).  -> [T or len(rows), vocab]
+
+    ``activations`` (e.g. ``torch.bfloat16``): every tensor handed from one op to the next
+    is rounded to that dtype, as in a run of the reference in that precision (see
+    ``Rounding``); the logits themselves stay as the head's 32-bit sum gives them.
 
     ``schedule`` (a test-only generality): a list of ``(layer, reads_entry)``; the
     default is every layer once, each with keys and values of its own. An entry with
@@ -220,7 +251,8 @@ def forward(
     w = {trunk_name(k): v.to(dtype) for k, v in weights.items()}
     ids = torch.as_tensor(ids, dtype=torch.long)
     positions = torch.arange(ids.shape[0])
-    x = embed(ids, w["embed_tokens.weight"], cfg["rms_norm_eps"])
+    r = Rounding(activations)
+    x = embed(ids, w["embed_tokens.weight"], cfg["rms_norm_eps"], r)
     if taps is not None:
         taps["embeddings"] = x
         taps["blocks"] = []
@@ -236,13 +268,16 @@ def forward(
             cfg["layer_types"][layer],
             cfg["layer_rope_theta"][layer],
             shared_kv=None if reads is None else produced[reads],
+            r=r,
         )
         produced.append(kv)
         if taps is not None:
             taps["blocks"].append(x)
     # The final norm multiplies its weight directly: no +1.
     # src/mlx_omnia/engine/models/muse_glimmer/layers/block.py:39; checkpoint.py:86-91
-    n = rms_norm(x, w["norm.weight"], cfg["rms_norm_eps"])
+    if rows is not None:
+        x = x[rows]
+    n = rms_norm(x, w["norm.weight"], cfg["rms_norm_eps"], r)
     # A tied head reads the embedding table (the house's dense model does so:
     # src/mlx_omnia/engine/core/attention.py:792-796).
     lm = w["embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]

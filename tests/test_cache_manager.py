@@ -11,7 +11,7 @@ from mlx_omnia_b200.cache import CacheError, CacheManager, PagePool
 from mlx_omnia_b200.parts.base import KVSpec, StateSpec
 from mlx_omnia_b200.parts.model import CacheNeed
 
-FULL, WINDOW = KVSpec(2, 16, None), KVSpec(2, 16, 10)
+FULL, WINDOW = KVSpec.keys_and_values(2, 16, None), KVSpec.keys_and_values(2, 16, 10)
 
 
 def manager(pages=24, page_size=4, max_requests=4):

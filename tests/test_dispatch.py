@@ -15,24 +15,24 @@ def test_decode_plan_is_a_tile_multiple_within_bounds_and_the_same_for_a_bucket(
     for requests in (1, 3, 8, 17, 64, 100, 512):
         for nkv in (1, 3, 8):
             for longest in (1, 90, 128, 1000, 4096, 5000, 100000):
-                chunk, warps = ops.decode_plan(requests, nkv, longest)
+                chunk, warps = ops.decode_plan(requests, nkv, longest, 148)
                 assert 128 <= chunk <= 1024 and chunk % 64 == 0 and warps in (1, 4)
                 # A captured graph's batch is a power of two: same plan.
-                assert (chunk, warps) == ops.decode_plan(1 << (requests - 1).bit_length(), nkv, longest)
+                assert (chunk, warps) == ops.decode_plan(1 << (requests - 1).bit_length(), nkv, longest, 148)
 
 
 def test_decode_plan_grows_with_the_work():
     """Few pairs: short chunks and four warps a block, so that enough warps run; more pairs: one
     warp a block and the shortest chunk whose blocks the GPU holds at a time."""
-    assert ops.decode_plan(1, 8, 4096) == (256, 4)
-    assert ops.decode_plan(2, 8, 4096) == (256, 4)
-    assert ops.decode_plan(4, 8, 4096) == (192, 1)
-    assert ops.decode_plan(8, 8, 4096) == (320, 1)
-    assert ops.decode_plan(8, 8, 5120) == (448, 1)
-    assert ops.decode_plan(16, 8, 4096) == (704, 1)
-    assert ops.decode_plan(64, 8, 8192) == (1024, 1)
+    assert ops.decode_plan(1, 8, 4096, 148) == (256, 4)
+    assert ops.decode_plan(2, 8, 4096, 148) == (256, 4)
+    assert ops.decode_plan(4, 8, 4096, 148) == (192, 1)
+    assert ops.decode_plan(8, 8, 4096, 148) == (320, 1)
+    assert ops.decode_plan(8, 8, 5120, 148) == (448, 1)
+    assert ops.decode_plan(16, 8, 4096, 148) == (704, 1)
+    assert ops.decode_plan(64, 8, 8192, 148) == (1024, 1)
     # One long request: four warps a block, chunks so long that two blocks an SM hold them all.
-    chunk, warps = ops.decode_plan(1, 8, 32768)
+    chunk, warps = ops.decode_plan(1, 8, 32768, 148)
     assert warps == 4 and 8 * -(-32768 // chunk) <= 2 * 148
 
 

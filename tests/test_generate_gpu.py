@@ -145,3 +145,41 @@ def test_pipelined_decoding_gives_the_same_tokens(tmp_path):
         if options.sampler.greedy:
             cut = plain_ids.index(plain_ids[9]) if options.stop else 24
             assert results[1][0] == plain_ids[:cut]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_preemption_on_the_gpu(dtype):
+    """A pool too small for three requests at once: the newest is preempted, gives its pages
+    back, and later recomputes its prompt and what it had generated as one long portion beside
+    the others' decoded tokens, with captured graphs and pipelined steps on. In 32-bit the
+    sampled tokens are those of a roomy pool; in bfloat16 (where a different batch rounds
+    differently) every greedy token is the plain implementation's best or nearly so."""
+    from mlx_omnia_b200 import repetition_penalty
+    from mlx_omnia_b200.engine.engine import Engine, EngineArgs
+    from mlx_omnia_b200.engine.generate import Generator
+
+    raw, weights = tiny_configs.config("A"), tiny_configs.tensors("A")
+    prompts = [tiny_configs.prompt(n, 512, 60 + n) for n in (17, 9, 12)]
+    if dtype == "float32":
+        options = GenerationOptions(max_tokens=14, sampler=sampler(temperature(0.9), top_k(20), seed=11), stop=(),
+                                    penalty=repetition_penalty(1.3))
+    else:
+        options = GenerationOptions(max_tokens=14, stop=())
+    results = {}
+    for pool in (512, 56):
+        engine = Engine.from_tensors(raw, weights, EngineArgs(dtype=dtype, page_size=4, cache_tokens=pool, max_requests=4))
+        generator = Generator(engine)
+        assert generator.pipelined and engine.runner.graphs is not None
+        requests = [generator.add(p, options) for p in prompts]
+        generator.run()
+        results[pool] = [r.generated for r in requests]
+        assert (sum(r.preemptions for r in requests) > 0) == (pool == 56)
+        assert not engine.cache.requests and all(g.pool.free == g.pool.count for g in engine.cache.groups)
+        engine.cache.check()
+    if dtype == "float32":
+        assert results[56] == results[512]
+    else:
+        for prompt, ids in zip(prompts, results[56]):
+            logits = plain_impl.forward(raw, weights, prompt + ids)[len(prompt) - 1: -1]
+            chosen = logits[torch.arange(len(ids)), torch.tensor(ids)]
+            assert float((logits.max(dim=-1).values - chosen).max()) < 0.03 * float(logits.abs().max())

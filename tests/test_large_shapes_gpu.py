@@ -1,8 +1,11 @@
 """The benchmark's layer sizes (hidden 2048, 16/8 heads of 128, intermediate 6144, vocabulary
 151936, tied head; two layers only, to keep the test short) through every way of cutting: the
 bfloat16 engine, whose steps run on the tcgen05, skinny and decode kernels at their real shapes,
-against the engine's own true 32-bit path, and the 32-bit path against the plain implementation.
-One query is made to match a key hundreds of positions back, so a fault in a far page shows."""
+and its true 32-bit path, both against the plain implementation itself (run whole in float64 on
+the CPU, the head on the compared rows only). One query is made to match a key hundreds of
+positions back, so a fault in a far page shows. Then the head counts and widths of the two
+larger benchmark configurations (groups of 4 and 5 query heads, hidden 4096 and 5120; two layers,
+a short vocabulary), so that those groupings and the wide residual stream pass every cut too."""
 
 from __future__ import annotations
 
@@ -11,7 +14,7 @@ import copy
 import pytest
 import torch
 
-import plain_impl
+from floors import Oracle
 from mlx_omnia_b200.engine.engine import Engine, EngineArgs
 from mlx_omnia_b200.engine.step import StepEntry
 from mlx_omnia_b200.kernels import ops
@@ -47,8 +50,8 @@ def model():
     return tensors, ids
 
 
-def run(tensors, ids, dtype, cuts, wanted_from):
-    engine = Engine.from_tensors(copy.deepcopy(CONFIG), tensors, EngineArgs(dtype=dtype, page_size=16, cache_tokens=4096,
+def run(config, tensors, ids, dtype, cuts, wanted_from):
+    engine = Engine.from_tensors(copy.deepcopy(config), tensors, EngineArgs(dtype=dtype, page_size=16, cache_tokens=4096,
                                                                              max_requests=4))
     request = engine.cache.open("r")
     rows, at = [], 0
@@ -66,26 +69,56 @@ def run(tensors, ids, dtype, cuts, wanted_from):
     return out
 
 
+TAIL = 64  # the logits of the last 64 positions are compared
+
+
+def exact_and_tolerances(config, tensors, ids):
+    oracle = Oracle(config, tensors, {"r": ids}, rows=lambda all_ids: list(range(len(all_ids) - TAIL, len(all_ids))))
+    return oracle
+
+
+CUTS = {"whole": [LENGTH], "chunks": [512, 2, 301, 128, 7, LENGTH - 950 - 32] + [1] * 32,
+        "tail": [1000, 500 - 32] + [1] * 32}
+
+
 def test_every_cut_at_the_benchmark_sizes(model):
     tensors, ids = model
-    tail = LENGTH - 64  # compare the logits of the last 64 positions
-    whole = [LENGTH]
-    chunks = [512, 2, 301, 128, 7, LENGTH - 950 - 32] + [1] * 32
-    assert sum(chunks) == LENGTH
-    reference = run(tensors, ids, "float32", whole, tail)
-    cut32 = run(tensors, ids, "float32", chunks, tail)
-    assert plain_impl.relative_diff(cut32, reference) < 1e-4
+    oracle = exact_and_tolerances(CONFIG, tensors, ids)
     worst = {}
-    for name, cuts in (("whole", whole), ("chunks", chunks), ("tail", [1000, 500 - 32] + [1] * 32)):
-        got = run(tensors, ids, "bfloat16", cuts, tail)
-        worst[name] = plain_impl.relative_diff(got, reference)
-        assert (got.argmax(-1) == reference.argmax(-1)).float().mean() > 0.9, name
-    assert max(worst.values()) < 3e-2, worst
+    for dtype, names in (("float32", ("whole", "chunks")), ("bfloat16", ("whole", "chunks", "tail"))):
+        for name in names:
+            assert sum(CUTS[name]) == LENGTH
+            got = run(CONFIG, tensors, ids, dtype, CUTS[name], LENGTH - TAIL)
+            worst[dtype, name] = oracle.diff("r", got) / oracle.tolerance[dtype]
+    assert max(worst.values()) < 1.0, f"in units of the tolerance: {worst}"
 
 
-def test_32_bit_path_matches_plain_at_the_benchmark_widths(model):
-    tensors, ids = model
-    short = ids[:200]
-    expect = plain_impl.forward(CONFIG, tensors, short)[-16:]
-    got = run(tensors, short, "float32", [150, 34] + [1] * 16, 200 - 16)
-    assert plain_impl.relative_diff(got, expect) < 1e-4
+def larger(hidden, heads, inner):
+    raw = copy.deepcopy(CONFIG)
+    raw["text_config"].update(hidden_size=hidden, num_attention_heads=heads, intermediate_size=inner, vocab_size=8192,
+                              tie_word_embeddings=False, sliding_window=300)
+    return raw
+
+
+@pytest.mark.parametrize("hidden,heads,inner", [(4096, 32, 12288), (5120, 40, 17408)])
+def test_the_larger_configurations_head_counts_and_widths(hidden, heads, inner):
+    """Groups of 4 and 5 query heads per key/value head at head size 128, residual streams of
+    4,096 and 5,120: whole, in portions, and decoded one by one (the decode path of streams wider
+    than 2,048), in bfloat16 against the plain implementation."""
+    raw = larger(hidden, heads, inner)
+    architecture = resolve_architecture(raw)
+    tensors = architecture.random_tensors(architecture.parse(raw), 3)
+    tensors = {k: (t * (2.0 if "proj" in k else 1.0) if t.dim() == 2 else t) for k, t in tensors.items()}
+    tensors["lm_head.weight"] *= 20.0
+    tensors = {k: (t if t.dim() < 2 else t.bfloat16().float()) for k, t in tensors.items()}
+    g = torch.Generator().manual_seed(hidden)
+    length = 700
+    ids = torch.randint(0, 8192, (length,), generator=g).tolist()
+    ids[length - 20] = ids[333]
+    oracle = exact_and_tolerances(raw, tensors, ids)
+    worst = {}
+    for name, cuts in (("whole", [length]), ("chunks", [300, 2, 129, 7, length - 438 - 32] + [1] * 32)):
+        assert sum(cuts) == length
+        got = run(raw, tensors, ids, "bfloat16", cuts, length - TAIL)
+        worst[name] = oracle.diff("r", got) / oracle.tolerance["bfloat16"]
+    assert max(worst.values()) < 1.0, f"in units of the tolerance: {worst}"

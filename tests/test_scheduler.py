@@ -14,9 +14,9 @@ from mlx_omnia_b200.parts.model import CacheNeed
 
 
 def make(pages=16, page_size=4, max_requests=4, budget=16, window=None):
-    needs = [CacheNeed(KVSpec(1, 8, None), None, None)]
+    needs = [CacheNeed(KVSpec.keys_and_values(1, 8, None), None, None)]
     if window:
-        needs.append(CacheNeed(KVSpec(1, 8, window), None, None))
+        needs.append(CacheNeed(KVSpec.keys_and_values(1, 8, window), None, None))
     cache = CacheManager(needs, page_size=page_size, pages_per_group=pages, max_requests=max_requests, allocate=False)
     return Scheduler(cache, max_tokens_per_step=budget), cache
 

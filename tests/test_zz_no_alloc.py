@@ -34,7 +34,7 @@ def test_static_scratch_entry_point_matches_the_allocating_one(monkeypatch):
 
     # The ordinary entry point picks its chunk and warps per block from the batch; held to the
     # chunk and the single warp that this test gives the static one, the two add in the same order.
-    monkeypatch.setattr(ops, "decode_plan", lambda requests, nkv, longest, sms=148: (ops.DECODE_CHUNK, 1))
+    monkeypatch.setattr(ops, "decode_plan", lambda requests, nkv, longest, sms: (ops.DECODE_CHUNK, 1))
 
     device = torch.device("cuda:0")
     torch.cuda.set_device(device)
@@ -46,7 +46,7 @@ def test_static_scratch_entry_point_matches_the_allocating_one(monkeypatch):
     reason = library.omnia_attention_static_error
     reason.restype = c_char_p
 
-    nq, nkv, page, window = 6, 3, 16, None
+    nq, nkv, page = 6, 3, 16
     generator = torch.Generator(device="cuda").manual_seed(77)
 
     def rand(*shape, scale=1.0):
@@ -55,7 +55,8 @@ def test_static_scratch_entry_point_matches_the_allocating_one(monkeypatch):
     def int32(values):
         return torch.tensor(values, dtype=torch.int32, device=device)
 
-    for seq_lens in ([1, 130, 700, 257], [513, 64, 5, 129, 1000]):  # two calls in a row, different shapes
+    # Two calls in a row, of different shapes; the second with a window of 200 positions.
+    for seq_lens, window in (([1, 130, 700, 257], None), ([513, 64, 5, 129, 1000], 200)):
         batch = len(seq_lens)
         need = [-(-n // page) for n in seq_lens]
         num_pages = sum(need) + 3
@@ -79,7 +80,7 @@ def test_static_scratch_entry_point_matches_the_allocating_one(monkeypatch):
         stream = torch.cuda.current_stream().cuda_stream
         code = entry(q.data_ptr(), pages.data_ptr(), table.data_ptr(), step.cu_seqlens.data_ptr(),
                      step.seq_lens.data_ptr(), None, batch, ops.DECODE_CHUNK, max_chunks, gate.data_ptr(),
-                     gate.shape[1], out.data_ptr(), table.shape[1], num_pages, nq, nkv, page, 0, scale,
+                     gate.shape[1], out.data_ptr(), table.shape[1], num_pages, nq, nkv, page, window or 0, scale,
                      ops.error_word(device).data_ptr(), stream)
         assert code == 0, reason().decode()
         torch.cuda.synchronize()
@@ -97,5 +98,16 @@ def test_static_scratch_entry_point_matches_the_allocating_one(monkeypatch):
                  table.shape[1], num_pages, nq, nkv, page, 0, scale, ops.error_word(device).data_ptr(),
                  torch.cuda.current_stream().cuda_stream)
     assert code == -2 and b"static scratch holds" in reason()
+    torch.cuda.synchronize()
+    assert float(out.abs().max()) == 0.0
+
+    # Arguments that would make the kernel divide by zero or index before its buffers are
+    # refused with a reason, and nothing is launched.
+    for requests, chunk in ((-1, ops.DECODE_CHUNK), (batch, 0), (batch, -128), (batch, 100)):
+        code = entry(q.data_ptr(), pages.data_ptr(), table.data_ptr(), step.cu_seqlens.data_ptr(),
+                     step.seq_lens.data_ptr(), None, requests, chunk, 8, None, 0, out.data_ptr(),
+                     table.shape[1], num_pages, nq, nkv, page, 0, scale, ops.error_word(device).data_ptr(),
+                     torch.cuda.current_stream().cuda_stream)
+        assert code == 1 and reason(), (requests, chunk)  # cudaErrorInvalidValue
     torch.cuda.synchronize()
     assert float(out.abs().max()) == 0.0

@@ -50,15 +50,30 @@ class Trace:
         for rid in end:
             del self.held[rid]
 
+    def text(self) -> str:
+        return "".join(json.dumps(s) + "\n" for s in self.steps)
+
     def run(self, model: Path, dtype: str, out: Path, max_tokens: int | None = None, extra: list[str] = ()) -> dict:
         """Replay through bin/trace_run; returns {request: {position: logits}}."""
-        text = "".join(json.dumps(s) + "\n" for s in self.steps)
         command = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(model), "--dtype", dtype,
                    "--out", str(out), "--max-tokens", str(max_tokens or self.peak), *extra]
-        done = subprocess.run(command, input=text, capture_output=True, text=True, timeout=600)
+        done = subprocess.run(command, input=self.text(), capture_output=True, text=True, timeout=600)
         assert done.returncode == 0, done.stderr[-4000:]
         assert done.stdout.split() == [w for s in self.steps for w in ("done", str(s["step"]))], done.stdout[-2000:]
         vocab = json.loads((model / "config.json").read_text())["text_config"]["vocab_size"]
+        return self.gather(out, vocab)
+
+    def run_engine(self, engine, out: Path, before_step=None) -> dict:
+        """Replay in this process through the package's own replay loop over `engine` (what
+        bin/trace_run does after loading); `before_step(engine, record)` runs ahead of every step."""
+        import io
+
+        from mlx_omnia_b200.engine.trace import replay
+
+        replay(engine, io.StringIO(self.text()), out, done=io.StringIO(), before_step=before_step)
+        return self.gather(out, engine.vocab_size)
+
+    def gather(self, out: Path, vocab: int) -> dict:
         got: dict[str, dict[int, torch.Tensor]] = {}
         for index, rows in enumerate(self.where):
             if not rows:
