@@ -116,3 +116,31 @@ def test_random_orders_lose_nothing(seed):
         m.close(name)
     m.check()
     assert all(g.pool.free == g.pool.count for g in m.groups) and m.slots.free == 4 and slots_seen <= {0, 1, 2, 3}
+
+
+def test_rows_of_any_shape_and_a_stride_size_their_own_pages():
+    """A group's pages are made from what its entries say they keep per position: two equal rows
+    (keys and values), one latent row, rows of unequal width, or a row for every fourth position."""
+    import torch
+
+    latent = KVSpec(((1, 12),))
+    uneven = KVSpec(((2, 16), (2, 8)), window=None)
+    sparse = KVSpec(((1, 6),), stride=4)
+    needs = [CacheNeed(FULL, None, None), CacheNeed(latent, None, None), CacheNeed(uneven, None, None),
+             CacheNeed(sparse, None, None)]
+    m = CacheManager(needs, page_size=4, pages_per_group=10, max_requests=2, dtype=torch.float32, device="cpu")
+    assert [tuple(g.pages.shape) for g in m.groups] == [(1, 10, 2, 2, 4, 16), (1, 10, 1, 1, 4, 12),
+                                                       (1, 10, 4 * (2 * 16 + 2 * 8)), (1, 10, 1, 1, 4, 6)]
+    assert CacheManager.bytes_per_token(needs, 2) == 2 * (64 + 12 + 48 + 2)  # the sparse row: 6 / 4, rounded up
+    assert m.capacity_tokens() == 40
+    r = m.open("r")
+    assert m.pages_needed(r, 17) == [5, 5, 5, 2]  # 17 positions: five pages of four rows; 5 sparse rows: two
+    m.grow(r, 17)
+    assert [len(t) for t in r.tables] == [5, 5, 5, 2]
+    assert m.pages_needed(r, 3) == [0, 0, 0, 0] and m.pages_needed(r, 16) == [4, 4, 4, 1]
+    assert m.slot_of(r, 3, 13) == r.tables[3][0] * 4 + 3 and m.slot_of(r, 3, 16) == r.tables[3][1] * 4
+    m.check()
+    m.close("r")
+    assert all(g.pool.free == 10 for g in m.groups)
+    with pytest.raises(ValueError, match="positive"):
+        KVSpec(())

@@ -146,6 +146,37 @@ def test_paged_attention(ops, dtype, nq, nkv, d, page, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(6, 3, 128, 16, 33), (16, 8, 64, 16, 20), (6, 3, 128, 16, None),
+                                                   (4, 2, 128, 32, 100), (8, 1, 24, 8, 16), (5, 5, 40, 4, 70)])
+def test_prefill_attention_at_a_window_s_edge_with_nan_elsewhere(ops, dtype, nq, nkv, d, page, window):
+    """Prompt portions that start at, inside and past a 64-key tile edge, with a window whose
+    first key falls inside a tile and inside a page. Everything a request may not read holds
+    NaN: free pages, the unwritten tail of each request's last page, and the pages wholly
+    behind the window, whose block-table entries are -1 as the cache manager leaves them. One
+    key too many at either edge of the window is a NaN in the output."""
+    q_lens, seq_lens = [40, 30, 50, 2, 64, 1, 17], [104, 100, 180, 67, 64, 90, 33]
+    step = step_of(q_lens, seq_lens)
+    pages, table = make_kv(seq_lens, nkv, d, page, dtype, 8 + sum(-(-n // page) for n in seq_lens), seed=21)
+    pages.fill_(float("nan"))
+    for s, (q, n) in enumerate(zip(q_lens, seq_lens)):
+        dead_below = n - q - window + 1 if window else 0  # no token of this step sees positions below this
+        for first in range(0, n, page):
+            if first + page <= dead_below:
+                table[s, first // page] = -1
+                continue
+            count = min(page, n - first)
+            pages[int(table[s, first // page]), :, :, :count, :] = rand(2, nkv, count, d, dtype=dtype, seed=100 * s + first)
+    q = rand(step.num_tokens, nq, d, dtype=dtype, seed=31)
+    gate = rand(step.num_tokens, nq * d, dtype=dtype, seed=32)
+    view = KVView(pages, table, torch.zeros(step.num_tokens, dtype=torch.int64, device="cuda"), page, window)
+    scale = 1.1 * d ** -0.5
+    got = ops.paged_attention(q, view, step, scale, gate=gate)
+    assert not torch.isnan(got).any()
+    close(got, kernel_refs.paged_attention(q, view, step, scale, gate=gate), dtype)
+    ops.raise_on_error(q.device)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,d,page,window", [(4, 2, 16, 4, None), (8, 1, 24, 8, 16), (6, 3, 128, 16, None),
                                                    (6, 3, 128, 16, 200), (5, 5, 40, 3, 130), (16, 8, 64, 16, None),
                                                    (10, 2, 96, 16, None), (16, 1, 128, 32, 300), (4, 4, 64, 64, 70),

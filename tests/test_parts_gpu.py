@@ -15,7 +15,8 @@ from mlx_omnia_b200.engine.engine import Engine, EngineArgs
 from mlx_omnia_b200.engine.step import StepEntry, StepRunner
 from mlx_omnia_b200.parts import (DecoderModel, LayerSpec, ModelSpec, PartSpec, Runtime, ScheduleEntry, StateSpec,
                                   register_mixer)
-from mlx_omnia_b200.parts.base import FEED_FORWARDS, HEADS, EMBEDDINGS, MIXERS, NORMS, POSITIONS, Mixer, TensorSpec
+from mlx_omnia_b200.parts.base import (FEED_FORWARDS, HEADS, EMBEDDINGS, MIXERS, NORMS, POSITIONS, Embedding, KVSpec,
+                                       Mixer, TensorSpec, register_embedding)
 from mlx_omnia_b200.architectures.muse_glimmer import model_spec, parse
 
 pytestmark = pytest.mark.gpu
@@ -134,19 +135,28 @@ def test_schedule_is_data(schedule, dtype):
     assert plain_impl.relative_diff(got, expect) < (1e-4 if dtype == torch.float32 else 3e-2)
 
 
-# ---- a toy mixer with state of its own, defined here --------------------------------------
+# ---- toy parts, defined here: none of them is a change to the framework's files ---------------
+# A mixer with state of its own (and a start that is not zero), a mixer that keeps one latent
+# row per token in the paged cache instead of keys and values, and an embedding that adds a
+# learned absolute position encoding. They never become anyone's model.
 
 
 @register_mixer("toy_decay_mixer")
 class ToyDecayMixer(Mixer):
-    """s_t = decay * s_{t-1} + h_t W_in ; out_t = s_t W_out. Its state is one vector per
-    request, kept in a state slot between steps; it keeps no pages."""
+    """s_t = decay * s_{t-1} + h_t W_in ; out_t = s_t W_out, with s_{-1} = start. Its state is
+    one vector per request, kept in a state slot between steps; it keeps no pages. A step of
+    single tokens touches no host memory, so it can be captured into a graph."""
 
-    def __init__(self, hidden: int, width: int, decay: float) -> None:
-        self.hidden, self.width, self.decay = hidden, width, decay
+    graph_safe = True
+
+    def __init__(self, hidden: int, width: int, decay: float, start: float = 0.0) -> None:
+        self.hidden, self.width, self.decay, self.start = hidden, width, decay, start
 
     def state_spec(self):
         return StateSpec((self.width,), torch.float32)
+
+    def initial_state(self):
+        return torch.full((self.width,), self.start) if self.start else None
 
     def tensors(self):
         return {"in_proj.weight": TensorSpec((self.width, self.hidden)), "out_proj.weight": TensorSpec((self.hidden, self.width))}
@@ -157,71 +167,153 @@ class ToyDecayMixer(Mixer):
 
     def forward(self, h, ctx):
         u = (h.float() @ self.w_in.float().t())
-        out = torch.empty_like(u)
-        slots = ctx.step.state_slots.tolist()
-        start = 0
-        for slot, count in zip(slots, ctx.step.q_lens):
-            state = ctx.state[slot]
-            for t in range(start, start + count):
-                state = self.decay * state + u[t]
-                out[t] = state
-            ctx.state[slot] = state
-            start += count
+        if ctx.step.decode_only:
+            # One token per request (padding rows of a captured step point at the scratch slot).
+            slots = ctx.step.state_slots.long()
+            out = self.decay * ctx.state[slots] + u
+            ctx.state[slots] = out
+        else:
+            out = torch.empty_like(u)
+            start = 0
+            for slot, count in zip(ctx.step.state_slots.tolist(), ctx.step.q_lens):
+                state = ctx.state[slot]
+                for t in range(start, start + count):
+                    state = self.decay * state + u[t]
+                    out[t] = state
+                ctx.state[slot] = state
+                start += count
         return (out @ self.w_out.float().t()).to(h.dtype)
+
+
+@register_mixer("toy_latent_mixer")
+class ToyLatentMixer(Mixer):
+    """Keeps ONE row of `latent` numbers per token in the paged cache (no keys and values): c_t =
+    h_t W_c; the output at t is softmax_j<=t(q_t . c_j / 4) weighted sum of the c_j, projected."""
+
+    def __init__(self, hidden: int, latent: int) -> None:
+        self.hidden, self.latent = hidden, latent
+
+    def kv_spec(self):
+        return KVSpec(((1, self.latent),))
+
+    def tensors(self):
+        return {"c_proj.weight": TensorSpec((self.latent, self.hidden)), "q_proj.weight": TensorSpec((self.latent, self.hidden)),
+                "o_proj.weight": TensorSpec((self.hidden, self.latent))}
+
+    def load(self, tensors, runtime):
+        super().load(tensors, runtime)
+        self.w = {k: v.float() for k, v in tensors.items()}
+
+    def forward(self, h, ctx):
+        kv, step = ctx.kv, ctx.step
+        c = h.float() @ self.w["c_proj.weight"].t()
+        q = h.float() @ self.w["q_proj.weight"].t()
+        rows = kv.row(0)  # [pages, 1, page_size, latent]
+        assert kv.pages.shape[1:] == (1, 1, kv.page_size, self.latent)
+        flat = rows.reshape(-1, self.latent)  # slot = page * page_size + offset, one head
+        flat[kv.slot_mapping] = c.to(flat.dtype)
+        out = torch.empty_like(c)
+        start = 0
+        for s, (count, held) in enumerate(zip(step.q_lens, step.seq_lens_host)):
+            table = kv.block_table[s].long()
+            js = torch.arange(held, device=h.device)
+            cached = flat[table[js // kv.page_size] * kv.page_size + js % kv.page_size].float()
+            for t in range(count):
+                seen = cached[: held - count + t + 1]
+                out[start + t] = torch.softmax(seen @ q[start + t] / 4.0, dim=0) @ seen
+            start += count
+        return (out @ self.w["o_proj.weight"].t()).to(h.dtype)
+
+
+@register_embedding("toy_absolute_embedding")
+class ToyAbsoluteEmbedding(Embedding):
+    """x = table[id] + place[position]: a learned absolute position encoding."""
+
+    def __init__(self, vocab: int, hidden: int, places: int) -> None:
+        self.vocab, self.hidden, self.places = vocab, hidden, places
+
+    def tensors(self):
+        return {"weight": TensorSpec((self.vocab, self.hidden)), "place": TensorSpec((self.places, self.hidden))}
+
+    def load(self, tensors, runtime):
+        super().load(tensors, runtime)
+        self.weight, self.place = tensors["weight"], tensors["place"]
+
+    def forward(self, token_ids, positions):
+        return self.weight[token_ids.long()].float() + self.place[positions.clamp_min(0).long()].float()
+
+
+START = 0.25
 
 
 def toy_spec(hidden=32, vocab=50):
     norm = PartSpec("rms_norm", {"size": hidden, "eps": 1e-6, "weight": "plain"})
     ff = PartSpec("gated_mlp", {"hidden": hidden, "inner": 48})
-    toy = PartSpec("pre_norm", {"mixer": PartSpec("toy_decay_mixer", {"hidden": hidden, "width": 24, "decay": 0.9}),
-                                "feed_forward": ff, "norms": {"input_layernorm": norm, "post_attention_layernorm": norm},
-                                "mixer_name": "mixer"})
+    norms = {"input_layernorm": norm, "post_attention_layernorm": norm}
+    toy = PartSpec("pre_norm", {"mixer": PartSpec("toy_decay_mixer", {"hidden": hidden, "width": 24, "decay": 0.9,
+                                                                      "start": START}),
+                                "feed_forward": ff, "norms": norms, "mixer_name": "mixer"})
+    latent = PartSpec("pre_norm", {"mixer": PartSpec("toy_latent_mixer", {"hidden": hidden, "latent": 12}),
+                                   "feed_forward": ff, "norms": norms, "mixer_name": "mixer"})
     attention = PartSpec("pre_norm", {"mixer": PartSpec("gqa_attention", {
         "hidden": hidden, "heads": 2, "kv_heads": 1, "head_dim": 16, "scale": 0.25,
-        "position": PartSpec("rotary", {"dims": 8, "theta": 100.0})}), "feed_forward": ff,
-        "norms": {"input_layernorm": norm, "post_attention_layernorm": norm}})
-    return ModelSpec(PartSpec("token_embedding", {"vocab": vocab, "hidden": hidden}),
-                     (LayerSpec(toy, "layers.0"), LayerSpec(attention, "layers.1")),
-                     (ScheduleEntry(0), ScheduleEntry(1)), norm, PartSpec("lm_head", {"vocab": vocab, "hidden": hidden}),
+        "position": PartSpec("rotary", {"dims": 8, "theta": 100.0})}), "feed_forward": ff, "norms": norms})
+    return ModelSpec(PartSpec("toy_absolute_embedding", {"vocab": vocab, "hidden": hidden, "places": 64}),
+                     (LayerSpec(toy, "layers.0"), LayerSpec(latent, "layers.1"), LayerSpec(attention, "layers.2")),
+                     (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2)), norm,
+                     PartSpec("lm_head", {"vocab": vocab, "hidden": hidden}),
                      embedding_prefix="embed", final_norm_prefix="final_norm", head_prefix="head")
 
 
-def toy_plain(w, ids):
-    """The toy model, whole sequence, plain PyTorch."""
-    x = w["embed.weight"][ids]
-    rms = lambda v, name: plain_impl.rms_norm(v, w[name], 1e-6)
-    h = rms(x, "layers.0.input_layernorm.weight")
-    u = h @ w["layers.0.mixer.in_proj.weight"].t()
-    state, rows = torch.zeros(24), []
-    for t in range(len(ids)):
-        state = 0.9 * state + u[t]
-        rows.append(state)
-    x = x + torch.stack(rows) @ w["layers.0.mixer.out_proj.weight"].t()
-    x = x + plain_impl.swiglu(rms(x, "layers.0.post_attention_layernorm.weight"), plain_impl.sub(w, "layers.0.mlp."))
-    h = rms(x, "layers.1.input_layernorm.weight")
+def toy_plain(w, ids, layout=(("decay", "layers.0"), ("latent", "layers.1"), ("attention", "layers.2"))):
+    """The toy model, whole sequence, plain PyTorch; `layout` lists its layers' mixers in order."""
     positions = torch.arange(len(ids))
-    a = plain_impl.sub(w, "layers.1.self_attn.")
-    q = (h @ a["q_proj.weight"].t()).reshape(-1, 2, 16)
-    k = (h @ a["k_proj.weight"].t()).reshape(-1, 1, 16)
-    v = (h @ a["v_proj.weight"].t()).reshape(-1, 1, 16)
-    rot = lambda z: torch.cat([plain_impl.rope(z[..., :8], positions, 100.0), z[..., 8:]], dim=-1)
-    att = plain_impl.attention_core(rot(q), rot(k), v, plain_impl.visible(positions, positions, None), 0.25)
-    x = x + att @ a["o_proj.weight"].t()
-    x = x + plain_impl.swiglu(rms(x, "layers.1.post_attention_layernorm.weight"), plain_impl.sub(w, "layers.1.mlp."))
+    x = w["embed.weight"][ids] + w["embed.place"][positions]
+    rms = lambda v, name: plain_impl.rms_norm(v, w[name], 1e-6)
+    causal = plain_impl.visible(positions, positions, None)
+    for kind, prefix in layout:
+        h = rms(x, f"{prefix}.input_layernorm.weight")
+        if kind == "decay":
+            u = h @ w[f"{prefix}.mixer.in_proj.weight"].t()
+            state, rows = torch.full((24,), START), []
+            for t in range(len(ids)):
+                state = 0.9 * state + u[t]
+                rows.append(state)
+            x = x + torch.stack(rows) @ w[f"{prefix}.mixer.out_proj.weight"].t()
+        elif kind == "latent":
+            m = plain_impl.sub(w, f"{prefix}.mixer.")
+            c, q = h @ m["c_proj.weight"].t(), h @ m["q_proj.weight"].t()
+            scores = (q @ c.t() / 4.0).masked_fill(~causal, float("-inf"))
+            x = x + (torch.softmax(scores, dim=-1) @ c) @ m["o_proj.weight"].t()
+        else:
+            a = plain_impl.sub(w, f"{prefix}.self_attn.")
+            q = (h @ a["q_proj.weight"].t()).reshape(-1, 2, 16)
+            k = (h @ a["k_proj.weight"].t()).reshape(-1, 1, 16)
+            v = (h @ a["v_proj.weight"].t()).reshape(-1, 1, 16)
+            rot = lambda z: torch.cat([plain_impl.rope(z[..., :8], positions, 100.0), z[..., 8:]], dim=-1)
+            x = x + plain_impl.attention_core(rot(q), rot(k), v, causal, 0.25) @ a["o_proj.weight"].t()
+        x = x + plain_impl.swiglu(rms(x, f"{prefix}.post_attention_layernorm.weight"), plain_impl.sub(w, f"{prefix}.mlp."))
     return rms(x, "final_norm.weight") @ w["head.weight"].t()
 
 
-def test_toy_mixer_with_state_is_registered_built_and_stepped():
-    spec = toy_spec()
-    model = DecoderModel(spec)
+def toy_model():
+    model = DecoderModel(toy_spec())
     g = torch.Generator().manual_seed(4)
     w = {name: (torch.randn(*s.shape, generator=g) * (0.2 if s.kind == "matrix" else 0.1) + (s.kind == "vector"))
          for name, s in model.tensors().items()}
     rt = runtime()
     model.load({k: v.to(CUDA) for k, v in w.items()}, rt)
+    return model, w, rt
+
+
+def test_toy_parts_are_registered_built_and_stepped():
+    model, w, rt = toy_model()
     needs = model.cache_needs()
-    assert needs[0].kv is None and needs[0].state == StateSpec((24,)) and needs[1].kv is not None
+    assert needs[0].kv is None and needs[0].state == StateSpec((24,)) and needs[0].initial_state is not None
+    assert needs[1].kv == KVSpec(((1, 12),)) and needs[2].kv == KVSpec.keys_and_values(1, 16)
     cache = CacheManager(needs, page_size=4, pages_per_group=24, max_requests=2, dtype=torch.float32, device=CUDA)
+    assert len(cache.groups) == 2  # the latent rows and the keys and values have pages of their own
+    assert cache.groups[0].pages.shape == (1, 24, 1, 1, 4, 12) and cache.groups[1].pages.shape == (1, 24, 2, 1, 4, 16)
     runner = StepRunner(model, cache, rt)
     a, b = tiny_configs.prompt(21, 50, 1), tiny_configs.prompt(14, 50, 2)
     ra, rb = cache.open("a"), cache.open("b")
@@ -234,8 +326,40 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     got_a.append(mixed[6:])
     assert plain_impl.relative_diff(torch.cat(got_a), toy_plain(w, a)) < 2e-5
     assert plain_impl.relative_diff(torch.cat(got_b), toy_plain(w, b)) < 2e-5
-    # a slot that is reused starts from zero state again
+    # a slot that is reused starts from the mixer's initial state again
     cache.close("a")
     rc = cache.open("c")
     again = runner.run([StepEntry(rc, a, list(range(21)))])
     assert plain_impl.relative_diff(again, toy_plain(w, a)) < 2e-5
+    cache.check()
+
+
+def test_a_toy_mixer_with_state_decodes_from_a_captured_graph():
+    """Three requests decode from a graph made for four: the padding row points at the scratch
+    state slot, so no live request's state is touched by it."""
+    spec = toy_spec()
+    # Without the latent layer, whose toy mixer loops over requests on the host.
+    spec = ModelSpec(spec.embedding, (spec.layers[0], spec.layers[2]), (ScheduleEntry(0), ScheduleEntry(1)),
+                     spec.final_norm, spec.head, embedding_prefix="embed", final_norm_prefix="final_norm",
+                     head_prefix="head")
+    model = DecoderModel(spec)
+    g = torch.Generator().manual_seed(9)
+    w = {name: (torch.randn(*s.shape, generator=g) * (0.2 if s.kind == "matrix" else 0.1) + (s.kind == "vector"))
+         for name, s in model.tensors().items()}
+    rt = runtime()
+    model.load({k: v.to(CUDA) for k, v in w.items()}, rt)
+
+    plain = lambda ids: toy_plain(w, ids, layout=(("decay", "layers.0"), ("attention", "layers.2")))
+
+    cache = CacheManager(model.cache_needs(), page_size=4, pages_per_group=64, max_requests=4, dtype=torch.float32,
+                         device=CUDA)
+    runner = StepRunner(model, cache, rt, cuda_graphs=True)
+    assert runner.graphs is not None
+    prompts = [tiny_configs.prompt(n, 50, 20 + n) for n in (17, 30, 9)]
+    requests = [cache.open(f"r{i}") for i in range(3)]
+    runner.run([StepEntry(r, p[:-5], []) for r, p in zip(requests, prompts)])
+    rows = [runner.run([StepEntry(r, [p[len(p) - 5 + k]], [0]) for r, p in zip(requests, prompts)]) for k in range(5)]
+    assert runner.graphs.replays == 5
+    got = torch.stack(rows)  # [5, 3, vocab]
+    for i, p in enumerate(prompts):
+        assert plain_impl.relative_diff(got[:, i], plain(p)[-5:]) < 2e-5, i
