@@ -241,7 +241,8 @@ def run(args) -> dict:
     # tables are as wide as the graph's bucket, not as the requests' own.
     graphs = getattr(engine.runner, "graphs", None)
     bucket = 1 << max(args.batch - 1, 0).bit_length()
-    copied = [c.host.nbytes for c in graphs.captured.values() if c.batch == bucket] if graphs is not None else []
+    copied = [c.host_tensor.numel() * 4 for c in graphs.captured.values() if c.layout.seqs == bucket] \
+        if graphs is not None else []
     if copied:
         h2d = int(max(copied))
     return {

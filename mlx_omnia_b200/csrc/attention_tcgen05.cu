@@ -7,12 +7,18 @@
 // so one block's softmax overlaps the other's matrix products):
 //   S = Q K^T   tcgen05.mma (M 128, N 64) over the head size, accumulator in tensor memory
 //   softmax     four warps, one thread per row: tcgen05.ld the scores, mask, running maximum and
-//               sum in float32, exp2, P rounded to bfloat16 into shared memory (128-byte swizzle)
-//   O += P V    tcgen05.mma (M 128, N head size) over the tile's keys, accumulator in tensor memory;
-//               when a row's maximum grows its accumulator is rescaled in tensor memory first
+//               sum in float32, exp2, P rounded to bfloat16 and stored (tcgen05.st) over the scores
+//               it came from: the score accumulator is double-buffered, so P of one tile and S of
+//               the next never share columns, and a tile's softmax need not wait for the product
+//               of the tile before
+//   O += P V    tcgen05.mma (M 128, N head size) over the tile's keys, P read from tensor memory,
+//               accumulator in tensor memory. The exponent's offset follows a row's maximum lazily:
+//               it moves (and the accumulator is rescaled in tensor memory, after the products so
+//               far) only when the maximum has grown by more than 2^8 since, which after the first
+//               tiles is rare; until then P simply exceeds 1, which float32 sums do not mind
 // Warps 0 (K) and 6 (V) feed the rings of K and V stages with TMA, one box of 16 keys x 64 dims per page
-// group (the block table is read there; page sizes must be multiples of 16); warp 1 issues the
-// MMAs; warps 2-5 are the softmax and the epilogue (normalise, optional sigmoid gate, store). The score
+// group (the block table is read there; page sizes must be multiples of 16); warps 1 and 7 issue the
+// two kinds of MMA; warps 2-5 are the softmax and the epilogue (normalise, optional sigmoid gate, store). The score
 // accumulator is double-buffered, so S of the next tile is computed while this tile's softmax runs.
 // Key groups whose page is not loaded (beyond the request, or given back behind a window) are
 // masked in S and skipped in P V, so stale shared memory never reaches the arithmetic; the rows
@@ -47,19 +53,20 @@ constexpr int DH = D / 64;                 // 64-wide halves of a head
 constexpr int BM = 128, BN = 64;      // rows per block, keys per tile
 constexpr int TOKENS = BM / GROUP;         // tokens per block
 constexpr int ROWS = TOKENS * GROUP;       // rows in use (<= 128)
-constexpr int KV_STAGES = 2;
-constexpr int THREADS = 224;  // warps: 0 K producer, 1 MMA issuer, 2-5 softmax, 6 V producer
+constexpr int K_STAGES = 2, V_STAGES = 3;
+static_assert(K_STAGES == 2, "a K stage is freed by the score buffer of the same index");  // ring depths (a K stage is free once its scores are computed, a V stage
+                                           // only after its product, two tiles later: V needs the deeper ring)
+constexpr int THREADS = 256;  // warps: 0 K producer, 1 issuer of Q K^T, 2-5 softmax, 6 V producer, 7 issuer of P V
 constexpr uint32_t HALF_BYTES = 128 * 128;           // 128 rows of 128 bytes
 constexpr uint32_t Q_BYTES = DH * HALF_BYTES;
-constexpr uint32_t P_BYTES = HALF_BYTES;             // 128 rows x 64 keys
 constexpr uint32_t TILE_HALF = BN * 128;             // 64 keys of 128 bytes
 constexpr uint32_t K_BYTES = DH * TILE_HALF, V_BYTES = DH * TILE_HALF;
-constexpr uint32_t STAGE_BYTES = K_BYTES + V_BYTES;
 constexpr uint32_t GROUP_BYTES = 16 * 128;           // one TMA box: 16 keys x 64 dims
 constexpr uint32_t TMEM_COLS = 256;                  // two blocks share an SM's 512 columns
 constexpr uint32_t S_COL = 0, O_COL = 128;
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RESCALE_STEP = 8.f;  // log2 of how far a row's maximum may outgrow its exponent offset
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -83,11 +90,20 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait; false when the block is giving up (its own limit, or another role's).
-// 1 / (1 + e^-x) from the hardware's exponential and reciprocal (a few units in the last place of
-// float32, far below the bfloat16 the result is rounded to). The exact expf and division are some
-// forty instructions an element; unrolled over a row they made the epilogue a 5,000-instruction
-// stretch that every warp ran once, and the block spent 12 to 25 us fetching it.
-__device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+// 1 / (1 + e^-x) = (1 + tanh(x / 2)) / 2 for a pair of bfloat16 gate values, from the hardware's
+// packed tanh: one trip to the special-function unit per PAIR, the result rounded to bfloat16 (the
+// reference, too, rounds the gate's sigmoid to the activations' type before it multiplies:
+// src/mlx_omnia/engine/core/attention.py:673-681). That unit is what the epilogue waits for: the
+// softmax of the block next door keeps it three quarters busy, and an operation that should take a
+// warp 8 cycles takes 40 to 80 there. Of a block's 5.6 us of epilogue the sigmoids are 2.9 and the
+// gate's reads from shared memory 1.3 (an exponential and a reciprocal per value: 6.3 us in all).
+__device__ __forceinline__ float2 sigmoid_pair(uint32_t gates) {
+  const __nv_bfloat162 half = __floats2bfloat162_rn(0.5f, 0.5f);
+  const __nv_bfloat162 x = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&gates), half);
+  uint32_t t;
+  asm("tanh.approx.bf16x2 %0, %1;" : "=r"(t) : "r"(*reinterpret_cast<const uint32_t*>(&x)));
+  return __bfloat1622float2(__hfma2(*reinterpret_cast<const __nv_bfloat162*>(&t), half, half));
+}
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
@@ -139,6 +155,15 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t 
       ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(instr), "r"(accumulate)
       : "memory");
 }
+// The same with the A operand in tensor memory (rows on the lanes, two 16-bit elements per column).
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t instr, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(instr), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -152,6 +177,11 @@ __device__ __forceinline__ void tmem_load32(uint32_t addr, uint32_t* v) {
         "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
         "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(addr));
+}
+__device__ __forceinline__ void tmem_load8(uint32_t addr, uint32_t* v) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "r"(addr));
 }
 __device__ __forceinline__ void tmem_store32(uint32_t addr, const uint32_t* v) {
   asm volatile(
@@ -186,7 +216,7 @@ __device__ __forceinline__ void stamp(int slot) {
 
 }  // namespace
 
-// grid (blocks of the work list); 192 threads. work[b] = (request, first token of the block among
+// grid (blocks of the work list); THREADS threads. work[b] = (request, first token of the block among
 // the request's tokens of this step, key/value head); the caller lists the longest blocks first.
 __global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
@@ -204,13 +234,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     return;
   }
   unsigned char* q_s = smem_raw;
-  unsigned char* p_s = q_s + Q_BYTES;
-  unsigned char* kv_s = p_s + P_BYTES;  // KV_STAGES x (K, V)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + KV_STAGES * STAGE_BYTES);
-  // bars: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11 p_full | 12 o_done | 13 g_full
+  unsigned char* k_s = q_s + Q_BYTES;            // K_STAGES tiles of keys
+  unsigned char* v_s = k_s + K_STAGES * K_BYTES;  // V_STAGES tiles of values
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + V_STAGES * V_BYTES);
+  // bars: q_full | k_full[2] | v_full[3] | v_done[3] | s_full[2] | p_full[2] | g_full
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
-  volatile uint32_t* group_mask = reinterpret_cast<volatile uint32_t*>(tmem_holder + 2);  // [KV_STAGES]
+  volatile uint32_t* group_mask = reinterpret_cast<volatile uint32_t*>(tmem_holder + 2);  // [V_STAGES]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq = work[3 * blockIdx.x], tok0 = work[3 * blockIdx.x + 1], kvh = work[3 * blockIdx.x + 2];
@@ -223,19 +253,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int tile0 = first / BN, n_tiles = last / BN - tile0 + 1;
 
   const uint32_t bar0 = smem_u32(bars);
-  const uint32_t q_full = bar0, k_full0 = bar0 + 8, k_empty0 = bar0 + 24, v_full0 = bar0 + 40,
-                 v_empty0 = bar0 + 56, s_full0 = bar0 + 72, p_full = bar0 + 88, o_done = bar0 + 96, g_full = bar0 + 104;
+  const uint32_t q_full = bar0, k_full0 = bar0 + 8, v_full0 = k_full0 + 8 * K_STAGES, v_done0 = v_full0 + 8 * V_STAGES,
+                 s_full0 = v_done0 + 8 * V_STAGES, p_full0 = s_full0 + 16, g_full = p_full0 + 16;
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(k_full0 + 8 * s, 1);
-      mbar_init(k_empty0 + 8 * s, 1);
-      mbar_init(v_full0 + 8 * s, 1);
-      mbar_init(v_empty0 + 8 * s, 1);
-      mbar_init(s_full0 + 8 * s, 1);
-    }
-    mbar_init(p_full, 128);
-    mbar_init(o_done, 1);
+    for (int s = 0; s < K_STAGES; ++s) mbar_init(k_full0 + 8 * s, 1);
+    for (int s = 0; s < V_STAGES; ++s) mbar_init(v_full0 + 8 * s, 1), mbar_init(v_done0 + 8 * s, 1);
+    for (int s = 0; s < 2; ++s) mbar_init(s_full0 + 8 * s, 1), mbar_init(p_full0 + 8 * s, 128);  // one per score buffer
     mbar_init(g_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -280,9 +304,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     bool ok = true;
     int issued = 0;
     auto load_tile = [&](int j, int page) {
-      const int s = j % KV_STAGES;
-      const uint32_t full = (which ? v_full0 : k_full0) + 8 * s, empty = (which ? v_empty0 : k_empty0) + 8 * s;
-      if (lane == 0) ok = mbar_wait(empty, ((j / KV_STAGES) & 1) ^ 1, abort_flag);
+      // A K stage is free when the scores computed from it are there (s_full of the same index: there
+      // are as many score buffers as K stages), a V stage when its product is done (v_done).
+      const int stages = which ? V_STAGES : K_STAGES, s = j % stages;
+      const uint32_t full = (which ? v_full0 : k_full0) + 8 * s, empty = (which ? v_done0 : s_full0) + 8 * s;
+      if (lane == 0 && j >= stages) ok = mbar_wait(empty, ((j / stages) & 1) ^ 1, abort_flag);
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) return;
       if (lane == 0) STAMP(0, j, which * 2);
@@ -306,7 +332,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       __syncwarp();
       if (load) {
         const int y = (((page * 2 + which) * nkv + kvh) * page_size) + pos % page_size;
-        const uint32_t dst = smem_u32(kv_s + s * STAGE_BYTES) + which * K_BYTES + h * TILE_HALF + g * GROUP_BYTES;
+        const uint32_t dst = smem_u32(which ? v_s + s * V_BYTES : k_s + s * K_BYTES) + h * TILE_HALF + g * GROUP_BYTES;
         tma_load_2d(dst, &map_kv, full, h * 64, y);
       }
       if (lane == 0) STAMP(0, j, which * 2 + 1);
@@ -322,48 +348,55 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     }
     if (lane == 0 && *abort_flag) {
       const uint32_t full0 = which ? v_full0 : k_full0;
-      for (int j = max(0, issued - KV_STAGES); j < issued; ++j)
-        for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(full0 + 8 * (j % KV_STAGES), (j / KV_STAGES) & 1); ++i) {
+      const int stages = which ? V_STAGES : K_STAGES;
+      for (int j = max(0, issued - stages); j < issued; ++j)
+        for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(full0 + 8 * (j % stages), (j / stages) & 1); ++i) {
         }
       for (uint32_t i = 0; warp == 0 && i < WAIT_LIMIT && !mbar_try(q_full, 0); ++i) {
       }
     }
   } else if (warp == 1) {
-    // ---- MMA issuer ------------------------------------------------------------------------------
+    // ---- issuer of the score products: S[j & 1] = Q K_j^T --------------------------------------------
+    // The two kinds of product are issued by two threads (this warp and warp 7). The products of one
+    // accumulator depend on one another and run one at a time, some 50 to 100 ns each whatever their
+    // size; a single thread issuing a tile's twelve kept at most one chain in flight and a tile took
+    // 1.27 us, two threads keep the scores' chain and the values' chain going side by side (1.06 us).
+    // What one thread's products must wait for of the other's goes through barriers: a score buffer
+    // is written again only when the P V product that read P from it is done (v_done, two tiles back).
     if (lane == 0) {
-      constexpr uint32_t instr_s = idesc(BM, BN, false), instr_o = idesc(BM, D, true);
+      constexpr uint32_t instr_s = idesc(BM, BN, false);
       // Descriptors differ only in their address field (the low 14 bits, in units of 16 bytes).
-      const uint64_t q_desc = desc_k_major(smem_u32(q_s)), p_desc = desc_k_major(smem_u32(p_s));
-      uint64_t k_desc[KV_STAGES], v_desc[KV_STAGES];
-      for (int s = 0; s < KV_STAGES; ++s) {
-        k_desc[s] = desc_k_major(smem_u32(kv_s + s * STAGE_BYTES));
-        v_desc[s] = desc_mn_major(smem_u32(kv_s + s * STAGE_BYTES) + K_BYTES, TILE_HALF);
-      }
-      auto scores = [&](int j) {  // S[j & 1] = Q K_j^T, then the K slot is free
-        const int s = j % KV_STAGES;
+      const uint64_t q_desc = desc_k_major(smem_u32(q_s));
+      uint64_t k_desc[K_STAGES];
+      for (int s = 0; s < K_STAGES; ++s) k_desc[s] = desc_k_major(smem_u32(k_s + s * K_BYTES));
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % K_STAGES;
+        ok = mbar_wait(k_full0 + 8 * s, (j / K_STAGES) & 1, abort_flag);
+        if (ok && j >= 2) ok = mbar_wait(v_done0 + 8 * ((j - 2) % V_STAGES), ((j - 2) / V_STAGES) & 1, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        STAMP(1, j, 0);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           umma(tmem_base + S_COL + (j & 1) * BN, q_desc + (((kk / 4) * HALF_BYTES + (kk % 4) * 32) >> 4),
                k_desc[s] + (((kk / 4) * TILE_HALF + (kk % 4) * 32) >> 4), instr_s, kk != 0);
-        umma_commit(s_full0 + 8 * (j & 1));
-        umma_commit(k_empty0 + 8 * s);
-      };
-      bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(k_full0, 0, abort_flag);
-      if (ok) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        scores(0);
+        umma_commit(s_full0 + 8 * (j & 1));  // the scores are there, and with them the K stage is free again
+        STAMP(1, j, 3);
       }
+    }
+  } else if (warp == 7) {
+    // ---- issuer of the value products: O += P_j V_j ---------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t instr_o = idesc(BM, D, true);
+      uint64_t v_desc[V_STAGES];
+      for (int s = 0; s < V_STAGES; ++s) v_desc[s] = desc_mn_major(smem_u32(v_s + s * V_BYTES), TILE_HALF);
       uint32_t accumulate = 0;
+      bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) {
-          ok = mbar_wait(k_full0 + 8 * ((j + 1) % KV_STAGES), ((j + 1) / KV_STAGES) & 1, abort_flag);
-          if (!ok) break;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          STAMP(1, j, 0);
-          scores(j + 1);
-        }
-        const int s = j % KV_STAGES;
-        ok = mbar_wait(v_full0 + 8 * s, (j / KV_STAGES) & 1, abort_flag) && mbar_wait(p_full, j & 1, abort_flag);
+        const int s = j % V_STAGES;
+        ok = mbar_wait(v_full0 + 8 * s, (j / V_STAGES) & 1, abort_flag) &&
+             mbar_wait(p_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         STAMP(1, j, 1);
@@ -371,11 +404,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           if (!(mask & (1u << kk))) continue;  // keys never loaded: their P is zero, their V is stale
-          umma(tmem_base + O_COL, p_desc + ((kk * 32) >> 4), v_desc[s] + ((kk * GROUP_BYTES) >> 4), instr_o, accumulate);
+          // P: 16 keys are eight columns of packed bfloat16 pairs in the score buffer's place
+          umma_ts(tmem_base + O_COL, tmem_base + S_COL + (j & 1) * BN + kk * 8, v_desc[s] + ((kk * GROUP_BYTES) >> 4),
+                  instr_o, accumulate);
           accumulate = 1;
         }
-        umma_commit(v_empty0 + 8 * s);
-        umma_commit(o_done);
+        umma_commit(v_done0 + 8 * s);  // the product is done: the V stage is free, and O may be read or rescaled
         STAMP(1, j, 2);
       }
     }
@@ -429,12 +463,20 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
           if (i >= lo && i <= hi) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
       }
       if (row == 0) STAMP(2, j, 1);
-      const float m_new = fmaxf(m, tile_max);
-      const float offset = m_new == -INFINITY ? 0.f : m_new * sl2;
-      const float alpha = (m == -INFINITY || m_new == m) ? 1.f : fast_exp2(m * sl2 - offset);
-      m = m_new;
-      // P = exp2(s * scale * log2e - offset), rounded to bfloat16, kept in registers: the
-      // arithmetic overlaps the previous tile's P V, which still reads the shared P tile.
+      // The offset of the exponent (m) follows the row's maximum lazily: a softmax does not care
+      // which offset it is computed with, so m moves only when the maximum has outgrown it by more
+      // than 2^RESCALE_STEP (P then stays below that), and only then is the accumulator rescaled.
+      float alpha = 1.f;
+      if (tile_max > m) {
+        if (m == -INFINITY) {
+          m = tile_max;  // the row's first keys: nothing has been accumulated yet
+        } else if ((tile_max - m) * sl2 > RESCALE_STEP) {
+          alpha = fast_exp2((m - tile_max) * sl2);
+          m = tile_max;
+        }
+      }
+      const float offset = m == -INFINITY ? 0.f : m * sl2;
+      // P = exp2(s * scale * log2e - offset), rounded to bfloat16.
       float sums[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[32];
       if (whole) {
@@ -459,55 +501,50 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
       }
       const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
-      // The previous tile's P V must be done before O is rescaled or P is overwritten.
-      if (j > 0) {
-        ok = mbar_wait(o_done, (j - 1) & 1, abort_flag);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+      if (__any_sync(0xffffffffu, alpha != 1.f)) {
+        // The products so far must be done before the accumulator is rescaled.
+        if (j > 0) {
+          ok = mbar_wait(v_done0 + 8 * ((j - 1) % V_STAGES), ((j - 1) / V_STAGES) & 1, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
 #pragma unroll 1
-          for (int c = 0; c < D; c += 32) {
-            uint32_t v[32];
-            tmem_load32(tmem_base + lane_field + O_COL + c, v);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        for (int c = 0; c < D; c += 32) {
+          uint32_t o[32];
+          tmem_load32(tmem_base + lane_field + O_COL + c, o);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_store32(tmem_base + lane_field + O_COL + c, v);
-          }
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_store32(tmem_base + lane_field + O_COL + c, o);
         }
       }
       if (row == 0) STAMP(2, j, 2);
       l *= alpha;
-      {
-        // The tile's 64 columns are the eight 16-byte chunks of the row; chunk x of row r lives at x ^ (r % 8).
-        unsigned char* row_base = p_s + row * 128;
-#pragma unroll
-        for (int x = 0; x < 8; ++x) {
-          *reinterpret_cast<uint4*>(row_base + ((x ^ (row & 7)) * 16)) =
-              make_uint4(packed[4 * x], packed[4 * x + 1], packed[4 * x + 2], packed[4 * x + 3]);
-        }
-      }
+      // P takes the place of the scores it came from (this buffer's next scores are two tiles away,
+      // and their product is issued after this tile's P V): 64 keys are 32 columns of packed pairs.
+      tmem_store32(s_addr, packed);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       l += sum;
       if (j == n_tiles - 1 && ((last + 1) & 15)) {
         // The last group of 16 keys reaches past the block's last key. Those rows of V get a
         // zero weight, but what they hold need not be a number: past the request's last token
         // the page still holds whatever its previous owner left (0 x NaN is NaN). Clear them in
-        // the tile once it has landed; the fence below orders the stores before the P V product.
-        const int s = j % KV_STAGES;
-        ok = mbar_wait(v_full0 + 8 * s, (j / KV_STAGES) & 1, abort_flag);
+        // the tile once it has landed; the fence orders the stores before the P V product.
+        const int s = j % V_STAGES;
+        ok = mbar_wait(v_full0 + 8 * s, (j / V_STAGES) & 1, abort_flag);
         if (!ok) break;
         const int r0 = last - key0 + 1, r1 = (r0 + 15) & ~15;  // rows [r0, r1) of the tile
-        unsigned char* v_s = kv_s + s * STAGE_BYTES + K_BYTES;
+        unsigned char* v_tile = v_s + s * V_BYTES;
         for (int i = row; i < (r1 - r0) * DH * 8; i += 128) {
           const int piece = i & 7, h = (i >> 3) % DH, r = r0 + (i >> 3) / DH;
-          *reinterpret_cast<uint4*>(v_s + h * TILE_HALF + r * 128 + piece * 16) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(v_tile + h * TILE_HALF + r * 128 + piece * 16) = make_uint4(0u, 0u, 0u, 0u);
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // V is read by the tensor core (async proxy)
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core (async proxy)
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(p_full);
+      mbar_arrive(p_full0 + 8 * (j & 1));
       if (row == 0) STAMP(2, j, 3);
+      if (lane == 0) STAMP(3, j, quarter);
     }
     // Epilogue: O / l, gate, store. A thread owns a row, so a warp's loads and stores go to 32
     // different rows, each a trip to L2 of its own: read that way (two bytes at a time, then
@@ -518,54 +555,51 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const int head = kvh * GROUP + row % GROUP;
     const bf16* gp = gate ? gate + token * gate_stride + (size_t)head * D : nullptr;
     const bool gate_wide = gp != nullptr && (reinterpret_cast<uintptr_t>(gp) & 15) == 0;
-    if (ok) ok = mbar_wait(o_done, (n_tiles - 1) & 1, abort_flag);
+    if (ok) ok = mbar_wait(v_done0 + 8 * ((n_tiles - 1) % V_STAGES), ((n_tiles - 1) / V_STAGES) & 1, abort_flag);
     if (ok && gate_tma) ok = mbar_wait(g_full, 0, abort_flag);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     OMNIA_TRACE_IF(row == 0, 7);
     if (ok) {
+      // Eight dims a turn, the next turn's accumulator columns already on their way.
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = out + (token * nq + head) * D;
+      const uint32_t o_addr = tmem_base + lane_field + O_COL;
+      uint32_t cur[8], next[8];
+      tmem_load8(o_addr, cur);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll 1
-      for (int c = 0; c < D; c += 32) {
-        uint4 g4[4];
-        if (live && gate_tma) {
-          // Row `row` of the 64-dim half c / 64, 128 bytes a row, its 16-byte pieces swizzled by the row.
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int piece = (c % 64) / 8 + i;
-            g4[i] = *reinterpret_cast<const uint4*>(q_s + (c / 64) * HALF_BYTES + row * 128 + ((piece ^ (row & 7)) << 4));
+      for (int c = 0; c < D; c += 8) {
+        if (c + 8 < D) tmem_load8(o_addr + c + 8, next);
+        if (live) {
+          uint4 g = make_uint4(0u, 0u, 0u, 0u);
+          if (gate_tma) {
+            // Row `row` of the 64-dim half c / 64, 128 bytes a row, its 16-byte pieces swizzled by the row.
+            g = *reinterpret_cast<const uint4*>(q_s + (c / 64) * HALF_BYTES + row * 128 + ((((c % 64) / 8) ^ (row & 7)) << 4));
+          } else if (gate_wide) {
+            g = __ldg(reinterpret_cast<const uint4*>(gp + c));
+          } else if (gp) {
+            g.x = pack_bf16(__bfloat162float(gp[c]), __bfloat162float(gp[c + 1]));
+            g.y = pack_bf16(__bfloat162float(gp[c + 2]), __bfloat162float(gp[c + 3]));
+            g.z = pack_bf16(__bfloat162float(gp[c + 4]), __bfloat162float(gp[c + 5]));
+            g.w = pack_bf16(__bfloat162float(gp[c + 6]), __bfloat162float(gp[c + 7]));
           }
-        } else if (live && gate_wide) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) g4[i] = __ldg(reinterpret_cast<const uint4*>(gp + c) + i);
-        }
-        uint32_t v[32];
-        tmem_load32(tmem_base + lane_field + O_COL + c, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (!live) continue;
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          const uint4 g = g4[i / 8];
           const uint32_t g2[4] = {g.x, g.y, g.z, g.w};
           uint32_t w[4];
 #pragma unroll
-          for (int e = 0; e < 8; e += 2) {
-            float a = __uint_as_float(v[i + e]) * inv, b = __uint_as_float(v[i + e + 1]) * inv;
+          for (int e = 0; e < 4; ++e) {
+            float a = __uint_as_float(cur[2 * e]) * inv, b2 = __uint_as_float(cur[2 * e + 1]) * inv;
             if (gp) {
-              float ga, gb;
-              if (gate_tma || gate_wide) {
-                const float2 pair = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g2[e / 2]));
-                ga = pair.x, gb = pair.y;
-              } else {
-                ga = __bfloat162float(gp[c + i + e]), gb = __bfloat162float(gp[c + i + e + 1]);
-              }
-              a *= fast_sigmoid(ga);
-              b *= fast_sigmoid(gb);
+              const float2 gate2 = sigmoid_pair(g2[e]);
+              a *= gate2.x;
+              b2 *= gate2.y;
             }
-            w[e / 2] = pack_bf16(a, b);
+            w[e] = pack_bf16(a, b2);
           }
-          *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
         }
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < 8; ++i) cur[i] = next[i];
       }
     } else if (gate_issued) {
       // Giving up: the gate's copy must land before the block's shared memory goes away.
@@ -663,7 +697,7 @@ extern "C" int omnia_attention_prefill_tcgen05(const void* q, int tokens, const 
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return (int)cudaErrorInvalidValue;
   }
-  constexpr size_t smem = Q_BYTES + P_BYTES + KV_STAGES * STAGE_BYTES + 256;
+  constexpr size_t smem = Q_BYTES + K_STAGES * K_BYTES + V_STAGES * V_BYTES + 256;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel,

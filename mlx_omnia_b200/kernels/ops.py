@@ -371,19 +371,12 @@ class Projection:
     inv_freq: torch.Tensor | None
 
 
-DECODE_SPREAD = True
-"""The decode attention kernel's blocks ask for enough shared memory that they spread over all SMs."""
-
-USE_FUSED_DECODE = True
-"""Decode-only steps leave QK-norm, rotation and the cache write to the attention kernel."""
-
-
 def decode_fusable(proj: torch.Tensor, nq: int, nkv: int, d: int, inv_freq: torch.Tensor | None,
                    kv: KVView, step: StepContext) -> bool:
     """Whether the decode attention kernel can take the projected rows as they are: a step of
     single tokens, bfloat16, a head size that is a multiple of 32, rotated whole or not at all,
     and a cache entry that this layer writes."""
-    return (USE_FUSED_DECODE and step.decode_only and proj.is_cuda and kv.writes and d % 32 == 0
+    return (step.decode_only and proj.is_cuda and kv.writes and d % 32 == 0
             and (inv_freq is None or 2 * inv_freq.shape[0] == d) and proj.shape[1] % 2 == 0
             and tiled_attention_supported(proj.dtype, nq, nkv, d))
 
@@ -446,10 +439,10 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
         _check(fn(None if p is not None else _ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens),
                   _ptr(step.seq_lens), _ptr(single), count, _ptr(part_o), _ptr(part_ml), _ptr(tickets), chunk,
                   max_chunks, gate_ptr, gate_stride, _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size,
-                  kv.window or 0, scale, warps, *fused, int(DECODE_SPREAD), err, _stream()), "attention_decode")
+                  kv.window or 0, scale, warps, *fused, 1, err, _stream()), "attention_decode")
         if step.decode_only or all(n == 1 for n in step.q_lens):
             return out
-    if USE_TCGEN05 and tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):
+    if tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):
         work = _prefill_work_flat(step, 128 // (nq // nkv), 64, nkv, kv.window or 0, q.device)
         fn = _function("attention_tcgen05", "omnia_attention_prefill_tcgen05",
                        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
@@ -499,70 +492,34 @@ def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
 SKINNY_ROWS = 16
 """Up to this many activation rows, bfloat16 products run on the weight-streaming kernel."""
 
+TENSOR_CORE_ROWS = 129
+"""From this many rows on, bfloat16 products run on this package's tcgen05 kernels. Between the
+streaming kernel's rows and these, a 128-row tile would be mostly padding and too few tiles would
+keep the SMs busy, so the vendor library's product stands there (measured: 11-17 us against
+17-35 us for a padded tile, at 64 rows of 2,048 to 6,144 columns)."""
+
+PENDING_MAX_ROWS = 8
+PENDING_MAX_WIDTH = 2048
+"""The most rows and the widest residual stream whose pending step the weight-streaming kernel runs itself."""
 
 def _skinny(a: torch.Tensor, weight: torch.Tensor) -> bool:
     return (a.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < a.shape[0] <= SKINNY_ROWS
-            and a.shape[1] % 8 == 0 and a.is_cuda)
-
-
-USE_GEMV_STREAM = True
-"""Products of up to 16 rows run on the kernel that streams the matrix through a shared-memory
-ring (gemv_stream.cu); off, they run on the register-fed kernel (gemm_skinny.cu)."""
-
-
-def _gemv_stream(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, multiplier: float = 1.0,
-                 cap: float = 0.0) -> torch.Tensor:
-    fn = _function("gemv_stream", "omnia_gemv_stream",
-                   [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p])
-    _check(fn(_ptr(a), _ptr(weight), _ptr(out), a.shape[0], weight.shape[0], a.shape[1], epilogue, multiplier, cap,
-              _ptr(error_word(a.device)), _stream()), "gemv_stream")
-    return out
-
-
-def _small_product(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, multiplier: float = 1.0,
-                   cap: float = 0.0) -> torch.Tensor:
-    """A product of few rows, on whichever of the two weight-streaming kernels takes it."""
-    if USE_GEMV_STREAM and a.shape[0] <= 16 and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
-        return _gemv_stream(a, weight, out, epilogue, multiplier, cap)
-    return _gemm_skinny(a, weight, out, epilogue, multiplier, cap)
-
-
-def _gemm_skinny(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, multiplier: float = 1.0,
-                 cap: float = 0.0) -> torch.Tensor:
-    fn = _function("gemm_skinny", "omnia_gemm_skinny",
-                   [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
-    _check(fn(_ptr(a), _ptr(weight), _ptr(out), a.shape[0], weight.shape[0], a.shape[1], epilogue, multiplier, cap,
-              _stream()), "gemm_skinny")
-    return out
-
-
-TENSOR_CORE_ROWS = 129
-"""From this many rows on, bfloat16 products run on this package's tcgen05 kernel. Between the
-skinny kernel's rows and these, a 128-row tile would be mostly padding and too few tiles would
-keep the SMs busy, so the vendor library's product stands there (measured: 11-17 us against
-17-35 us for the configs[2] shapes at 64 rows)."""
-
-USE_TCGEN05 = True
-"""False hands every product above SKINNY_ROWS to the vendor library (kept for measuring one
-against the other)."""
+            and a.shape[1] % 8 == 0 and a.is_cuda and a.is_contiguous() and weight.is_contiguous()
+            and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
 def _tensor_core(a: torch.Tensor, weight: torch.Tensor) -> bool:
-    return (USE_TCGEN05 and a.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and a.is_cuda
+    return (a.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and a.is_cuda
             and a.shape[0] >= TENSOR_CORE_ROWS and a.shape[1] % 8 == 0 and a.is_contiguous()
             and weight.is_contiguous())
 
 
-USE_TCGEN05_PAIR = True
-"""Large bfloat16 products run two SMs to a tile (gemm_tcgen05_pair.cu); off, one SM to a tile."""
-
-
 def _pair_pays(rows: int, n: int, k: int, epilogue: int, sms: int) -> bool:
     """Whether the two-SM kernel is the faster one: it brings in a third less per step of k, but
-    has half as many (twice as large) tiles to hand out and a longer start. Measured at the
-    benchmark's shapes it wins by 4 to 13 % where a pair of SMs gets at least 64 steps of k of
-    a 256 x 256 tile to do (2,048 rows: q/gate/k/v, gate/up, down; 8,192 rows: all), and loses
-    where the work is less (2,048 x 2,048 x 2,048; 512 rows)."""
+    has half as many (twice as large) tiles to hand out and a longer start. Measured on a GPU of
+    148 SMs it wins by 4 to 13 % where a pair of SMs gets at least 64 steps of k of a 256 x 256
+    tile to do (2,048 rows of 2,048 columns times 6,144 or more; 8,192 rows: all), and loses where
+    the work is less (2,048 x 2,048 x 2,048; 512 rows)."""
     if rows < 256:
         return False
     tile_cols = 128 if epilogue == 1 else 256
@@ -571,22 +528,16 @@ def _pair_pays(rows: int, n: int, k: int, epilogue: int, sms: int) -> bool:
 
 
 def _gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, multiplier: float = 1.0,
-                  cap: float = 0.0) -> torch.Tensor:
-    if USE_TCGEN05_PAIR and _pair_pays(a.shape[0], weight.shape[0], a.shape[1], epilogue, sm_count(a.device)):
-        return _gemm_tcgen05_pair(a, weight, out, epilogue, multiplier, cap)
-    fn = _function("gemm_tcgen05", "omnia_gemm_tcgen05",
+                  cap: float = 0.0, pair: bool | None = None) -> torch.Tensor:
+    """The product on one of the two tcgen05 kernels: two SMs to a tile where that pays (`pair` None),
+    or the one the caller names."""
+    if pair is None:
+        pair = _pair_pays(a.shape[0], weight.shape[0], a.shape[1], epilogue, sm_count(a.device))
+    library, name = ("gemm_tcgen05_pair", "omnia_gemm_tcgen05_pair") if pair else ("gemm_tcgen05", "omnia_gemm_tcgen05")
+    fn = _function(library, name,
                    [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p])
     _check(fn(_ptr(a), _ptr(weight), _ptr(out), a.shape[0], weight.shape[0], a.shape[1], epilogue, multiplier, cap,
-              _ptr(error_word(a.device)), _stream()), "gemm_tcgen05")
-    return out
-
-
-def _gemm_tcgen05_pair(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, multiplier: float = 1.0,
-                       cap: float = 0.0) -> torch.Tensor:
-    fn = _function("gemm_tcgen05_pair", "omnia_gemm_tcgen05_pair",
-                   [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p])
-    _check(fn(_ptr(a), _ptr(weight), _ptr(out), a.shape[0], weight.shape[0], a.shape[1], epilogue, multiplier, cap,
-              _ptr(error_word(a.device)), _stream()), "gemm_tcgen05_pair")
+              _ptr(error_word(a.device)), _stream()), library)
     return out
 
 
@@ -597,12 +548,14 @@ def _library_mm(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return torch.mm(a, weight.t())
 
 
-USE_PENDING_STEP = True
-"""A decode step's residual updates run inside the product that takes their result."""
-
-PENDING_MAX_ROWS = 8
-PENDING_MAX_WIDTH = 2048
-"""The most rows and the widest residual stream whose pending step the weight-streaming kernel runs itself."""
+def _gemv_stream(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int, multiplier: float = 1.0,
+                 cap: float = 0.0) -> torch.Tensor:
+    """The product of up to 16 rows on the weight-streaming kernel (epilogue 0 store, 1 SwiGLU, 2 soft cap)."""
+    fn = _function("gemv_stream", "omnia_gemv_stream",
+                   [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p])
+    _check(fn(_ptr(a), _ptr(weight), _ptr(out), a.shape[0], weight.shape[0], a.shape[1], epilogue, multiplier, cap,
+              _ptr(error_word(a.device)), _stream()), "gemv_stream")
+    return out
 
 
 @dataclass
@@ -625,9 +578,9 @@ class PendingStep:
 
 def pending_supported(x: torch.Tensor, branch: torch.Tensor) -> bool:
     """Whether a product of this step's rows could run the residual step itself."""
-    return (USE_PENDING_STEP and USE_GEMV_STREAM and x.is_cuda and branch.dtype == torch.bfloat16
-            and 0 < x.shape[0] <= PENDING_MAX_ROWS and x.shape[1] % 8 == 0 and x.shape[1] <= PENDING_MAX_WIDTH
-            and x.is_contiguous() and branch.is_contiguous())
+    return (x.is_cuda and branch.dtype == torch.bfloat16 and 0 < x.shape[0] <= PENDING_MAX_ROWS
+            and x.shape[1] % 8 == 0 and x.shape[1] <= PENDING_MAX_WIDTH and x.is_contiguous()
+            and branch.is_contiguous())
 
 
 def settle(h):
@@ -655,7 +608,8 @@ def residual_after(h, x: torch.Tensor) -> torch.Tensor:
 def _pending_product(step: PendingStep, weight: torch.Tensor, epilogue: int) -> torch.Tensor | None:
     """The product with the pending step in front, or None where the kernel does not take it."""
     if step.x_new is not None or not (weight.dtype == torch.bfloat16 and weight.shape[1] == step.x.shape[1]
-                                      and weight.data_ptr() % 16 == 0 and pending_supported(step.x, step.branch)):
+                                      and weight.data_ptr() % 16 == 0 and weight.is_contiguous()
+                                      and pending_supported(step.x, step.branch)):
         return None
     rows, n = step.x.shape[0], weight.shape[0]
     out = torch.empty(rows, n // 2 if epilogue == 1 else n, dtype=torch.bfloat16, device=step.x.device)
@@ -672,20 +626,19 @@ def _pending_product(step: PendingStep, weight: torch.Tensor, epilogue: int) -> 
 
 def linear(a, weight: torch.Tensor) -> torch.Tensor:
     """a [rows, k] times weight [n, k] transposed -> [rows, n], float32 accumulation.
-    A few bfloat16 rows (a decode step) run on this package's weight-streaming kernel.
-    Otherwise the matrix product is the vendor library's (as the reference's is MLX's);
-    on the 32-bit path it runs without any reduced-precision mode. `a` may be a PendingStep."""
+    A few bfloat16 rows (a decode step) run on this package's weight-streaming kernel, 129 rows
+    and more on its tcgen05 kernels. Otherwise the matrix product is the vendor library's (as the
+    reference's is MLX's); on the 32-bit path it runs without any reduced-precision mode.
+    `a` may be a PendingStep."""
     if isinstance(a, PendingStep):
         out = _pending_product(a, weight, 0)
         if out is not None:
             return out
         a = settle(a)
     if _skinny(a, weight):
-        out = torch.empty(a.shape[0], weight.shape[0], dtype=a.dtype, device=a.device)
-        return _small_product(a, weight, out, 0)
+        return _gemv_stream(a, weight, torch.empty(a.shape[0], weight.shape[0], dtype=a.dtype, device=a.device), 0)
     if _tensor_core(a, weight):
-        out = torch.empty(a.shape[0], weight.shape[0], dtype=a.dtype, device=a.device)
-        return _gemm_tcgen05(a, weight, out, 0)
+        return _gemm_tcgen05(a, weight, torch.empty(a.shape[0], weight.shape[0], dtype=a.dtype, device=a.device), 0)
     return _library_mm(a, weight)
 
 
@@ -698,11 +651,9 @@ def linear_swiglu(a, gate_up: torch.Tensor) -> torch.Tensor:
             return out
         a = settle(a)
     if _skinny(a, gate_up):
-        out = torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device)
-        return _small_product(a, gate_up, out, 1)
+        return _gemv_stream(a, gate_up, torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device), 1)
     if _tensor_core(a, gate_up):
-        out = torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device)
-        return _gemm_tcgen05(a, gate_up, out, 1)
+        return _gemm_tcgen05(a, gate_up, torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device), 1)
     return swiglu(_library_mm(a, gate_up))
 
 
@@ -710,7 +661,7 @@ def linear_softcap(a: torch.Tensor, weight: torch.Tensor, multiplier: float, cap
     """float32 logits = cap * tanh((a @ weight^T) * multiplier / cap) -> [rows, n]."""
     if _skinny(a, weight):
         out = torch.empty(a.shape[0], weight.shape[0], dtype=torch.float32, device=a.device)
-        return _small_product(a, weight, out, 2, multiplier, cap or 0.0)
+        return _gemv_stream(a, weight, out, 2, multiplier, cap or 0.0)
     if _tensor_core(a, weight):
         out = torch.empty(a.shape[0], weight.shape[0], dtype=torch.float32, device=a.device)
         return _gemm_tcgen05(a, weight, out, 2, multiplier, cap or 0.0)

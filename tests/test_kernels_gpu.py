@@ -283,32 +283,26 @@ def test_linear_is_true_float32(ops):
     close(ops.linear(ab, wb), (ab.double() @ wb.double().t()).float(), torch.bfloat16, scale=3)
 
 
-@pytest.mark.parametrize("m", [1, 3, 8, 11, 16, 23, 32, 47, 64])
+@pytest.mark.parametrize("m", [1, 3, 8, 11, 16])
 @pytest.mark.parametrize("n,k", [(2048, 2048), (6144, 2048), (2048, 6144), (1000, 96), (777, 160), (50, 8), (5000, 520)])
-@pytest.mark.parametrize("kernel", ["registers", "ring"])
-def test_skinny_products(ops, kernel, m, n, k):
-    """The two weight-streaming kernels (fed through registers, up to 64 rows; fed through a
-    shared-memory ring, up to 16 rows) and their fused epilogues against float64 products of
-    the same bfloat16 operands, at sizes with ragged edges in every dimension."""
-    if kernel == "ring" and m > 16:
-        pytest.skip("the ring-fed kernel takes up to 16 rows")
+def test_streamed_products(ops, m, n, k):
+    """The weight-streaming kernel and its fused epilogues against float64 products of the same
+    bfloat16 operands, at sizes with ragged edges in every dimension."""
     a = rand(m, k, dtype=torch.bfloat16, seed=m)
     w = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=n + k)
     exact = a.double() @ w.double().t()
     z = exact.float().bfloat16().double()
+    def streamed(epilogue, multiplier=1.0, cap=0.0):
+        out = torch.empty(m, n // 2 if epilogue == 1 else n, dtype=torch.float32 if epilogue == 2 else torch.bfloat16,
+                          device="cuda")
+        return ops._gemv_stream(a, w, out, epilogue, multiplier, cap)
 
-    def skinny(epilogue, out, multiplier=1.0, cap=0.0):  # the kernel itself, whatever `linear` would pick
-        product = ops._gemv_stream if kernel == "ring" else ops._gemm_skinny
-        return product(a, w, out, epilogue, multiplier, cap)
-
-    close(skinny(0, torch.empty(m, n, dtype=torch.bfloat16, device="cuda")), exact, torch.bfloat16)
-    close(skinny(2, torch.empty(m, n, dtype=torch.float32, device="cuda"), 3.0, 7.0), 7.0 * torch.tanh(z * 3.0 / 7.0),
-          torch.bfloat16)
-    close(skinny(2, torch.empty(m, n, dtype=torch.float32, device="cuda"), 0.5, 0.0), z * 0.5, torch.bfloat16)
+    close(streamed(0), exact, torch.bfloat16)
+    close(streamed(2, 3.0, 7.0), 7.0 * torch.tanh(z * 3.0 / 7.0), torch.bfloat16)
+    close(streamed(2, 0.5, 0.0), z * 0.5, torch.bfloat16)
     if n % 2 == 0:
         g, u = z[:, : n // 2], z[:, n // 2:]
-        close(skinny(1, torch.empty(m, n // 2, dtype=torch.bfloat16, device="cuda")), g * torch.sigmoid(g) * u,
-              torch.bfloat16)
+        close(streamed(1), g * torch.sigmoid(g) * u, torch.bfloat16)
     close(ops.linear(a, w), exact, torch.bfloat16)
     ops.raise_on_error(a.device)
 
@@ -367,15 +361,10 @@ def test_tcgen05_products(ops, kernel, m, n, k):
     if kernel == "dispatch":
         plain, capped, gated = ops.linear(a, w), ops.linear_softcap(a, w, 3.0, 7.0), ops.linear_swiglu(a, w)
     else:
-        product = ops._gemm_tcgen05_pair if kernel == "two_sm" else ops._gemm_tcgen05
-        if kernel == "one_sm":
-            ops.USE_TCGEN05_PAIR = False
-        try:
-            plain = product(a, w, torch.empty(m, n, dtype=torch.bfloat16, device="cuda"), 0)
-            capped = product(a, w, torch.empty(m, n, dtype=torch.float32, device="cuda"), 2, 3.0, 7.0)
-            gated = product(a, w, torch.empty(m, n // 2, dtype=torch.bfloat16, device="cuda"), 1)
-        finally:
-            ops.USE_TCGEN05_PAIR = True
+        pair = kernel == "two_sm"
+        plain = ops._gemm_tcgen05(a, w, torch.empty(m, n, dtype=torch.bfloat16, device="cuda"), 0, pair=pair)
+        capped = ops._gemm_tcgen05(a, w, torch.empty(m, n, dtype=torch.float32, device="cuda"), 2, 3.0, 7.0, pair=pair)
+        gated = ops._gemm_tcgen05(a, w, torch.empty(m, n // 2, dtype=torch.bfloat16, device="cuda"), 1, pair=pair)
     close(plain, exact, torch.bfloat16)
     close(capped, 7.0 * torch.tanh(z * 3.0 / 7.0), torch.bfloat16)
     close(gated, g * torch.sigmoid(g) * u, torch.bfloat16)
