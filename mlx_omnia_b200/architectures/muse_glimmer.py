@@ -191,6 +191,7 @@ ARCHITECTURE = Architecture(
     random_tensors=random_tensors,
     stop_tokens=lambda config: config.text_config.eos,
     dropped_tensors=lambda config: ("lm_head.weight",) if config.tie_word_embeddings else (),
+    max_context=lambda config: config.text_config.max_position_embeddings,
 )
 
 register_architecture(ARCHITECTURE, "muse_glimmer", "MuseGlimmerForConditionalGeneration", "MuseGlimmerForCausalLM")

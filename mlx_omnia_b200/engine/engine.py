@@ -82,6 +82,9 @@ class Engine:
             free, _ = torch.cuda.mem_get_info(runtime.device)
             tokens = pool_tokens(free, CacheManager.bytes_per_token(needs, element), args.page_size,
                                  args.memory_fraction)
+            longest = architecture.max_context(config)
+            if longest:  # no more than every request at the longest context the checkpoint declares
+                tokens = min(tokens, -(-longest // args.page_size) * args.page_size * args.max_requests)
         self.cache_tokens = tokens
         pages = -(-tokens // args.page_size)
         self.cache = CacheManager(needs, page_size=args.page_size, pages_per_group=pages,

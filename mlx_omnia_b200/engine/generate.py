@@ -21,11 +21,14 @@ from pathlib import Path
 import torch
 
 from mlx_omnia_b200.engine.engine import DTYPES, Engine, EngineArgs
+from mlx_omnia_b200.engine.meter import Meter
 from mlx_omnia_b200.engine.scheduler import PlannedEntry, Request, Scheduler, StepOutput, StepPlan
 from mlx_omnia_b200.engine.step import StepEntry
 from mlx_omnia_b200.kernels import ops
 from mlx_omnia_b200.sampling.batch import sample_rows
 from mlx_omnia_b200.sampling.options import GenerationOptions
+from mlx_omnia_b200.text.bpe import Detokenizer
+from mlx_omnia_b200.text.defaults import GenerationDefaults
 
 
 @dataclass(frozen=True)
@@ -73,8 +76,12 @@ class _Launched:
 class Generator:
     """Continuous batching over one `Engine`."""
 
-    def __init__(self, engine: Engine, *, max_tokens_per_step: int = 2048, max_running: int | None = None) -> None:
+    def __init__(self, engine: Engine, *, max_tokens_per_step: int = 2048, max_running: int | None = None,
+                 stop: Sequence[int] | None = None) -> None:
+        """`stop`: the ids that end a generation whose options name none (None: config.json's own)."""
         self.engine = engine
+        self.default_stop = tuple(stop) if stop is not None else \
+            tuple(engine.architecture.stop_tokens(engine.config))
         self.scheduler = Scheduler(engine.cache, max_tokens_per_step=max_tokens_per_step, max_running=max_running)
         self._ids = itertools.count()
         self._seeds: dict[str, int] = {}
@@ -91,9 +98,11 @@ class Generator:
         budget = options.max_tokens
         if options.context_limit is not None:
             budget = min(budget, options.context_limit - len(prompt))
-        stop = options.stop if options.stop is not None else self.engine.architecture.stop_tokens(self.engine.config)
+        stop = options.stop if options.stop is not None else self.default_stop
         params = options.params()
         request = Request(request_id or f"req-{next(self._ids)}", prompt, max(budget, 0), params, frozenset(stop))
+        request.meter = options.meter if options.meter is not None else Meter()
+        request.meter.begin(len(prompt))
         self.scheduler.add(request)
         self._seeds[request.request_id] = params.seed if params.seed is not None else secrets.randbits(63)
         return request
@@ -163,6 +172,8 @@ class Generator:
         live = [e for e in plan.entries if e.request.status == "running"]
         outputs = self.scheduler.commit(StepPlan(live, plan.preempted), sampled)
         for output in outputs:
+            if output.token is not None:
+                output.request.meter.token()
             if output.finished:
                 self._seeds.pop(output.request.request_id, None)
         return outputs
@@ -223,24 +234,31 @@ class Generator:
 class LanguageModel:
     """What `load` returns: a model that streams text (or token ids)."""
 
-    def __init__(self, engine: Engine, tokenizer=None, **generator_args) -> None:
+    def __init__(self, engine: Engine, tokenizer=None, defaults: GenerationDefaults | None = None,
+                 **generator_args) -> None:
         self.engine = engine
         self.tokenizer = tokenizer or TokenIdTokenizer()
-        self.generator = Generator(engine, **generator_args)
+        self.defaults = defaults or GenerationDefaults(tuple(engine.architecture.stop_tokens(engine.config)))
+        self.generator = Generator(engine, stop=self.defaults.stop, **generator_args)
 
     def _ids(self, prompt) -> list[int]:
         if isinstance(prompt, Text):
             prompt = prompt.prompt
-        return self.tokenizer.encode(prompt) if isinstance(prompt, str) else [int(t) for t in prompt]
+        return list(self.tokenizer.encode(prompt)) if isinstance(prompt, str) else [int(t) for t in prompt]
 
     def stream(self, input, options: GenerationOptions) -> Iterator[Segment]:
-        """Generate for one prompt, yielding each token as it is chosen."""
+        """Generate for one prompt, yielding each token as it is chosen. A segment's text is
+        whole characters: bytes that do not yet end one wait for the token that completes them."""
         request = self.generator.add(self._ids(input), options)
+        pieces = Detokenizer(self.tokenizer)
         try:
             while request.status != "finished":
                 for output in self.generator.step():
                     if output.request is request and output.token is not None:
-                        yield Segment(self.tokenizer.decode([output.token]), output.token)
+                        yield Segment(pieces.feed(output.token), output.token)
+            rest = pieces.flush()
+            if rest:
+                yield Segment(rest, -1)
         finally:
             if request.status != "finished":
                 self.generator.abort(request.request_id)
@@ -250,14 +268,16 @@ class LanguageModel:
         return self.generator.generate([self._ids(p) for p in inputs], options)
 
 
-def load(model: str | Path, *, dtype=None, quantize=None, page_size: int = 16, cache_tokens: int = 32768,
+def load(model: str | Path, *, dtype=None, quantize=None, page_size: int = 16, cache_tokens: int | None = None,
          max_requests: int = 64, max_tokens_per_step: int = 2048, device: str = "cuda:0") -> LanguageModel:
-    """Load a model folder (config.json + safetensors).
+    """Load a model folder (config.json + safetensors, and tokenizer.json / generation_config.json
+    where it has them).
 
     dtype: None or "bfloat16" keeps the checkpoint's bfloat16; "float32" runs everything
     in true 32-bit. `quantize` exists in the reference's signature; this engine has no
     quantised path and refuses it. The remaining arguments size the engine: tokens per
-    cache page, tokens the page pool holds, live requests, tokens per step."""
+    cache page, tokens the page pool holds (None: sized from the device memory that is free
+    once the weights are placed), live requests, tokens per step."""
     if quantize is not None:
         raise ValueError("quantised weights are not part of this engine")
     if isinstance(dtype, torch.dtype):
@@ -267,4 +287,6 @@ def load(model: str | Path, *, dtype=None, quantize=None, page_size: int = 16, c
         raise ValueError(f"{folder} is not a model folder (no config.json); hub downloads are not part of this engine")
     engine = Engine.from_folder(folder, EngineArgs(dtype=dtype or "bfloat16", page_size=page_size,
                                                    cache_tokens=cache_tokens, max_requests=max_requests, device=device))
-    return LanguageModel(engine, max_tokens_per_step=max_tokens_per_step)
+    architecture = engine.architecture
+    return LanguageModel(engine, tokenizer=architecture.tokenizer(folder),
+                         defaults=architecture.defaults(folder, engine.config), max_tokens_per_step=max_tokens_per_step)

@@ -54,6 +54,7 @@ class Request:
     finish_reason: str | None = None  # stop | length | abort
     preemptions: int = 0
     order: int = 0
+    meter: object | None = None  # an engine.meter.Meter, filled by the generation loop
 
     @property
     def tokens(self) -> list[int]:
@@ -146,6 +147,8 @@ class Scheduler:
         self.cache.close(request.request_id)
         request.cache, request.computed, request.status = None, 0, "waiting"
         request.preemptions += 1
+        if request.meter is not None:
+            request.meter.preemptions += 1
         self.running.remove(request)
         self.waiting.appendleft(request)
 

@@ -12,7 +12,12 @@ returning that configuration; `model_spec(config)` returning the parts and sched
 for tensors the text engine ignores on purpose); and `random_tensors(config, seed)`
 for the random-weights mode; `dropped_tensors(config)` names tensors a file may carry
 that the configuration makes unused (a tied head's `lm_head.weight`, which the
-reference drops too: src/mlx_omnia/engine/checkpoint.py:630-631).
+reference drops too: src/mlx_omnia/engine/checkpoint.py:630-631); `tokenizer(folder)`
+returns the folder's tokenizer (anything with `encode` and `decode`) or None;
+`generation_defaults(folder, config)` returns the ids that end a generation and the
+sampling the checkpoint asks for (`text.GenerationDefaults`). The last two default to a
+byte-level BPE read from tokenizer.json and to generation_config.json, which is where the
+reference finds them for every family.
 """
 
 from __future__ import annotations
@@ -20,9 +25,12 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any, Callable
 
+from pathlib import Path
+
 import torch
 
 from mlx_omnia_b200.parts.model import ModelSpec
+from mlx_omnia_b200.text.defaults import GenerationDefaults, generation_defaults, read_tokenizer
 
 
 @dataclass(frozen=True)
@@ -36,6 +44,16 @@ class Architecture:
     stop_tokens: Callable[[Any], tuple[int, ...]] = lambda config: ()
     # Model tensor names a file may hold that this configuration does not use (dropped).
     dropped_tensors: Callable[[Any], tuple[str, ...]] = lambda config: ()
+    tokenizer: Callable[[Path], Any] = read_tokenizer
+    # The longest context the checkpoint declares (None: it declares none).
+    max_context: Callable[[Any], int | None] = lambda config: None
+    generation_defaults: Callable[[Path, Any], GenerationDefaults] | None = None
+
+    def defaults(self, folder: Path, config: Any) -> GenerationDefaults:
+        """What the checkpoint in `folder` says about stopping and sampling."""
+        if self.generation_defaults is not None:
+            return self.generation_defaults(folder, config)
+        return generation_defaults(folder, self.stop_tokens(config))
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}

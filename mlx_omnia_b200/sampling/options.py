@@ -117,8 +117,10 @@ class GenerationOptions:
                     the model's own (config.json's eos_token_id)
     penalty:        what `repetition_penalty(...)` returns, or None
     context_limit:  ceiling on prompt and generation together, or None
-    The reference's remaining fields (constraint, meter, prefix, reasoning_budget,
-    speculate) belong to its server, grammar and drafter, which this engine leaves out.
+    meter:          an `engine.meter.Meter` that the generation fills (token counts, time to the
+                    first token, decode rate), or None
+    The reference's remaining fields (constraint, prefix, reasoning_budget, speculate) belong
+    to its server, grammar and drafter, which this engine leaves out.
     """
 
     max_tokens: int
@@ -126,6 +128,7 @@ class GenerationOptions:
     stop: Collection[int] | None = None
     penalty: Penalty | None = None
     context_limit: int | None = None
+    meter: object | None = None
 
     def params(self) -> SamplingParams:
         if self.penalty is None:

@@ -56,3 +56,32 @@ def test_preemption_does_not_change_the_tokens(cpu_ops):
     assert sum(r.preemptions for r in requests) > 0
     assert [r.generated for r in requests] == roomy
     assert all(g.pool.free == g.pool.count for g in tight_engine.cache.groups)
+
+
+def test_a_step_that_raises_fails_its_requests_and_frees_what_they_hold(cpu_ops, monkeypatch):
+    """The step function fails in the middle of a generation: the requests of that step end as
+    aborted, every page and slot is back in the pool, and the engine goes on with new requests
+    (the reference aborts the round's members and carries on: src/mlx_omnia/server/runtime/rounds.py:88-93)."""
+    engine, raw, weights = engine_for("A")
+    generator = Generator(engine, max_tokens_per_step=8)
+    prompts = [tiny_configs.prompt(n, engine.vocab_size, 80 + n) for n in (6, 11)]
+    requests = [generator.add(p, GenerationOptions(max_tokens=6, stop=())) for p in prompts]
+    for _ in range(3):
+        generator.step()
+    assert engine.cache.requests and all(r.status == "running" for r in requests)
+    real = engine.model.forward
+
+    def broken(*args, **kwargs):
+        raise RuntimeError("the device fell over")
+
+    monkeypatch.setattr(engine.model, "forward", broken)
+    with pytest.raises(RuntimeError, match="fell over"):
+        generator.run()
+    assert all(r.status == "finished" and r.finish_reason == "abort" for r in requests)
+    assert not engine.cache.requests and engine.cache.slots.free == engine.cache.slots.count
+    assert all(g.pool.free == g.pool.count for g in engine.cache.groups)
+    engine.cache.check()
+    monkeypatch.setattr(engine.model, "forward", real)
+    again = generator.generate([prompts[0]], GenerationOptions(max_tokens=4, stop=()))
+    assert again == [plain_impl.greedy_generate(raw, weights, prompts[0], 4)]
+    assert requests[0].meter.prompt_tokens == 6 and requests[0].meter.completion_tokens == len(requests[0].generated)

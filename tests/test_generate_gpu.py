@@ -183,3 +183,33 @@ def test_preemption_on_the_gpu(dtype):
             logits = plain_impl.forward(raw, weights, prompt + ids)[len(prompt) - 1: -1]
             chosen = logits[torch.arange(len(ids)), torch.tensor(ids)]
             assert float((logits.max(dim=-1).values - chosen).max()) < 0.03 * float(logits.abs().max())
+
+
+def test_command_line_takes_text_and_the_checkpoint_s_defaults(tmp_path):
+    """A folder with a tokenizer.json and a generation_config.json: `omnia run -m DIR "hello world"`
+    encodes the prompt, decodes greedily because the checkpoint says `do_sample: false`, stops at the
+    id the generation config adds, prints text, and with --verbose the request's numbers on stderr."""
+    import json
+
+    from test_text import tokenizer_json
+
+    raw, weights = write_folder(tmp_path / "m", "A")
+    declared = tokenizer_json()
+    known = len(declared["model"]["vocab"]) + len(declared["added_tokens"])
+    declared["added_tokens"] += [{"id": i, "content": f"<|{i}|>"} for i in range(known, 512)]
+    (tmp_path / "m" / "tokenizer.json").write_text(json.dumps(declared), encoding="utf-8")
+    vocab = declared["model"]["vocab"]
+    prompt = [vocab["hello"], vocab["Ġworld"]]
+    expect = plain_impl.greedy_generate(raw, weights, prompt, 12)
+    stop_at = expect[7]
+    (tmp_path / "m" / "generation_config.json").write_text(json.dumps({"do_sample": False, "eos_token_id": [stop_at]}))
+    done = subprocess.run([sys.executable, str(ROOT / "bin" / "omnia"), "run", "-m", str(tmp_path / "m"),
+                           "--max-tokens", "12", "--dtype", "float32", "--verbose", "hello world"],
+                          capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0, done.stderr[-2000:]
+    cut = min(expect.index(t) for t in (stop_at, 0) if t in expect)  # token 0 is config.json's own eos
+    from mlx_omnia_b200.text import ByteLevelBPE
+
+    tokenizer = ByteLevelBPE.from_file(tmp_path / "m" / "tokenizer.json")
+    assert done.stdout.rstrip("\n") == tokenizer.decode(expect[:cut]).rstrip("\n")
+    assert f"prompt 2 tokens, completion {cut} tokens" in done.stderr

@@ -27,12 +27,17 @@ def test_replay_in_process(cpu_ops, tmp_path, name):
                                                           max_requests=4, device="cpu"))
     done = io.StringIO()
     lines = io.StringIO("".join(json.dumps(s) + "\n" for s in trace.steps))
-    assert replay(engine, lines, tmp_path, done) == len(trace.steps)
+    assert replay(engine, lines, tmp_path, done, npy=True) == len(trace.steps)
     assert done.getvalue().split()[-1] == str(len(trace.steps) - 1)
     expect = {rid: plain_impl.forward(raw, weights, ids) for rid, ids in prompts.items()}
     for index, rows in enumerate(trace.where):
         data = torch.from_numpy(np.fromfile(tmp_path / f"{index}.f32", dtype="<f4").reshape(len(rows), vocab))
         want = torch.stack([expect[rid.split("-")[1]][position] for rid, position in rows])
         assert plain_impl.relative_diff(data, want) < 2e-5, index
+    # The same logits once more, gathered per request: every position of every replayed request.
+    for request in {rid for rows in trace.where for rid, _ in rows}:
+        whole = torch.from_numpy(np.load(tmp_path / f"logits_{request}.npy"))
+        assert whole.shape == expect[request.split("-")[1]].shape
+        assert plain_impl.relative_diff(whole, expect[request.split("-")[1]]) < 2e-5, request
     assert not engine.cache.requests
     engine.cache.check()
