@@ -10,7 +10,12 @@ through the Python entry point's generation loop, which copies every step's inpu
 from pinned host memory and reads the chosen tokens back. `prefill` is one step of
 2,048 prompt tokens; `roofline` relates the decode step's time to the bytes it must
 read (every weight once, and the live requests' cache). `points` holds decode at
-batch 1 and 64. Data is synthetic: seeded uniform-random token ids.
+batch 1 and 64 and two mixed steps (milliseconds a step: eight decoding requests at
+4,096 tokens beside a 256-token portion of a prompt, and a lone 128-token portion).
+`kernels` times each class of kernel alone (operands rotated through more memory than
+L2 holds, replayed from a CUDA graph) against the measured peaks: the streamed product
+of a decode step, the head, decode attention (GB/s), the prefill product and prefill
+attention (TFLOP/s). Data is synthetic: seeded uniform-random token ids.
 """
 
 from __future__ import annotations
@@ -192,6 +197,106 @@ def run(args) -> dict:
         return {"value": tokens * 1000.0 / ms, "tokens": tokens, "ms": ms,
                 "frac": flops / (ms / 1000.0) / (measured["bf16_tflops"] * 1e12), "flops": flops}
 
+    def mixed(decoders: int, portion: int, steps: int, warmup: int) -> dict:
+        """`decoders` requests at `args.context` tokens decode beside `portion` tokens of a long prompt."""
+        requests = [engine.cache.open(f"mixed-{i}") for i in range(decoders)]
+        reader = engine.cache.open("mixed-reader")
+        if decoders:
+            engine.runner.run([StepEntry(r, p, []) for r, p in zip(requests, prompts(decoders, args.context - steps - warmup - 1))])
+        times, walls = [], []
+        for index in range(warmup + steps):
+            entries = [StepEntry(r, [1 + index], [0]) for r in requests] + [StepEntry(reader, prompts(1, portion)[0], [])]
+            torch.cuda.synchronize()
+            start, stop = events()
+            wall = time.perf_counter()
+            start.record()
+            engine.runner.run(entries)
+            stop.record()
+            torch.cuda.synchronize()
+            wall = time.perf_counter() - wall
+            if index >= warmup:
+                times.append(start.elapsed_time(stop))
+                walls.append(wall * 1e3)
+        for r in requests + [reader]:
+            engine.cache.close(r.request_id)
+        return {"ms": statistics.median(times), "wall_ms": statistics.median(walls)}
+
+    def kernel_classes() -> dict:
+        """Each class of kernel alone, replayed from a graph over operands that do not fit L2."""
+        from mlx_omnia_b200.parts.base import KVView, StepContext
+
+        device = engine.runtime.device
+        h, inner, d = text["hidden_size"], text["intermediate_size"], text["head_dim"]
+        nq, nkv = text["num_attention_heads"], text["num_key_value_heads"]
+        draw = lambda *shape: torch.randn(*shape, device=device, dtype=torch.bfloat16) * 0.05
+
+        def timed(body, sets: int) -> float:
+            """Seconds per call of `body(i)`, i cycling through `sets` operand sets."""
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                for i in range(sets):
+                    body(i)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(sets):
+                        body(i)
+            torch.cuda.synchronize()
+            for _ in range(3):
+                graph.replay()
+            start, stop = events()
+            start.record()
+            for _ in range(5):
+                graph.replay()
+            stop.record()
+            torch.cuda.synchronize()
+            return start.elapsed_time(stop) / 1e3 / (5 * sets)
+
+        def record(seconds: float, amount: float, peak: float, unit: str) -> dict:
+            achieved = amount / seconds / (1e9 if unit == "GB/s" else 1e12)
+            return {"achieved": round(achieved, 1), "unit": unit, "frac": round(achieved / peak, 3), "us": round(seconds * 1e6, 2)}
+
+        out = {}
+        hbm, tensor = measured["hbm_gbs"], measured["bf16_tflops"]
+        # K3: the streamed product of a decode step (gate|up with SwiGLU, 8 rows).
+        weights = [draw(2 * inner, h) for _ in range(6)]
+        rows8 = draw(8, h)
+        out["k3_streamed_product"] = record(timed(lambda i: ops.linear_swiglu(rows8, weights[i]), 6), 2 * 2 * inner * h, hbm, "GB/s")
+        # K10: the head with its soft cap, 8 rows.
+        table = engine.model.embedding.weight
+        out["k10_head"] = record(timed(lambda i: ops.linear_softcap(rows8, table, 1.0, 30.0), 1), 2 * vocab * h, hbm, "GB/s")
+        # K2: a prefill product (2,048 rows, gate|up with SwiGLU).
+        rows2k = draw(PREFILL_TOKENS, h)
+        out["k2_prefill_product"] = record(timed(lambda i: ops.linear_swiglu(rows2k, weights[i]), 6),
+                                           2.0 * PREFILL_TOKENS * 2 * inner * h, tensor, "TFLOP/s")
+        del weights
+        # K6 / K5: attention over a paged cache of random values, pages in order.
+        def attention(batch: int, q_len: int, context: int):
+            pages_per = -(-context // 16)
+            sets = max(2, int(200e6 // (batch * pages_per * 2 * nkv * 16 * d * 2)) + 1)
+            caches = [draw(batch * pages_per, 2, nkv, 16, d) for _ in range(sets)]
+            i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+            table = torch.arange(batch * pages_per, dtype=torch.int32, device=device).view(batch, pages_per)
+            tokens = batch * q_len
+            step = StepContext(
+                num_tokens=tokens, num_seqs=batch, token_ids=i32([0] * tokens),
+                positions=i32([context - q_len + t for _ in range(batch) for t in range(q_len)]),
+                cu_seqlens=i32([q_len * b for b in range(batch + 1)]), seq_lens=i32([context] * batch),
+                state_slots=i32([0] * batch), fresh=i32([0] * batch), logit_rows=i32([]), q_lens=[q_len] * batch,
+                seq_lens_host=[context] * batch, max_q_len=q_len, max_seq_len=context, decode_only=q_len == 1,
+                groups={}, workspace={"private": True})
+            q, gate = draw(tokens, nq, d) * 20, draw(tokens, nq * d)
+            slots = torch.zeros(tokens, dtype=torch.int64, device=device)
+            seconds = timed(lambda i: ops.paged_attention(q, KVView(caches[i], table, slots, 16, None), step,
+                                                          d ** -0.5, gate=gate), sets)
+            return seconds
+
+        out["k6_decode_attention"] = record(attention(args.batch, 1, args.context),
+                                            args.batch * args.context * 2 * nkv * d * 2, hbm, "GB/s")
+        out["k5_prefill_attention"] = record(attention(1, PREFILL_TOKENS, PREFILL_TOKENS),
+                                             4.0 * nq * d * PREFILL_TOKENS * (PREFILL_TOKENS + 1) / 2, tensor, "TFLOP/s")
+        return out
+
     if args.timeline:
         # One step of a tracing build, kernel by kernel as it runs (set OMNIA_TIMELINE=1): the lines
         # go to stderr, the record says how many kernels were seen.
@@ -231,6 +336,11 @@ def run(args) -> dict:
     side_steps = max(8, min(args.steps, 32))
     points = {f"decode_b{b}": round(decode(b, side_steps, 3)["tokens_per_s"], 1) for b in (1, 64)}
     pre = prefill(PREFILL_TOKENS, 5, 3)
+    for name, (decoders, portion) in {"mixed_b8_ctx4096_portion256": (8, 256), "mixed_portion128": (0, 128)}.items():
+        part = mixed(decoders, portion, 8, 3)
+        points[name + "_ms"] = round(part["ms"], 3)
+        points[name + "_host_ms"] = round(part["wall_ms"], 3)
+    kernels = kernel_classes()
     ops.raise_on_error(engine.runtime.device)
 
     step_bytes = weight_bytes + args.batch * main["context"] * kv_per_token
@@ -266,6 +376,7 @@ def run(args) -> dict:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": measured["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / measured["hbm_gbs"], 4)},
         "points": points,
+        "kernels": kernels,
     }
 
 

@@ -494,9 +494,11 @@ SKINNY_ROWS = 16
 
 TENSOR_CORE_ROWS = 129
 """From this many rows on, bfloat16 products run on this package's tcgen05 kernels. Between the
-streaming kernel's rows and these, a 128-row tile would be mostly padding and too few tiles would
-keep the SMs busy, so the vendor library's product stands there (measured: 11-17 us against
-17-35 us for a padded tile, at 64 rows of 2,048 to 6,144 columns)."""
+streaming kernel's rows and these the vendor library's product stands (inside a replayed graph it
+takes 5 to 11 us for matrices of 8 to 50 MB at 17 to 128 rows). A kernel of this package's own for
+that range (the weights as the 128-row operand of tcgen05.mma, the few activation rows as its
+columns, the k range cut over a thread-block cluster that adds its partial sums through distributed
+shared memory) gave right results and took 11 to 44 us, growing with the rows: it was not kept."""
 
 PENDING_MAX_ROWS = 8
 PENDING_MAX_WIDTH = 2048
