@@ -14,6 +14,20 @@ and filled by the same `StepLayout` as an uncaptured step's.
 At most `MAX_GRAPHS` captured graphs are kept; the one replayed longest ago is dropped
 for a new bucket (each holds its own logits, activations and scratch buffers).
 
+Mixed steps (`MixedGraphs`). A step of a few hundred tokens, portions of prompts beside
+decoded tokens, launches some 230 kernels one by one from Python and is bound by the host
+(16 us a launch) long before the GPU. In continuous batching such steps repeat in shape:
+the same requests decode while a long prompt is read in portions of the token budget. So
+a step whose shape (tokens per request, wanted rows per request, the bucket of the
+longest decoding request) comes a second time is captured with exactly that shape, and
+replayed whenever it comes again. Its block tables are as wide as the pool allows, so the
+width never changes; the small lists that the attention kernels read (which block of
+query tokens runs where) are given a place on the device during the capture and filled by
+the host before every replay (`ops.fill_step_lists`). The second step of a shape runs
+uncaptured on the buffers the graph will use (so every scratch buffer and list exists
+before the capture), and the capture that follows runs nothing, so a mixer's state is
+never stepped twice; from its third coming on the shape is replayed.
+
 The kernels and the model code are the same as in an uncaptured step; only the way
 they are launched differs, so logits agree bit for bit with an eager step of the same
 bucket. Capture is used only when every mixer of the model declares `graph_safe`
@@ -138,3 +152,96 @@ class DecodeGraphs:
             return captured.logits[:0]
         # The graph owns its output buffer; the next replay overwrites it.
         return logits.clone() if copy else logits
+
+
+MIXED_MAX_TOKENS = 1024
+"""Steps of more tokens are bound by the GPU, not by launching them, and stay uncaptured."""
+MIXED_MAX_GRAPHS = 8
+
+
+class MixedGraphs:
+    """Captured steps of mixed shape, keyed by that shape (see the head of the file)."""
+
+    def __init__(self, runner) -> None:
+        self.runner = runner
+        self.seen: dict[tuple, int] = {}
+        self.captured: dict[tuple, _Captured] = {}  # in order of last use, oldest first
+        self.replays = 0
+        cache = runner.cache
+        # Block tables as wide as the longest request the pools can hold: the width is then no part of a shape.
+        self.widths = [cache.pages_for(g, cache.capacity_tokens()) for g in range(len(cache.groups))]
+
+    @staticmethod
+    def supported(model) -> bool:
+        return all(getattr(block.mixer, "graph_safe_mixed", False) for block in model.blocks)
+
+    def key(self, entries) -> tuple | None:
+        q_lens = tuple(len(e.tokens) for e in entries)
+        if sum(q_lens) > MIXED_MAX_TOKENS or all(q == 1 for q in q_lens):
+            return None
+        page = self.runner.cache.page_size
+        longest = max((e.request.tokens + 1 for e, q in zip(entries, q_lens) if q == 1), default=0)
+        return q_lens, tuple(len(e.want) for e in entries), ops.width_bucket(-(-longest // page)) if longest else 0
+
+    def wants(self, entries) -> tuple | None:
+        """The shape's key if this step should run from a graph: the shape has come before."""
+        key = self.key(entries)
+        if key is None:
+            return None
+        if key in self.captured:
+            return key
+        self.seen[key] = self.seen.get(key, 0) + 1
+        if len(self.seen) > 4096:
+            self.seen.clear()
+        return key if self.seen[key] >= 2 else None
+
+    def run(self, key: tuple, entries, copy: bool = True) -> torch.Tensor:
+        runner = self.runner
+        for entry in entries:
+            if any(not 0 <= w < len(entry.tokens) for w in entry.want):
+                raise ValueError(f"request {entry.request.request_id!r}: a wanted place lies outside its tokens")
+        starts = runner.take_pages(entries)
+        at, rows = 0, []
+        for e in entries:
+            rows += [at + w for w in e.want]
+            at += len(e.tokens)
+        captured = self.captured.pop(key, None)
+        fresh = captured is None
+        if fresh:
+            while len(self.captured) >= MIXED_MAX_GRAPHS:
+                torch.cuda.synchronize(runner.runtime.device)
+                del self.captured[next(iter(self.captured))]
+            layout = StepLayout(at, len(entries), len(rows), self.widths)
+            host_tensor = torch.zeros(layout.words, dtype=torch.int32).pin_memory()
+            dev = torch.zeros(layout.words, dtype=torch.int32, device=runner.runtime.device)
+        else:
+            layout, host_tensor, dev = captured.layout, captured.host_tensor, captured.device
+            if captured.copied is not None:
+                captured.copied.synchronize()  # the pinned buffers are free to be written again
+        q_lens, held = layout.fill(host_tensor.numpy(), runner.cache, entries, starts, rows)
+        dev.copy_(host_tensor, non_blocking=True)
+        if fresh:
+            # This step runs kernel by kernel on the graph's buffers; then the same launches are captured.
+            step = layout.context(dev, q_lens=q_lens, seq_lens_host=held, max_q_len=max(q_lens), max_seq_len=max(held),
+                                  decode_only=False, workspace={"private": True})
+            layers = runner.layer_contexts(step)
+            result = runner.model.forward(step, layers)
+            torch.cuda.synchronize(runner.runtime.device)
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launches
+            with torch.cuda.graph(graph):
+                logits = runner.model.forward(step, layers)
+            launches = ops.launches - before
+            ops.launches = before  # the capture launched nothing
+            self.captured[key] = _Captured(graph, step, layout, host_tensor, dev, logits, launches)
+            return result
+        captured.step.seq_lens_host, captured.step.max_seq_len = held, max(held)
+        self.captured[key] = captured  # most recently used last
+        ops.fill_step_lists(captured.step)
+        if captured.copied is None:
+            captured.copied = torch.cuda.Event()
+        captured.copied.record()
+        captured.graph.replay()
+        self.replays += 1
+        ops.launches += captured.launches
+        return captured.logits.clone() if copy else captured.logits

@@ -114,12 +114,14 @@ class StepRunner:
     def __init__(self, model: DecoderModel, cache: CacheManager, runtime: Runtime, cuda_graphs: bool = False) -> None:
         self.model, self.cache, self.runtime = model, cache, runtime
         self.steps_run = 0
-        self.graphs = None
+        self.graphs = self.mixed_graphs = None
         if cuda_graphs and runtime.device.type == "cuda":
-            from mlx_omnia_b200.engine.decode_graph import DecodeGraphs
+            from mlx_omnia_b200.engine.decode_graph import DecodeGraphs, MixedGraphs
 
             if DecodeGraphs.supported(model):
                 self.graphs = DecodeGraphs(self)
+                if MixedGraphs.supported(model):
+                    self.mixed_graphs = MixedGraphs(self)
 
     # -- metadata ----------------------------------------------------------------------
     def take_pages(self, entries: list[StepEntry]) -> list[int]:
@@ -204,8 +206,12 @@ class StepRunner:
         else:
             if device_tokens is not None:
                 raise ValueError("tokens that live on the device can only feed a captured single-token step")
-            step = self.build_context(entries)
-            logits = self.model.forward(step, self.layer_contexts(step))
+            shape = self.mixed_graphs.wants(entries) if self.mixed_graphs is not None and entries else None
+            if shape is not None:
+                logits = self.mixed_graphs.run(shape, entries, copy)
+            else:
+                step = self.build_context(entries)
+                logits = self.model.forward(step, self.layer_contexts(step))
         for entry in entries:
             entry.request.fresh = False
             self.cache.release_behind_window(entry.request)

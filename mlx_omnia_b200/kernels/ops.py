@@ -286,21 +286,55 @@ def _ints_to_device(values, device: torch.device) -> torch.Tensor:
     return out
 
 
-def _prefill_work(step: StepContext, tokens_per_block: int, device: torch.device) -> torch.Tensor:
-    """(request, first token) of every block of `tokens_per_block` query tokens, the blocks
-    that see the most keys first (they run longest); built once per step and shared by all
-    layers."""
+def _step_list(step: StepContext, key, build, device: torch.device) -> torch.Tensor:
+    """A small list of ints that a kernel of this step reads (`build(step)` makes it on the host),
+    made once per step and shared by the layers. A step that is to be captured into a graph (its
+    workspace says `private`) runs once uncaptured first: the list then gets a place of its own
+    and its builder is kept, and the runner fills the list again before every replay of the graph
+    (`fill_step_lists`): a copy made during a capture would be replayed with whatever its staging
+    memory holds by then."""
     if step.workspace is None:
         step.workspace = {}
-    key = ("prefill_work", tokens_per_block)
-    work = step.workspace.get(key)
-    if work is None:
+    held = step.workspace.get(key)
+    if held is None:
+        if step.workspace.get("private"):
+            if torch.cuda.is_current_stream_capturing():
+                raise KernelError(f"the list {key} of a captured step was not made before the capture")
+            held = _ints_to_device(build(step), device).clone()  # a place of its own, kept with the graph
+            step.workspace.setdefault("lists", {})[key] = build
+        else:
+            held = _ints_to_device(build(step), device)
+        step.workspace[key] = held
+    return held
+
+
+def fill_step_lists(step: StepContext) -> None:
+    """Bring the lists of a captured step up to date with the step's host-side numbers (see
+    `_step_list`); each goes to the device from a pinned buffer of its own."""
+    workspace = step.workspace
+    pinned = workspace.setdefault("pinned", {})
+    for key, build in workspace.get("lists", {}).items():
+        values = np.ascontiguousarray(build(step), dtype=np.int32)
+        target = workspace[key]
+        if tuple(values.shape) != tuple(target.shape):
+            raise KernelError(f"the list {key} changed its shape between replays of one captured step")
+        host = pinned.get(key)
+        if host is None:
+            host = pinned[key] = torch.empty(values.shape, dtype=torch.int32).pin_memory()
+        host.numpy()[...] = values
+        target.copy_(host, non_blocking=True)
+
+
+def _prefill_work(step: StepContext, tokens_per_block: int, device: torch.device) -> torch.Tensor:
+    """(request, first token) of every block of `tokens_per_block` query tokens, the blocks
+    that see the most keys first (they run longest)."""
+    def build(step: StepContext) -> np.ndarray:
         items = [(s, t0) for s, n in enumerate(step.q_lens) if n > 1 for t0 in range(0, n, tokens_per_block)]
         if step.seq_lens_host:
             items.sort(key=lambda item: -(step.seq_lens_host[item[0]] - step.q_lens[item[0]] + item[1]))
-        work = _ints_to_device(items, device)
-        step.workspace[key] = work
-    return work
+        return np.asarray(items, dtype=np.int32).reshape(-1, 2)
+
+    return _step_list(step, ("prefill_work", tokens_per_block), build, device)
 
 
 def _prefill_work_flat(step: StepContext, tokens_per_block: int, tile: int, nkv: int, window: int,
@@ -308,13 +342,8 @@ def _prefill_work_flat(step: StepContext, tokens_per_block: int, tile: int, nkv:
     """(request, first token, key/value head) of every block of the tcgen05 prefill kernel, the
     blocks whose tokens see the most key tiles first: blocks are handed to SMs in this order as
     others finish, so the long ones start early and the short ones fill the gaps (measured: 30 %
-    off a 4,096-token prefill against an order that keeps a head's blocks together). Built once
-    per step and window, shared by the layers."""
-    if step.workspace is None:
-        step.workspace = {}
-    key = ("prefill_work_flat", tokens_per_block, tile, nkv, window)
-    work = step.workspace.get(key)
-    if work is None:
+    off a 4,096-token prefill against an order that keeps a head's blocks together)."""
+    def build(step: StepContext) -> np.ndarray:
         parts = []
         for s, n in enumerate(step.q_lens):
             if n <= 1:
@@ -331,23 +360,23 @@ def _prefill_work_flat(step: StepContext, tokens_per_block: int, tile: int, nkv:
                                    np.tile(np.arange(nkv), t0.size)], axis=1))
         table = np.concatenate(parts) if parts else np.zeros((0, 4), dtype=np.int64)
         order = np.argsort(-table[:, 0], kind="stable")
-        work = _ints_to_device(table[order, 1:], device)
-        step.workspace[key] = work
-    return work
+        return table[order, 1:].astype(np.int32)
+
+    return _step_list(step, ("prefill_work_flat", tokens_per_block, tile, nkv, window), build, device)
+
+
+def single_token_longest(step: StepContext) -> int:
+    """The longest of the requests that bring one token to a mixed step (they take the decode kernel)."""
+    return max((n for q, n in zip(step.q_lens, step.seq_lens_host) if q == 1), default=0)
 
 
 def _single_token_requests(step: StepContext, device: torch.device) -> tuple[torch.Tensor | None, int]:
-    """Indices of the requests that bring one token to a mixed step (they take the decode
-    kernel), and the longest of them."""
-    if step.workspace is None:
-        step.workspace = {}
-    held = step.workspace.get("single_token_requests")
-    if held is None:
-        ids = [s for s, n in enumerate(step.q_lens) if n == 1]
-        longest = max((step.seq_lens_host[s] for s in ids), default=0)
-        tensor = _ints_to_device(ids, device) if ids else None
-        held = step.workspace["single_token_requests"] = (tensor, longest)
-    return held
+    """Indices of the requests that bring one token to a mixed step, and the longest of them."""
+    ids = [s for s, n in enumerate(step.q_lens) if n == 1]
+    if not ids:
+        return None, 0
+    return _step_list(step, "single_token_requests", lambda _: np.asarray(ids, dtype=np.int32), device), \
+        single_token_longest(step)
 
 
 def tcgen05_attention_supported(dtype: torch.dtype, nq: int, nkv: int, d: int, page_size: int) -> bool:

@@ -29,6 +29,7 @@ class GQAAttention(Mixer):
     """
 
     graph_safe = True  # no host-side work per request: a decode step can be captured
+    graph_safe_mixed = True  # nor in a step of any other shape: repeated mixed steps can be captured too
     takes_pending = True  # h goes to the in-projection and nowhere else
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, scale: float,

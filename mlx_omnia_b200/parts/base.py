@@ -12,7 +12,9 @@ Interfaces
 Every part:
     ``tensors() -> {local_name: TensorSpec}``   what it loads
     ``load(tensors, runtime)``                  receives exactly those, on the device
-Mixer additionally:
+Mixer additionally (class attributes `graph_safe` / `graph_safe_mixed`: its forward does no
+host-side work per request in a step of single tokens / in any step, so such steps may be
+captured into CUDA graphs):
     ``kv_spec() -> KVSpec | None``              rows it keeps per position, in pages
     ``state_spec() -> StateSpec | None``        fixed-size state it keeps per request
     ``initial_state() -> Tensor | None``        what that state starts as (None: zeros)
