@@ -2,7 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
-The default run builds BASELINE.json's configs[2] (28 layers, hidden 2048, 16/8 heads
+The default run builds the headline model (28 layers, hidden 2048, 16/8 heads
 of 128, intermediate 6144, vocabulary 151936, tied head) with random bfloat16 weights,
 holds 8 requests whose contexts end at 4096 tokens, and times K decode steps.
 `value` is decoded tokens per second timed on the device; `e2e` is the same measured
@@ -135,9 +135,9 @@ def run(args) -> dict:
     weight_bytes, kv_per_token, params = model_bytes(text, layers)
 
     batches = sorted({1, args.batch, 64}) if args.only == "all" else [args.batch]
-    cache_tokens = max(batches) * (args.context + 16) + max(PREFILL_TOKENS, args.prefill_tokens)
+    cache_tokens = max(batches) * (args.context + 16) + max(PREFILL_TOKENS, args.prefill_tokens, 16 * args.portion)
     engine = Engine.from_random(raw, SEED, EngineArgs(dtype="bfloat16", page_size=16, cache_tokens=cache_tokens,
-                                                      max_requests=max(batches)))
+                                                      max_requests=max(batches) + 1))
     g = torch.Generator().manual_seed(SEED)
 
     def prompts(count: int, length: int) -> list[list[int]]:
@@ -307,6 +307,21 @@ def run(args) -> dict:
             timeline.spans()
             prefill(args.prefill_tokens, 1, 0)
             anchor = "attention_tcgen05"
+        elif args.only == "mixed":
+            # Eager steps (a captured shape would be replayed without passing the host-side marks).
+            decoders = [engine.cache.open(f"mixed-{i}") for i in range(args.batch)]
+            reader = engine.cache.open("mixed-reader")
+            if decoders:
+                engine.runner.run([StepEntry(r, p, []) for r, p in zip(decoders, prompts(args.batch, args.context - 4))])
+            graphs, engine.runner.mixed_graphs = getattr(engine.runner, "mixed_graphs", None), None
+            for index in range(3):
+                if index == 2:
+                    torch.cuda.synchronize()
+                    timeline.spans()
+                engine.runner.run([StepEntry(r, [1 + index], [0]) for r in decoders] +
+                                  [StepEntry(reader, prompts(1, args.portion)[0], [])])
+            engine.runner.mixed_graphs = graphs
+            anchor = "attention_tcgen05"
         else:
             length = args.context - 16
             generator = Generator(engine, max_tokens_per_step=args.batch * length)
@@ -326,6 +341,26 @@ def run(args) -> dict:
         part = decode(args.batch, args.steps, args.warmup)
         return {"only": "decode", "batch": args.batch, "layers": layers, "ms_per_step": round(part["ms"], 4),
                 "tokens_per_s": round(part["tokens_per_s"], 1), "context": part["context"]}
+    if args.only == "sampling":  # temperature, top-k and top-p over the full vocabulary, one row a request
+        rows = args.batch
+        logits = torch.randn(rows, vocab, device=engine.runtime.device, dtype=torch.float32) * 2.0
+        f32 = lambda v: torch.full((rows,), v, dtype=torch.float32, device=logits.device)
+        top_k = torch.full((rows,), 50, dtype=torch.int32, device=logits.device)
+        seeds = torch.arange(rows, dtype=torch.int64, device=logits.device)
+        call = lambda: ops.sample(logits, f32(0.8), top_k, f32(0.95), f32(0.0), seeds, seeds)
+        for _ in range(max(args.warmup, 1)):
+            call()
+        start, stop = events()
+        start.record()
+        for _ in range(args.steps):
+            call()
+        stop.record()
+        torch.cuda.synchronize()
+        return {"only": "sampling", "rows": rows, "vocab": vocab, "us": round(start.elapsed_time(stop) * 1e3 / args.steps, 2)}
+    if args.only == "mixed":
+        part = mixed(args.batch, args.portion, args.steps, max(args.warmup, 3))
+        return {"only": "mixed", "decoders": args.batch, "portion": args.portion, "layers": layers,
+                "ms": round(part["ms"], 3), "host_ms": round(part["wall_ms"], 3)}
     if args.only == "prefill":
         part = prefill(args.prefill_tokens, args.steps, args.warmup)
         return {"only": "prefill", "layers": layers, "tokens": args.prefill_tokens, "ms": round(part["ms"], 3),
@@ -391,10 +426,12 @@ def main() -> int:
     parser.add_argument("--timeline", action="store_true",
                         help="with --only decode|prefill and OMNIA_TIMELINE=1 in the environment: one step's "
                              "kernels with the time each takes in the stream, on stderr")
-    parser.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
+    parser.add_argument("--only", choices=["all", "decode", "prefill", "mixed", "sampling"], default="all",
                         help="time one part only (small cases for profilers); prints a short record")
     parser.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds at the last timed step")
     parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
+    parser.add_argument("--portion", type=int, default=256,
+                        help="--only mixed: tokens of a prompt that run beside --batch decoding requests")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

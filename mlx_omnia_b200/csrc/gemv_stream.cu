@@ -108,6 +108,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait; false when the block is giving up (its own limit, or another warp's).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (omnia_mbar_test(bar, parity)) return true;
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
     if (mbar_try(bar, parity)) return true;
     if ((i & 63) == 63 && *abort_flag) return false;

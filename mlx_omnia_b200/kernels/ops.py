@@ -521,13 +521,26 @@ def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
 SKINNY_ROWS = 16
 """Up to this many activation rows, bfloat16 products run on the weight-streaming kernel."""
 
-TENSOR_CORE_ROWS = 129
-"""From this many rows on, bfloat16 products run on this package's tcgen05 kernels. Between the
-streaming kernel's rows and these the vendor library's product stands (inside a replayed graph it
-takes 5 to 11 us for matrices of 8 to 50 MB at 17 to 128 rows). A kernel of this package's own for
-that range (the weights as the 128-row operand of tcgen05.mma, the few activation rows as its
-columns, the k range cut over a thread-block cluster that adds its partial sums through distributed
-shared memory) gave right results and took 11 to 44 us, growing with the rows: it was not kept."""
+FUSED_GATE_ROWS = 640
+FUSED_CAP_ROWS = 129
+"""From these many rows on, the products that have an epilogue fused into them (gate‖up with SwiGLU;
+the head with its soft cap) run on this package's tcgen05 kernels. Measured on B200 inside replayed
+graphs (weights of 8 to 50 MB, fresh for every launch): gate‖up with SwiGLU takes 46.7 us at 1,024
+rows, 87.5 at 2,048 and 305 at 8,192, against 58.7, 112 and 408 for the vendor library's product
+followed by the SwiGLU kernel; below some 600 rows the library's pair is the faster one (23 against
+24 us at 264 rows).
+
+A product with nothing fused into it is the vendor library's above the streaming kernel's rows, as the
+reference's is MLX's. The tcgen05 kernels take the same products (`_gemm_tcgen05`, tested), but the
+library is ahead at every size measured: by 3 to 10 % at 2,048 to 4,096 rows (38.5 against 39.6 us
+for 2,048 x 6,144 x 2,048), by 1.3 to 2.8 times between 129 and 1,024 rows, where 128 x 256 tiles
+are too few for the SMs (12.1 against 33.8 us for 264 x 2,048 x 6,144), and by 10 to 28 % at 8,192.
+Two kernels of this package's own for the rows in between were built, right and deterministic, and
+not kept: the weights as the 128-row operand of tcgen05.mma with the few activation rows as its
+columns (a tcgen05.mma with M = 128 occupies the tensor core for some 80 ns however few columns it
+has, so the weights stream at half the rate of 256-column tiles), and the k range of a 128 x 256 tile
+cut over a thread-block cluster (the exchange of partial sums, 128 KB a block, costs what the cut
+saves: 10.6 to 32 us against the library's 8 to 12)."""
 
 PENDING_MAX_ROWS = 8
 PENDING_MAX_WIDTH = 2048
@@ -539,9 +552,10 @@ def _skinny(a: torch.Tensor, weight: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-def _tensor_core(a: torch.Tensor, weight: torch.Tensor) -> bool:
+def _tensor_core(a: torch.Tensor, weight: torch.Tensor, rows: int) -> bool:
+    """Whether a product with a fused epilogue runs on the tcgen05 kernels (from `rows` rows on)."""
     return (a.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and a.is_cuda
-            and a.shape[0] >= TENSOR_CORE_ROWS and a.shape[1] % 8 == 0 and a.is_contiguous()
+            and a.shape[0] >= rows and a.shape[1] % 8 == 0 and a.is_contiguous()
             and weight.is_contiguous())
 
 
@@ -657,9 +671,9 @@ def _pending_product(step: PendingStep, weight: torch.Tensor, epilogue: int) -> 
 
 def linear(a, weight: torch.Tensor) -> torch.Tensor:
     """a [rows, k] times weight [n, k] transposed -> [rows, n], float32 accumulation.
-    A few bfloat16 rows (a decode step) run on this package's weight-streaming kernel, 129 rows
-    and more on its tcgen05 kernels. Otherwise the matrix product is the vendor library's (as the
-    reference's is MLX's); on the 32-bit path it runs without any reduced-precision mode.
+    A few bfloat16 rows (a decode step) run on this package's weight-streaming kernel, with the
+    pending residual step fused in front. Otherwise the matrix product is the vendor library's (as
+    the reference's is MLX's); on the 32-bit path it runs without any reduced-precision mode.
     `a` may be a PendingStep."""
     if isinstance(a, PendingStep):
         out = _pending_product(a, weight, 0)
@@ -668,8 +682,6 @@ def linear(a, weight: torch.Tensor) -> torch.Tensor:
         a = settle(a)
     if _skinny(a, weight):
         return _gemv_stream(a, weight, torch.empty(a.shape[0], weight.shape[0], dtype=a.dtype, device=a.device), 0)
-    if _tensor_core(a, weight):
-        return _gemm_tcgen05(a, weight, torch.empty(a.shape[0], weight.shape[0], dtype=a.dtype, device=a.device), 0)
     return _library_mm(a, weight)
 
 
@@ -683,7 +695,7 @@ def linear_swiglu(a, gate_up: torch.Tensor) -> torch.Tensor:
         a = settle(a)
     if _skinny(a, gate_up):
         return _gemv_stream(a, gate_up, torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device), 1)
-    if _tensor_core(a, gate_up):
+    if _tensor_core(a, gate_up, FUSED_GATE_ROWS):
         return _gemm_tcgen05(a, gate_up, torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device), 1)
     return swiglu(_library_mm(a, gate_up))
 
@@ -693,7 +705,7 @@ def linear_softcap(a: torch.Tensor, weight: torch.Tensor, multiplier: float, cap
     if _skinny(a, weight):
         out = torch.empty(a.shape[0], weight.shape[0], dtype=torch.float32, device=a.device)
         return _gemv_stream(a, weight, out, 2, multiplier, cap or 0.0)
-    if _tensor_core(a, weight):
+    if _tensor_core(a, weight, FUSED_CAP_ROWS):
         out = torch.empty(a.shape[0], weight.shape[0], dtype=torch.float32, device=a.device)
         return _gemm_tcgen05(a, weight, out, 2, multiplier, cap or 0.0)
     return softcap(_library_mm(a, weight), multiplier, cap)
