@@ -43,6 +43,18 @@ CONFIG2 = {
         "tie_word_embeddings": True,
     },
 }
+CONFIG3 = {
+    "architectures": ["MuseGlimmerForConditionalGeneration"], "model_type": "muse_glimmer",
+    "text_config": {
+        "hidden_size": 4096, "intermediate_size": 12288, "num_hidden_layers": 36, "num_attention_heads": 32,
+        "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 151936, "rms_norm_eps": 1e-6, "post_norm_eps": 1e-6,
+        "sliding_window": 8192, "qk_scale_factor": 1.0, "output_multiplier": 1.0, "final_logit_softcapping": 30.0,
+        "layer_types": ["full_attention"] * 36, "layer_rope_theta": [1000000.0] * 36,
+        "rope_parameters": {"rope_theta": 1000000.0, "rope_type": "default"}, "eos_token_id": [],
+        "tie_word_embeddings": False,
+    },
+}
+CONFIGS = {2: (CONFIG2, 4096), 3: (CONFIG3, 8192)}  # the sizes and the context of a benchmark configuration
 SEED = 2
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
@@ -124,7 +136,7 @@ def run(args) -> dict:
     from mlx_omnia_b200.kernels import ops
     from mlx_omnia_b200.sampling import GenerationOptions
 
-    raw = json.loads(json.dumps(CONFIG2))
+    raw = json.loads(json.dumps(CONFIGS[args.config][0]))
     text = raw["text_config"]
     full_layers = text["num_hidden_layers"]
     layers = args.layers or full_layers
@@ -339,8 +351,83 @@ def run(args) -> dict:
         return {"only": args.only, "timeline": True, "kernels": len(kernels), "layers": layers}
     if args.only == "decode":  # a small case for profilers: one batch size, no prefill timing
         part = decode(args.batch, args.steps, args.warmup)
-        return {"only": "decode", "batch": args.batch, "layers": layers, "ms_per_step": round(part["ms"], 4),
-                "tokens_per_s": round(part["tokens_per_s"], 1), "context": part["context"]}
+        step_bytes = weight_bytes + args.batch * part["context"] * kv_per_token
+        return {"only": "decode", "config": args.config, "batch": args.batch, "layers": layers,
+                "ms_per_step": round(part["ms"], 4), "tokens_per_s": round(part["tokens_per_s"], 1),
+                "context": part["context"], "step_gb": round(step_bytes / 1e9, 2),
+                "hbm_frac": round(step_bytes / (part["ms"] / 1e3) / 1e9 / measured["hbm_gbs"], 3)}
+    def replayed(body, sets: int, rounds: int = 10) -> float:
+        """Microseconds per call of `body(i)`, i over `sets` operand sets, replayed from a graph."""
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for i in range(sets):
+                body(i)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(sets):
+                    body(i)
+        torch.cuda.synchronize()
+        graph.replay()
+        start, stop = events()
+        start.record()
+        for _ in range(rounds):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) * 1e3 / (rounds * sets)
+
+    if args.only == "products":
+        # A layer's four products at several row counts: this package's kernels (the streaming kernel up
+        # to 16 rows, the one-SM and the two-SM tcgen05 kernels) beside the vendor library's product
+        # (followed by the SwiGLU kernel for gate|up); weights fresh for every launch.
+        device = engine.runtime.device
+        h, inner = text["hidden_size"], text["intermediate_size"]
+        q, kv = text["num_attention_heads"] * text["head_dim"], text["num_key_value_heads"] * text["head_dim"]
+        shapes = {"qkv": (2 * q + 2 * kv, h, 0), "o": (h, q, 0), "gate_up": (2 * inner, h, 1), "down": (h, inner, 0)}
+        draw = lambda *shape: torch.randn(*shape, device=device, dtype=torch.bfloat16) * 0.05
+        table = {}
+        for rows in (8, 16, 32, 64, 128, 264, 512, 1024, 2048, 4096, 8192):
+            for name, (n, k, epilogue) in shapes.items():
+                weights, a = [draw(n, k) for _ in range(6)], draw(rows, k) * 20
+                out = torch.empty(rows, n // 2 if epilogue else n, dtype=torch.bfloat16, device=device)
+                def library(i):
+                    z = torch.mm(a, weights[i].t())
+                    return ops.swiglu(z) if epilogue else z
+                entry = {"library": round(replayed(library, 6), 1)}
+                if rows <= 16:
+                    entry["streaming"] = round(replayed(lambda i: ops._gemv_stream(a, weights[i], out, epilogue), 6), 1)
+                if rows >= 128:
+                    entry["one_sm"] = round(replayed(lambda i: ops._gemm_tcgen05(a, weights[i], out, epilogue, pair=False), 6), 1)
+                if rows >= 256:
+                    entry["two_sm"] = round(replayed(lambda i: ops._gemm_tcgen05(a, weights[i], out, epilogue, pair=True), 6), 1)
+                table[f"{name}_{rows}"] = entry
+        ops.raise_on_error(device)
+        return {"only": "products", "config": args.config, "unit": "us", "products": table}
+    if args.only == "elementwise":
+        # The prefill step's element-wise kernels alone, buffers fresh for every launch.
+        from mlx_omnia_b200.parts.base import KVView
+        device = engine.runtime.device
+        tokens, h, d = args.prefill_tokens, text["hidden_size"], text["head_dim"]
+        nq, nkv = text["num_attention_heads"], text["num_key_value_heads"]
+        xs = [torch.randn(tokens, h, device=device) for _ in range(8)]
+        branches = [torch.randn(tokens, h, device=device).bfloat16() for _ in range(8)]
+        wb, wo = torch.rand(h, device=device) + 0.5, torch.rand(h, device=device) + 0.5
+        residual = replayed(lambda i: ops.add_rmsnorm(xs[i], branches[i], wb, 1e-6, wo, 1e-6), 8)
+        rows = [torch.randn(tokens, (2 * nq + 2 * nkv) * d, device=device).bfloat16() for _ in range(8)]
+        pages = [torch.zeros(-(-tokens // 16), 2, nkv, 16, d, device=device, dtype=torch.bfloat16) for _ in range(8)]
+        inv_freq = 1.0 / (1e6 ** (torch.arange(0, d, 2, device=device).float() / d))
+        positions = torch.arange(tokens, device=device, dtype=torch.int32)
+        slots = torch.arange(tokens, device=device, dtype=torch.int64)
+        blocks = torch.arange(-(-tokens // 16), device=device, dtype=torch.int32).view(1, -1)
+        rope = replayed(lambda i: ops.qk_norm_rope_store(rows[i], 0, 2 * nq * d, (2 * nq + nkv) * d, nq, nkv, d, 1e-6, inv_freq,
+                                                         positions, KVView(pages[i], blocks, slots, 16, None)), 8)
+        moved = {"add_rmsnorm": tokens * h * (4 + 2 + 4 + 2), "qk_norm_rope_store": tokens * (nq + 2 * nkv) * d * 2 * 2}
+        ops.raise_on_error(device)
+        return {"only": "elementwise", "config": args.config, "tokens": tokens,
+                "add_rmsnorm": {"us": round(residual, 2), "frac": round(moved["add_rmsnorm"] / residual / 1e3 / measured["hbm_gbs"], 3)},
+                "qk_norm_rope_store": {"us": round(rope, 2),
+                                       "frac": round(moved["qk_norm_rope_store"] / rope / 1e3 / measured["hbm_gbs"], 3)}}
     if args.only == "sampling":  # temperature, top-k and top-p over the full vocabulary, one row a request
         rows = args.batch
         logits = torch.randn(rows, vocab, device=engine.runtime.device, dtype=torch.float32) * 2.0
@@ -363,8 +450,8 @@ def run(args) -> dict:
                 "ms": round(part["ms"], 3), "host_ms": round(part["wall_ms"], 3)}
     if args.only == "prefill":
         part = prefill(args.prefill_tokens, args.steps, args.warmup)
-        return {"only": "prefill", "layers": layers, "tokens": args.prefill_tokens, "ms": round(part["ms"], 3),
-                "frac": round(part["frac"], 4)}
+        return {"only": "prefill", "config": args.config, "layers": layers, "tokens": args.prefill_tokens,
+                "ms": round(part["ms"], 3), "frac": round(part["frac"], 4)}
     with ClockSampler() as sampler:
         main = decode(args.batch, args.steps, args.warmup)
     clocks = sampler.summary()
@@ -426,9 +513,13 @@ def main() -> int:
     parser.add_argument("--timeline", action="store_true",
                         help="with --only decode|prefill and OMNIA_TIMELINE=1 in the environment: one step's "
                              "kernels with the time each takes in the stream, on stderr")
-    parser.add_argument("--only", choices=["all", "decode", "prefill", "mixed", "sampling"], default="all",
+    parser.add_argument("--only", choices=["all", "decode", "prefill", "mixed", "sampling", "products", "elementwise"], default="all",
                         help="time one part only (small cases for profilers); prints a short record")
-    parser.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds at the last timed step")
+    parser.add_argument("--config", type=int, choices=sorted(CONFIGS), default=2,
+                        help="with --only: the sizes of another benchmark configuration (3: 36 layers, hidden 4096, "
+                             "32/8 heads, intermediate 12288, untied head, context 8192)")
+    parser.add_argument("--context", type=int, default=0, help="tokens each request holds at the last timed step "
+                                                               "(default: the configuration's own)")
     parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
     parser.add_argument("--portion", type=int, default=256,
                         help="--only mixed: tokens of a prompt that run beside --batch decoding requests")
@@ -441,6 +532,10 @@ def main() -> int:
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
         return 2
+    if args.config != 2 and args.only == "all":
+        print("bench.py: the full record is of configuration 2; give --only decode|prefill|mixed with --config")
+        return 2
+    args.context = args.context or CONFIGS[args.config][1]
     if args.only == "all":
         args.warmup = max(args.warmup, 3)
     print(json.dumps(run(args)))
