@@ -1,7 +1,8 @@
 """Each part alone against the plain implementation's function for it, and the
 generality of the composition: a schedule that names a layer twice or lets a layer
 read another's cache, and a toy mixer with state of its own that is registered, built
-and stepped from this file without touching the framework."""
+and stepped from this file without touching the framework; likewise a toy feed-forward
+that routes each token to two of its experts and a toy position encoding."""
 
 from __future__ import annotations
 
@@ -13,10 +14,12 @@ import tiny_configs
 from mlx_omnia_b200.cache import CacheManager
 from mlx_omnia_b200.engine.engine import Engine, EngineArgs
 from mlx_omnia_b200.engine.step import StepEntry, StepRunner
+from mlx_omnia_b200.kernels import ops
 from mlx_omnia_b200.parts import (DecoderModel, LayerSpec, ModelSpec, PartSpec, Runtime, ScheduleEntry, StateSpec,
                                   register_mixer)
-from mlx_omnia_b200.parts.base import (FEED_FORWARDS, HEADS, EMBEDDINGS, MIXERS, NORMS, POSITIONS, Embedding, KVSpec,
-                                       Mixer, TensorSpec, register_embedding)
+from mlx_omnia_b200.parts.base import (FEED_FORWARDS, HEADS, EMBEDDINGS, MIXERS, NORMS, POSITIONS, Embedding, FeedForward,
+                                       KVSpec, Mixer, Position, TensorSpec, register_embedding, register_feed_forward,
+                                       register_position)
 from mlx_omnia_b200.architectures.muse_glimmer import model_spec, parse
 
 pytestmark = pytest.mark.gpu
@@ -363,3 +366,136 @@ def test_a_toy_mixer_with_state_decodes_from_a_captured_graph():
     got = torch.stack(rows)  # [5, 3, vocab]
     for i, p in enumerate(prompts):
         assert plain_impl.relative_diff(got[:, i], plain(p)[-5:]) < 2e-5, i
+
+
+# ---- a feed-forward with routing and another position encoding, again only here -------------------
+
+
+@register_feed_forward("toy_routed_experts")
+class ToyRoutedExperts(FeedForward):
+    """Every token goes to the `top` experts with the largest router logits (float32), weighted by the
+    softmax over those logits; an expert is a small gated MLP run on the package's products."""
+
+    def __init__(self, hidden: int, inner: int, experts: int, top: int) -> None:
+        self.hidden, self.inner, self.experts, self.top = hidden, inner, experts, top
+
+    def tensors(self):
+        out = {"router.weight": TensorSpec((self.experts, self.hidden))}
+        for e in range(self.experts):
+            out[f"experts.{e}.gate_up.weight"] = TensorSpec((2 * self.inner, self.hidden))
+            out[f"experts.{e}.down.weight"] = TensorSpec((self.hidden, self.inner))
+        return out
+
+    def load(self, tensors, runtime):
+        super().load(tensors, runtime)
+        self.w = tensors
+
+    def forward(self, h, ctx):
+        logits = h.float() @ self.w["router.weight"].float().t()
+        best, chosen = torch.topk(logits, self.top, dim=-1)
+        share = torch.softmax(best, dim=-1)
+        out = torch.zeros(h.shape[0], self.hidden, dtype=torch.float32, device=h.device)
+        for e in range(self.experts):
+            rows, place = torch.nonzero(chosen == e, as_tuple=True)
+            if rows.numel() == 0:
+                continue
+            act = ops.linear_swiglu(h[rows].contiguous(), self.w[f"experts.{e}.gate_up.weight"])
+            out.index_add_(0, rows, ops.linear(act, self.w[f"experts.{e}.down.weight"]).float() * share[rows, place, None])
+        return out.to(h.dtype)
+
+
+@register_position("toy_interpolated_rotary")
+class ToyInterpolatedRotary(Position):
+    """Rotary angles of positions divided by `factor` (linear position interpolation)."""
+
+    def __init__(self, dims: int, theta: float, factor: float) -> None:
+        self.dims, self.theta, self.factor = dims, theta, factor
+
+    def load(self, tensors, runtime):
+        super().load(tensors, runtime)
+        exponent = torch.arange(self.dims // 2, dtype=torch.float64) * (2.0 / self.dims)
+        self._table = (torch.pow(torch.tensor(self.theta, dtype=torch.float64), -exponent) / self.factor).float().to(runtime.device)
+
+    def table(self):
+        return self._table
+
+
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding():
+    """A layer whose feed-forward routes tokens to two of five experts and whose attention rotates by
+    interpolated positions, beside a layer of the architecture's own parts: built from data, stepped
+    whole, in portions and token by token, mixed with another request, against plain PyTorch."""
+    hidden, vocab, inner, experts, top, factor = 40, 60, 24, 5, 2, 4.0
+    norm = PartSpec("rms_norm", {"size": hidden, "eps": 1e-5, "weight": "plain"})
+    norms = {"input_layernorm": norm, "post_attention_layernorm": norm}
+    attention = lambda position: PartSpec("gqa_attention", {"hidden": hidden, "heads": 4, "kv_heads": 2, "head_dim": 16,
+                                                            "scale": 0.25, "position": position})
+    routed = PartSpec("pre_norm", {"mixer": attention(PartSpec("toy_interpolated_rotary", {"dims": 16, "theta": 50.0, "factor": factor})),
+                                   "feed_forward": PartSpec("toy_routed_experts", {"hidden": hidden, "inner": inner,
+                                                                                   "experts": experts, "top": top}),
+                                   "norms": norms})
+    dense = PartSpec("pre_norm", {"mixer": attention(PartSpec("rotary", {"dims": 16, "theta": 50.0})),
+                                  "feed_forward": PartSpec("gated_mlp", {"hidden": hidden, "inner": 56}), "norms": norms})
+    spec = ModelSpec(PartSpec("token_embedding", {"vocab": vocab, "hidden": hidden}),
+                     (LayerSpec(routed, "layers.0"), LayerSpec(dense, "layers.1")), (ScheduleEntry(0), ScheduleEntry(1)), norm,
+                     PartSpec("lm_head", {"vocab": vocab, "hidden": hidden}),
+                     embedding_prefix="embed", final_norm_prefix="final_norm", head_prefix="head")
+    model = DecoderModel(spec)
+    g = torch.Generator().manual_seed(11)
+    w = {name: (torch.randn(*s.shape, generator=g) * (0.3 if s.kind == "matrix" else 0.1) + (s.kind == "vector"))
+         for name, s in model.tensors().items()}
+    rt = runtime()
+    model.load({k: v.to(CUDA) for k, v in w.items()}, rt)
+
+    routes = []
+
+    def plain(ids):
+        positions = torch.arange(len(ids))
+        x = w["embed.weight"][ids]
+        rms = lambda v, name: plain_impl.rms_norm(v, w[name], 1e-5)
+        causal = plain_impl.visible(positions, positions, None)
+        for prefix, scale in (("layers.0", factor), ("layers.1", 1.0)):
+            h = rms(x, f"{prefix}.input_layernorm.weight")
+            a = plain_impl.sub(w, f"{prefix}.self_attn.")
+            q = (h @ a["q_proj.weight"].t()).reshape(-1, 4, 16)
+            k = (h @ a["k_proj.weight"].t()).reshape(-1, 2, 16)
+            v = (h @ a["v_proj.weight"].t()).reshape(-1, 2, 16)
+            rot = lambda z: plain_impl.rope(z, positions / scale, 50.0)
+            x = x + plain_impl.attention_core(rot(q), rot(k), v, causal, 0.25) @ a["o_proj.weight"].t()
+            h = rms(x, f"{prefix}.post_attention_layernorm.weight")
+            if prefix == "layers.1":
+                x = x + plain_impl.swiglu(h, plain_impl.sub(w, f"{prefix}.mlp."))
+                continue
+            m = plain_impl.sub(w, f"{prefix}.mlp.")
+            best, chosen = torch.topk(h @ m["router.weight"].t(), top, dim=-1)
+            share = torch.softmax(best, dim=-1)
+            routes.append(chosen)
+            rows = []
+            for t in range(len(ids)):
+                row = torch.zeros(hidden)
+                for j in range(top):
+                    e = int(chosen[t, j])
+                    gu = h[t] @ m[f"experts.{e}.gate_up.weight"].t()
+                    act = torch.nn.functional.silu(gu[:inner]) * gu[inner:]
+                    row = row + share[t, j] * (act @ m[f"experts.{e}.down.weight"].t())
+                rows.append(row)
+            x = x + torch.stack(rows)
+        return rms(x, "final_norm.weight") @ w["head.weight"].t()
+
+    cache = CacheManager(model.cache_needs(), page_size=4, pages_per_group=32, max_requests=2, dtype=torch.float32, device=CUDA)
+    runner = StepRunner(model, cache, rt)
+    a, b = tiny_configs.prompt(23, vocab, 5), tiny_configs.prompt(11, vocab, 6)
+    ra, rb = cache.open("a"), cache.open("b")
+    got_a = [runner.run([StepEntry(ra, a[:10], list(range(10)))])]
+    mixed = runner.run([StepEntry(ra, a[10:12], [0, 1]), StepEntry(rb, b[:7], list(range(7)))])
+    got_a.append(mixed[:2])
+    got_b = [mixed[2:]]
+    for t in range(12, 23):
+        step = [StepEntry(ra, a[t:t + 1], [0])] + ([StepEntry(rb, b[7:], list(range(4)))] if t == 12 else [])
+        out = runner.run(step)
+        got_a.append(out[:1])
+        if t == 12:
+            got_b.append(out[1:])
+    assert plain_impl.relative_diff(torch.cat(got_a), plain(a)) < 2e-5
+    assert plain_impl.relative_diff(torch.cat(got_b), plain(b)) < 2e-5
+    assert len(set(torch.cat(routes).flatten().tolist())) == experts  # the routing is not trivial: every expert is used
+    cache.check()
