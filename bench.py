@@ -10,8 +10,9 @@ through the Python entry point's generation loop, which copies every step's inpu
 from pinned host memory and reads the chosen tokens back. `prefill` is one step of
 2,048 prompt tokens; `roofline` relates the decode step's time to the bytes it must
 read (every weight once, and the live requests' cache). `points` holds decode at
-batch 1 and 64 and two mixed steps (milliseconds a step: eight decoding requests at
-4,096 tokens beside a 256-token portion of a prompt, and a lone 128-token portion).
+batch 1 and 64, two mixed steps (milliseconds a step: eight decoding requests at
+4,096 tokens beside a 256-token portion of a prompt, and a lone 128-token portion) and the
+time to read a prompt of 8,192 tokens in portions of 512 (a token budget).
 `kernels` times each class of kernel alone (operands rotated through more memory than
 L2 holds, replayed from a CUDA graph) against the measured peaks: the streamed product
 of a decode step, the head, decode attention (GB/s), the prefill product and prefill
@@ -147,7 +148,9 @@ def run(args) -> dict:
     weight_bytes, kv_per_token, params = model_bytes(text, layers)
 
     batches = sorted({1, args.batch, 64}) if args.only == "all" else [args.batch]
-    cache_tokens = max(batches) * (args.context + 16) + max(PREFILL_TOKENS, args.prefill_tokens, 16 * args.portion)
+    cache_tokens = max(batches) * (args.context + 16) + max(PREFILL_TOKENS, args.prefill_tokens,
+                                                              32768 + 16 if args.only == "portions" else 8192 + 16,
+                                                              (max(args.steps, 8) + max(args.warmup, 3) + 2) * args.portion)
     engine = Engine.from_random(raw, SEED, EngineArgs(dtype="bfloat16", page_size=16, cache_tokens=cache_tokens,
                                                       max_requests=max(batches) + 1))
     g = torch.Generator().manual_seed(SEED)
@@ -232,6 +235,23 @@ def run(args) -> dict:
         for r in requests + [reader]:
             engine.cache.close(r.request_id)
         return {"ms": statistics.median(times), "wall_ms": statistics.median(walls)}
+
+    def portions(total: int, portion: int) -> float:
+        """Milliseconds to read a prompt of `total` tokens in portions of `portion` (a token budget), warm."""
+        best = None
+        for attempt in range(3):
+            request = engine.cache.open(f"portions-{attempt}")
+            ids = prompts(1, total)[0]
+            torch.cuda.synchronize()
+            start, stop = events()
+            start.record()
+            for at in range(0, total, portion):
+                engine.runner.run([StepEntry(request, ids[at:at + portion], [portion - 1] if at + portion >= total else [])])
+            stop.record()
+            torch.cuda.synchronize()
+            engine.cache.close(request.request_id)
+            best = start.elapsed_time(stop) if best is None else min(best, start.elapsed_time(stop))
+        return best
 
     def kernel_classes() -> dict:
         """Each class of kernel alone, replayed from a graph over operands that do not fit L2."""
@@ -377,6 +397,19 @@ def run(args) -> dict:
         torch.cuda.synchronize()
         return start.elapsed_time(stop) * 1e3 / (rounds * sets)
 
+    if args.only == "portions":
+        # Prompts read in portions (a token budget): milliseconds for the whole prompt, with the attention
+        # kernel's blocks cut into parts as the dispatch cuts them, and whole (no part shorter than a
+        # million tiles).
+        record = {"only": "portions", "config": args.config, "layers": layers, "unit": "ms"}
+        kept = ops.PREFILL_MIN_PART_TILES
+        for label, least in (("in_parts", kept), ("whole_blocks", 10 ** 6)):
+            ops.PREFILL_MIN_PART_TILES = least
+            record[label] = {f"{total}_in_{portion}": round(portions(total, portion), 2)
+                             for total, portion in ((8192, 512), (8192, 256), (32768, 1024), (32768, 512))}
+        ops.PREFILL_MIN_PART_TILES = kept
+        ops.raise_on_error(engine.runtime.device)
+        return record
     if args.only == "products":
         # A layer's four products at several row counts: this package's kernels (the streaming kernel up
         # to 16 rows, the one-SM and the two-SM tcgen05 kernels) beside the vendor library's product
@@ -462,6 +495,7 @@ def run(args) -> dict:
         part = mixed(decoders, portion, 8, 3)
         points[name + "_ms"] = round(part["ms"], 3)
         points[name + "_host_ms"] = round(part["wall_ms"], 3)
+    points["prefill_8192_in_portions_of_512_ms"] = round(portions(8192, 512), 2)
     kernels = kernel_classes()
     ops.raise_on_error(engine.runtime.device)
 
@@ -513,7 +547,7 @@ def main() -> int:
     parser.add_argument("--timeline", action="store_true",
                         help="with --only decode|prefill and OMNIA_TIMELINE=1 in the environment: one step's "
                              "kernels with the time each takes in the stream, on stderr")
-    parser.add_argument("--only", choices=["all", "decode", "prefill", "mixed", "sampling", "products", "elementwise"], default="all",
+    parser.add_argument("--only", choices=["all", "decode", "prefill", "mixed", "portions", "sampling", "products", "elementwise"], default="all",
                         help="time one part only (small cases for profilers); prints a short record")
     parser.add_argument("--config", type=int, choices=sorted(CONFIGS), default=2,
                         help="with --only: the sizes of another benchmark configuration (3: 36 layers, hidden 4096, "

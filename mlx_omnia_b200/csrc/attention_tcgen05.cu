@@ -26,6 +26,13 @@
 // request's last page) are cleared in the V tile, so whatever a page's previous owner left
 // there (a NaN included) meets its zero weight as a zero.
 //
+// A block that would walk many tiles (a portion of a prompt over a long context; the last blocks of a
+// long prompt) can be listed as several PARTS, each a run of the block's key tiles: a part leaves its
+// unnormalised accumulator, its exponent offset and its sum in a workspace (float32, laid out so that
+// a warp's accesses are whole lines), draws a ticket, and the part that draws the last one adds the
+// parts in their order (the result does not depend on which part came last), normalises, applies
+// the gate and stores. Nobody waits for another block.
+//
 // Every wait on a barrier is bounded: when the bound is hit the block raises OMNIA_ERR_TIMEOUT
 // in the error word, every role leaves its loop, the producer waits (bounded) for loads in
 // flight, the block frees its tensor memory and returns.
@@ -200,6 +207,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// The four softmax warps among themselves.
+__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 #ifdef ATTN_TIMING
 // Debug build only: nanosecond stamps of block (0, 0), read back with omnia_attention_timing.
 __device__ unsigned long long g_timing[8192];
@@ -218,15 +228,23 @@ __device__ __forceinline__ void stamp(int slot) {
 }  // namespace
 
 // grid (blocks of the work list); THREADS threads. work[b] = (request, first token of the block among
-// the request's tokens of this step, key/value head); the caller lists the longest blocks first.
+// the request's tokens of this step, key/value head, first key tile of this part counted from the
+// block's first, tiles of this part (< 0: all the block's), parts of the block + 256 x this part's
+// number, place of the block's first part in the workspace, number of the block among the split
+// ones); request < 0: nothing to do. The caller lists the longest first.
+constexpr int WORK_INTS = 8;
+constexpr int MAX_PARTS = 16;
+constexpr int PART_FLOATS = BM * D + 2 * BM;  // a part in the workspace: O as [D / 4][128 rows] float4, then offsets, then sums
 __global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                                  const __grid_constant__ CUtensorMap map_gate, int gate_tma,
                                  const int* __restrict__ block_table, const int* __restrict__ cu_seqlens,
                                  const int* __restrict__ seq_lens, const int* __restrict__ work,
                                  const bf16* __restrict__ gate, int gate_stride, bf16* __restrict__ out,
+                                 float* __restrict__ partial, int* __restrict__ tickets,
                                  int max_pages, int num_pages, int nq, int nkv, int page_size, int window,
                                  float scale, int* err) {
+  if (work[WORK_INTS * blockIdx.x] < 0) return;  // a place of the list that this step does not use
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // The swizzled tiles need a base on 1024 bytes; the dynamic area starts on one (nothing static
   // precedes it). Two blocks per SM leave no room for padding, so this is checked, not forced.
@@ -242,16 +260,22 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   volatile uint32_t* group_mask = reinterpret_cast<volatile uint32_t*>(tmem_holder + 2);  // [V_STAGES]
+  volatile int* drawn = reinterpret_cast<volatile int*>(tmem_holder + 2 + V_STAGES);  // the ticket this part drew
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = work[3 * blockIdx.x], tok0 = work[3 * blockIdx.x + 1], kvh = work[3 * blockIdx.x + 2];
+  const int* item = work + WORK_INTS * blockIdx.x;
+  const int seq = item[0], tok0 = item[1], kvh = item[2], parts = item[5] & 255, part = item[5] >> 8, slot0 = item[6],
+            unit = item[7];
   const int q_begin = cu_seqlens[seq], q_len = cu_seqlens[seq + 1] - q_begin;
   const int pos0 = seq_lens[seq] - q_len + tok0;      // position of the block's first token
   const int tokens = min(TOKENS, q_len - tok0);
   const int rows = tokens * GROUP;
   const int last = pos0 + tokens - 1;                                   // last key any row sees
   const int first = window > 0 ? max(0, pos0 - window + 1) : 0;         // first key any row sees
-  const int tile0 = first / BN, n_tiles = last / BN - tile0 + 1;
+  const int last_tile = last / BN;
+  const int tile0 = first / BN + (item[4] < 0 ? 0 : item[3]);
+  const int n_tiles = item[4] < 0 ? last_tile - tile0 + 1 : item[4];
+  const bool whole = parts <= 1;  // this block does all of its rows' keys and stores the result itself
 
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t q_full = bar0, k_full0 = bar0 + 8, v_full0 = k_full0 + 8 * K_STAGES, v_done0 = v_full0 + 8 * V_STAGES,
@@ -431,7 +455,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       ok = mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (j == n_tiles - 1 && row == 0 && gate_tma) {
+      if (whole && j == n_tiles - 1 && row == 0 && gate_tma) {
         // The last scores are there, so Q has been read for the last time: the block's gate
         // values (the same rows and columns as Q, of another matrix) take its place, on their
         // way while the last softmax and product run.
@@ -445,7 +469,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       const uint32_t s_addr = tmem_base + lane_field + S_COL + (j & 1) * BN;
       // Which keys of the tile this row sees; a tile that the whole warp sees whole needs no masks.
       const int lo = max(row_lo - key0, 0), hi = min(row_hi - key0, BN - 1);  // visible columns [lo, hi]
-      const bool whole = __all_sync(0xffffffffu, lo == 0 && hi == BN - 1);
+      const bool unmasked = __all_sync(0xffffffffu, lo == 0 && hi == BN - 1);
       // The row's 64 scores, read once; then their maximum.
       static_assert(BN == 64, "the softmax below handles one 64-column pass per tile");
       uint32_t v[64];
@@ -453,7 +477,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       tmem_load32(s_addr + 32, v + 32);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       float tile_max = -INFINITY;
-      if (whole) {
+      if (unmasked) {
         float part[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one of 64
 #pragma unroll
         for (int i = 0; i < 64; ++i) part[i & 3] = fmaxf(part[i & 3], __uint_as_float(v[i]));
@@ -480,7 +504,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       // P = exp2(s * scale * log2e - offset), rounded to bfloat16.
       float sums[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[32];
-      if (whole) {
+      if (unmasked) {
 #pragma unroll
         for (int i = 0; i < 64; i += 2) {
           const float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), sl2, -offset));
@@ -526,7 +550,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       tmem_store32(s_addr, packed);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       l += sum;
-      if (j == n_tiles - 1 && ((last + 1) & 15)) {
+      if (tile0 + j == last_tile && ((last + 1) & 15)) {
         // The last group of 16 keys reaches past the block's last key. Those rows of V get a
         // zero weight, but what they hold need not be a number: past the request's last token
         // the page still holds whatever its previous owner left (0 x NaN is NaN). Clear them in
@@ -557,10 +581,58 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const bf16* gp = gate ? gate + token * gate_stride + (size_t)head * D : nullptr;
     const bool gate_wide = gp != nullptr && (reinterpret_cast<uintptr_t>(gp) & 15) == 0;
     if (ok) ok = mbar_wait(v_done0 + 8 * ((n_tiles - 1) % V_STAGES), ((n_tiles - 1) / V_STAGES) & 1, abort_flag);
-    if (ok && gate_tma) ok = mbar_wait(g_full, 0, abort_flag);
+    if (ok && whole && gate_tma) ok = mbar_wait(g_full, 0, abort_flag);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     OMNIA_TRACE_IF(row == 0, 7);
-    if (ok) {
+    if (!whole) {
+      // ---- a part: leave O, the exponent's offset and the sum in the workspace, draw a ticket. The
+      // four warps stay together through the named barriers whatever `ok` says. -----------------------
+      float* mine = partial + (size_t)(slot0 + part) * PART_FLOATS;
+      if (ok) {
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t o[32];
+          tmem_load32(tmem_base + lane_field + O_COL + c, o);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            __stcg(reinterpret_cast<float4*>(mine) + (size_t)((c + i) / 4) * BM + row,
+                   make_float4(__uint_as_float(o[i]), __uint_as_float(o[i + 1]), __uint_as_float(o[i + 2]),
+                               __uint_as_float(o[i + 3])));
+        }
+        __stcg(mine + BM * D + row, m == -INFINITY ? -INFINITY : m * sl2);
+        __stcg(mine + BM * D + BM + row, l);
+      }
+      __threadfence();
+      softmax_sync();
+      if (row == 0) *drawn = *abort_flag ? -1 : atomicAdd(tickets + unit, 1);
+      softmax_sync();
+      if (*drawn == parts - 1) {
+        // ---- the last part to arrive: every row's weights of the parts (the exponent offsets brought
+        // to their largest) and the reciprocal of its sum go to shared memory, in the K ring's place;
+        // all eight warps then add the parts (below, behind the block's barrier) ---------------------
+        __threadfence();
+        if (row == 0) tickets[unit] = 0;  // for the next launch
+        if (row == 0 && gate_tma) {
+          // Q has been read for the last time: the gate values of the block's rows take its place.
+          mbar_expect_tx(g_full, DH * ROWS * 128);
+          for (int h = 0; h < DH; ++h)
+            tma_load_3d(smem_u32(q_s) + h * HALF_BYTES, &map_gate, g_full, h * 64, kvh * GROUP, q_begin + tok0);
+        }
+        const float* all = partial + (size_t)slot0 * PART_FLOATS;
+        float* weights = reinterpret_cast<float*>(k_s);  // [parts + 1][128]: the parts' weights, then 1 / sum
+        float top = -INFINITY, total = 0.f;
+        for (int q = 0; q < parts; ++q) top = fmaxf(top, __ldcg(all + (size_t)q * PART_FLOATS + BM * D + row));
+        for (int q = 0; q < parts; ++q) {
+          const float offset = __ldcg(all + (size_t)q * PART_FLOATS + BM * D + row);
+          const float w = offset != -INFINITY ? fast_exp2(offset - top) : 0.f;
+          weights[q * BM + row] = w;
+          total += w * __ldcg(all + (size_t)q * PART_FLOATS + BM * D + BM + row);
+        }
+        weights[parts * BM + row] = total > 0.f ? 1.f / total : 0.f;
+      }
+    }
+    if (ok && whole) {
       // Eight dims a turn, the next turn's accumulator columns already on their way.
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = out + (token * nq + head) * D;
@@ -602,7 +674,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
         for (int i = 0; i < 8; ++i) cur[i] = next[i];
       }
-    } else if (gate_issued) {
+    } else if (whole && gate_issued) {
       // Giving up: the gate's copy must land before the block's shared memory goes away.
       for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(g_full, 0); ++i) {
       }
@@ -611,6 +683,62 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (!whole && *drawn == parts - 1) {
+    // ---- the merge, by all eight warps: an item is eight dims of a row, neighbouring threads take
+    // neighbouring rows (whole lines of the workspace), the parts are added in their order ------------
+    static_assert((MAX_PARTS + 1) * BM * sizeof(float) <= K_STAGES * K_BYTES, "the parts' weights fit the K ring's place");
+    bool merged = true;
+    if (gate_tma) {
+      merged = mbar_wait(g_full, 0, abort_flag);
+      // Giving up: the gate's copy must still land before the block's shared memory goes away.
+      for (uint32_t i = 0; !merged && i < WAIT_LIMIT && !mbar_try(g_full, 0); ++i) {
+      }
+    }
+    const float* all = partial + (size_t)slot0 * PART_FLOATS;
+    const float* weights = reinterpret_cast<const float*>(k_s);
+    if (merged) {
+#pragma unroll 2
+      for (int item = threadIdx.x; item < BM * (D / 8); item += THREADS) {
+        const int row = item % BM, c = (item / BM) * 8;
+        if (row >= rows) continue;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int q = 0; q < parts; ++q) {
+          const float4* src = reinterpret_cast<const float4*>(all + (size_t)q * PART_FLOATS) + (size_t)(c / 4) * BM + row;
+          const float4 a = __ldcg(src), b2 = __ldcg(src + BM);
+          const float w = weights[q * BM + row];
+          acc[0] += w * a.x, acc[1] += w * a.y, acc[2] += w * a.z, acc[3] += w * a.w;
+          acc[4] += w * b2.x, acc[5] += w * b2.y, acc[6] += w * b2.z, acc[7] += w * b2.w;
+        }
+        const float inv = weights[parts * BM + row];
+        const size_t token = (size_t)(q_begin + tok0 + row / GROUP);
+        const int head = kvh * GROUP + row % GROUP;
+        uint4 g = make_uint4(0u, 0u, 0u, 0u);
+        if (gate_tma) {
+          g = *reinterpret_cast<const uint4*>(q_s + (c / 64) * HALF_BYTES + row * 128 + ((((c % 64) / 8) ^ (row & 7)) << 4));
+        } else if (gate != nullptr) {
+          const bf16* gp = gate + token * gate_stride + (size_t)head * D + c;
+          g.x = pack_bf16(__bfloat162float(gp[0]), __bfloat162float(gp[1]));
+          g.y = pack_bf16(__bfloat162float(gp[2]), __bfloat162float(gp[3]));
+          g.z = pack_bf16(__bfloat162float(gp[4]), __bfloat162float(gp[5]));
+          g.w = pack_bf16(__bfloat162float(gp[6]), __bfloat162float(gp[7]));
+        }
+        const uint32_t g2[4] = {g.x, g.y, g.z, g.w};
+        uint32_t w4[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float a = acc[2 * e] * inv, b2 = acc[2 * e + 1] * inv;
+          if (gate != nullptr) {
+            const float2 gate2 = sigmoid_pair(g2[e]);
+            a *= gate2.x;
+            b2 *= gate2.y;
+          }
+          w4[e] = pack_bf16(a, b2);
+        }
+        *reinterpret_cast<uint4*>(out + (token * nq + head) * D + c) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+      }
+    }
+  }
   OMNIA_TRACE_BLOCK(4);
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
@@ -646,6 +774,8 @@ extern "C" int omnia_attention_timing(unsigned long long* host, int count) {
 }
 #endif
 
+extern "C" int omnia_attention_tcgen05_part_floats(void) { return PART_FLOATS; }
+
 extern "C" int omnia_attention_tcgen05_info(int* head_dim, int* group, int* tokens_per_block) {
   *head_dim = HEAD_DIM;
   *group = GROUP;
@@ -654,9 +784,13 @@ extern "C" int omnia_attention_tcgen05_info(int* head_dim, int* group, int* toke
 }
 
 // q: [tokens, nq, D]; pages: [num_pages, 2, nkv, page_size, D]; page_size a multiple of 16.
+// work: `blocks` items of 8 ints (see the kernel). partial: float32 workspace, omnia_attention_tcgen05_part_floats()
+// floats for every part of a split block (null when no block is split); tickets: one int per split
+// block, zero before the first launch (the kernel leaves them zero).
 extern "C" int omnia_attention_prefill_tcgen05(const void* q, int tokens, const void* pages, const int* block_table,
                                                const int* cu_seqlens, const int* seq_lens, const int* work,
                                                int blocks, const void* gate, int gate_stride, void* out,
+                                               float* partial, int* tickets,
                                                int max_pages, int num_pages, int nq, int nkv, int page_size,
                                                int window, float scale, int* err, cudaStream_t stream) {
   if (blocks == 0) return 0;
@@ -708,6 +842,6 @@ extern "C" int omnia_attention_prefill_tcgen05(const void* q, int tokens, const 
   }
   launch_pdl(attention_prefill_tcgen05_kernel, blocks, THREADS, smem, stream,
              map_q, map_kv, map_gate, gate_tma, block_table, cu_seqlens, seq_lens, work, (const bf16*)gate, gate_stride, (bf16*)out,
-             max_pages, num_pages, nq, nkv, page_size, window, scale, err);
+             partial, tickets, max_pages, num_pages, nq, nkv, page_size, window, scale, err);
   return OMNIA_LAUNCH_RESULT();
 }

@@ -337,31 +337,98 @@ def _prefill_work(step: StepContext, tokens_per_block: int, device: torch.device
     return _step_list(step, ("prefill_work", tokens_per_block), build, device)
 
 
+PREFILL_MAX_PARTS = 16
+PREFILL_MIN_PART_TILES = 4
+"""The tcgen05 prefill kernel's blocks may be listed in parts (runs of a block's key tiles, merged by
+the part that finishes last): at most this many parts a block, none shorter than this many tiles,
+and only in steps with at most one block per SM (portions of prompts over long contexts), whose
+tiles are then shared out over one and a half places per SM. Measured on B200, 16/8 heads of 128,
+microseconds a layer whole and in parts: 256 tokens over 4,096: 68.5 and 35.0; over 16,384: 244 and 69;
+512 over 8,192: 128 and 57; 64 over 8,192: 126 and 28; 1,024 over 8,192: 132 and 94. A whole prompt
+has blocks enough of its own: cut, its 2,048-token attention takes 47 us a layer against 44 (a part
+pays for its start, for writing its 64 KB and for the merge)."""
+
+
+def prefill_places(sms: int) -> int:
+    """Over how many places the tiles of a step's blocks are shared out when blocks are cut."""
+    return sms + sms // 2
+
+
+def prefill_blocks(step: StepContext, tokens_per_block: int, nkv: int) -> int:
+    """How many blocks of query tokens (each once per key/value head) the step's prompts' portions make."""
+    return sum(-(-n // tokens_per_block) for n in step.q_lens if n > 1) * nkv
+
+
+def prefill_work_table(q_lens, seq_lens, tokens_per_block: int, tile: int, nkv: int, window: int, places: int,
+                       capacity: int | None = None) -> np.ndarray:
+    """The tcgen05 prefill kernel's list, int32 [blocks, 8]: (request, first token, key/value head, first
+    key tile of the part, tiles of the part (-1: all), parts + 256 * part, place of the block's first
+    part in the workspace, number of the block among the split ones), the longest first: blocks are
+    handed to SMs in this order as others finish, so the long ones start early and the short ones
+    fill the gaps (measured: 30 % off a 4,096-token prefill against an order that keeps a head's
+    blocks together).
+
+    In a step of at most two thirds of `places` blocks, a block is cut into parts when it alone would
+    run longer than a place's share of all tiles: into runs of max(that share, PREFILL_MIN_PART_TILES)
+    tiles, so splitting adds at most `places` items. With `capacity` the list has
+    exactly that many items, the unused ones marked with request -1 (a captured step's list keeps
+    its shape from replay to replay while the contexts grow)."""
+    blocks = []
+    for s, n in enumerate(q_lens):
+        if n <= 1:
+            continue
+        t0 = np.arange(0, n, tokens_per_block, dtype=np.int64)
+        tiles = np.full_like(t0, -1)
+        if seq_lens:
+            pos0 = seq_lens[s] - n + t0
+            last = pos0 + np.minimum(tokens_per_block, n - t0) - 1
+            first = np.maximum(0, pos0 - window + 1) if window else np.zeros_like(t0)
+            tiles = last // tile - first // tile + 1
+        # Every block of tokens once per key/value head, heads innermost.
+        blocks.append(np.stack([np.repeat(tiles, nkv), np.full(t0.size * nkv, s), np.repeat(t0, nkv),
+                                np.tile(np.arange(nkv), t0.size)], axis=1))
+    table = np.concatenate(blocks) if blocks else np.zeros((0, 4), dtype=np.int64)
+    tiles = table[:, 0]
+    out = np.zeros((table.shape[0], 9), dtype=np.int64)  # column 0: the sort key
+    out[:, 0], out[:, 1:4], out[:, 5], out[:, 6] = tiles, table[:, 1:4], -1, 1
+    if table.shape[0] and tiles.min() > 0 and table.shape[0] * 3 <= places * 2:
+        share = max(PREFILL_MIN_PART_TILES, -(-int(tiles.sum()) // places))
+        wanted = np.minimum(PREFILL_MAX_PARTS, -(-tiles // share))
+        per = -(-tiles // wanted)
+        parts = -(-tiles // per)
+        if (parts > 1).any():
+            split = parts > 1
+            unit = np.cumsum(split) - 1
+            slot0 = np.concatenate([[0], np.cumsum(np.where(split, parts, 0))[:-1]])
+            index = np.repeat(np.arange(table.shape[0]), parts)
+            part = np.arange(index.size) - np.repeat(np.cumsum(parts) - parts, parts)
+            rows = np.zeros((index.size, 9), dtype=np.int64)
+            rows[:, 1:4] = table[index, 1:4]
+            rows[:, 4] = part * per[index]
+            rows[:, 5] = np.minimum(per[index], tiles[index] - rows[:, 4])
+            rows[:, 6] = parts[index] + 256 * part
+            rows[:, 7], rows[:, 8] = slot0[index], unit[index]
+            rows[:, 0] = rows[:, 5]
+            whole = ~split[index]
+            rows[whole, 4], rows[whole, 5], rows[whole, 6], rows[whole, 0] = 0, -1, 1, tiles[index][whole]
+            out = rows
+    order = np.argsort(-out[:, 0], kind="stable")
+    out = out[order, 1:].astype(np.int32)
+    if capacity is not None:
+        if out.shape[0] > capacity:
+            raise KernelError(f"the prefill kernel's list has {out.shape[0]} items, its place holds {capacity}")
+        padded = np.full((capacity, 8), -1, dtype=np.int32)
+        padded[: out.shape[0]] = out
+        out = padded
+    return out
+
+
 def _prefill_work_flat(step: StepContext, tokens_per_block: int, tile: int, nkv: int, window: int,
                        device: torch.device) -> torch.Tensor:
-    """(request, first token, key/value head) of every block of the tcgen05 prefill kernel, the
-    blocks whose tokens see the most key tiles first: blocks are handed to SMs in this order as
-    others finish, so the long ones start early and the short ones fill the gaps (measured: 30 %
-    off a 4,096-token prefill against an order that keeps a head's blocks together)."""
-    def build(step: StepContext) -> np.ndarray:
-        parts = []
-        for s, n in enumerate(step.q_lens):
-            if n <= 1:
-                continue
-            t0 = np.arange(0, n, tokens_per_block, dtype=np.int64)
-            tiles = np.zeros_like(t0)
-            if step.seq_lens_host:
-                pos0 = step.seq_lens_host[s] - n + t0
-                last = pos0 + np.minimum(tokens_per_block, n - t0) - 1
-                first = np.maximum(0, pos0 - window + 1) if window else np.zeros_like(t0)
-                tiles = last // tile - first // tile + 1
-            # Every block of tokens once per key/value head, heads innermost.
-            parts.append(np.stack([np.repeat(tiles, nkv), np.full(t0.size * nkv, s), np.repeat(t0, nkv),
-                                   np.tile(np.arange(nkv), t0.size)], axis=1))
-        table = np.concatenate(parts) if parts else np.zeros((0, 4), dtype=np.int64)
-        order = np.argsort(-table[:, 0], kind="stable")
-        return table[order, 1:].astype(np.int32)
-
+    """The list of `prefill_work_table` for this step, made once and shared by the layers of equal window."""
+    places = prefill_places(sm_count(device))
+    capacity = prefill_blocks(step, tokens_per_block, nkv) + places if (step.workspace or {}).get("private") else None
+    build = lambda st: prefill_work_table(st.q_lens, st.seq_lens_host, tokens_per_block, tile, nkv, window, places, capacity)
     return _step_list(step, ("prefill_work_flat", tokens_per_block, tile, nkv, window), build, device)
 
 
@@ -472,13 +539,22 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
         if step.decode_only or all(n == 1 for n in step.q_lens):
             return out
     if tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):
-        work = _prefill_work_flat(step, 128 // (nq // nkv), 64, nkv, kv.window or 0, q.device)
+        per_block = 128 // (nq // nkv)
+        work = _prefill_work_flat(step, per_block, 64, nkv, kv.window or 0, q.device)
+        # Room for the parts of blocks that are cut (at most one more item per block the device runs at
+        # a time) and a ticket per block; the sizes do not depend on the contexts' lengths.
+        part_floats = _function("attention_tcgen05", "omnia_attention_tcgen05_part_floats", [], defines)()
+        base = prefill_blocks(step, per_block, nkv)
+        partial, tickets = _step_buffers(step, q.device, {
+            "prefill_parts": ((base + prefill_places(sm_count(q.device))) * part_floats, torch.float32, False),
+            "prefill_tickets": (base, torch.int32, True)})
         fn = _function("attention_tcgen05", "omnia_attention_prefill_tcgen05",
                        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p], defines)
+                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+                       defines)
         _check(fn(_ptr(q), tokens, _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.seq_lens),
-                  _ptr(work), work.shape[0], gate_ptr, gate_stride, _ptr(out), max_pages, num_pages, nq, nkv,
-                  kv.page_size, kv.window or 0, scale, err, _stream()), "attention_prefill_tcgen05")
+                  _ptr(work), work.shape[0], gate_ptr, gate_stride, _ptr(out), _ptr(partial), _ptr(tickets), max_pages,
+                  num_pages, nq, nkv, kv.page_size, kv.window or 0, scale, err, _stream()), "attention_prefill_tcgen05")
         return out
     tokens_per_block = 64 // (nq // nkv)
     work = _prefill_work(step, tokens_per_block, q.device)

@@ -74,14 +74,17 @@ def test_a_pending_residual_step_is_settled_once_and_says_when_it_was_consumed(c
         ops.settle(consumed)
 
 
-def test_prefill_blocks_are_listed_longest_first_heads_innermost(monkeypatch):
-    """The tcgen05 prefill kernel's block list: every block of tokens of every multi-token request
-    once per key/value head, ordered by the key tiles it sees (most first), ties in the order
-    request, first token, head; requests that bring one token are left to the decode kernel."""
+def test_prefill_blocks_are_listed_longest_first_and_cut_into_parts(monkeypatch):
+    """The tcgen05 prefill kernel's list: every block of tokens of every multi-token request once per
+    key/value head (requests that bring one token are left to the decode kernel); a block that alone
+    would run longer than the device's share of all key tiles is listed as parts whose runs of tiles
+    cover the block's tiles once and in order; the items with the most tiles come first; parts of one
+    block share a place in the workspace and a ticket that no other block has."""
     from types import SimpleNamespace
+    import numpy as np
 
-    def expected(q_lens, seq_lens, tokens_per_block, tile, nkv, window):
-        items = []
+    def blocks_of(q_lens, seq_lens, tokens_per_block, tile, nkv, window):
+        items = {}
         for s, n in enumerate(q_lens):
             if n <= 1:
                 continue
@@ -89,15 +92,60 @@ def test_prefill_blocks_are_listed_longest_first_heads_innermost(monkeypatch):
                 pos0 = seq_lens[s] - n + t0
                 last = pos0 + min(tokens_per_block, n - t0) - 1
                 first = max(0, pos0 - window + 1) if window else 0
-                items += [(last // tile - first // tile + 1, s, t0, h) for h in range(nkv)]
-        items.sort(key=lambda item: -item[0])
-        return [list(item[1:]) for item in items]
+                for h in range(nkv):
+                    items[(s, t0, h)] = last // tile - first // tile + 1
+        return items
+
+    slots = 222  # one and a half places per SM of a 148-SM device
+    cases = [([2048], [2048], 64, 64, 8, 0), ([7, 1, 300, 40], [7, 90, 1000, 45], 64, 64, 3, 0),
+             ([500, 33], [900, 33], 32, 64, 2, 130), ([1, 1], [5, 9], 64, 64, 2, 0),
+             ([256] + [1] * 8, [8000] + [4096] * 8, 64, 64, 8, 0), ([512], [40000], 64, 64, 8, 0),
+             ([64], [40000], 64, 64, 8, 0)]
+    for q_lens, seq_lens, per_block, tile, nkv, window in cases:
+        table = ops.prefill_work_table(q_lens, seq_lens, per_block, tile, nkv, window, slots)
+        want = blocks_of(q_lens, seq_lens, per_block, tile, nkv, window)
+        assert table.shape == (table.shape[0], 8) and table.dtype == np.int32
+        assert table.shape[0] <= len(want) + slots
+        seen, places, tickets, lengths = {}, {}, {}, []
+        for s, t0, h, lo, count, packed, slot0, unit in table.tolist():
+            parts, part = packed & 255, packed >> 8
+            tiles = want[(s, t0, h)]
+            if parts == 1:
+                assert (lo, count, part) == (0, -1, 0)
+                count = tiles
+            else:
+                assert 1 < parts <= ops.PREFILL_MAX_PARTS and 0 <= part < parts and count >= 1
+                places.setdefault((slot0, parts), set()).add((s, t0, h))
+                tickets.setdefault(unit, set()).add((s, t0, h))
+            seen.setdefault((s, t0, h), []).append((part, lo, count, parts))
+            lengths.append(count)
+        assert lengths == sorted(lengths, reverse=True)
+        assert set(seen) == set(want)
+        for key, runs in seen.items():
+            runs.sort()
+            assert [r[0] for r in runs] == list(range(runs[0][3]))  # every part once
+            assert runs[0][1] == 0 and all(a[1] + a[2] == b[1] for a, b in zip(runs, runs[1:]))  # in order, no gap
+            assert runs[-1][1] + runs[-1][2] == want[key]
+        assert all(len(v) == 1 for v in places.values()) and all(len(v) == 1 for v in tickets.values())
+        spans = sorted((slot0, slot0 + parts) for slot0, parts in places)
+        assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))  # no two blocks share a place
+        assert sorted(tickets) == list(range(len(tickets)))
+        # A long block over few blocks is cut; a step with many blocks of its own is cut less or not at all.
+        if q_lens == [512]:  # 64 blocks of 618 to 625 tiles on 222 places: four parts each
+            assert {r[3] for runs in seen.values() for r in runs} == {4}
+        if q_lens == [64]:
+            assert {r[3] for runs in seen.values() for r in runs} == {ops.PREFILL_MAX_PARTS}
+        if q_lens == [2048]:  # a whole prompt has blocks enough of its own: none is cut
+            assert {r[3] for runs in seen.values() for r in runs} == {1}
+        if q_lens == [1, 1]:
+            assert table.shape[0] == 0
+        padded = ops.prefill_work_table(q_lens, seq_lens, per_block, tile, nkv, window, slots, capacity=len(want) + slots)
+        assert padded.shape[0] == len(want) + slots and (padded[: table.shape[0]] == table).all()
+        assert (padded[table.shape[0]:, 0] == -1).all()
 
     monkeypatch.setattr(ops, "_ints_to_device", lambda values, device: values)
-    for q_lens, seq_lens, per_block, tile, nkv, window in [([2048], [2048], 64, 64, 8, 0),
-                                                            ([7, 1, 300, 40], [7, 90, 1000, 45], 64, 64, 3, 0),
-                                                            ([500, 33], [900, 33], 32, 64, 2, 130), ([1, 1], [5, 9], 64, 64, 2, 0)]:
-        step = SimpleNamespace(workspace=None, q_lens=q_lens, seq_lens_host=seq_lens)
-        work = ops._prefill_work_flat(step, per_block, tile, nkv, window, None)
-        assert work.tolist() == expected(q_lens, seq_lens, per_block, tile, nkv, window)
-        assert ops._prefill_work_flat(step, per_block, tile, nkv, window, None) is work  # built once per step
+    monkeypatch.setattr(ops, "sm_count", lambda device=None: 148)
+    step = SimpleNamespace(workspace=None, q_lens=[300, 1], seq_lens_host=[5000, 77])
+    work = ops._prefill_work_flat(step, 64, 64, 8, 0, None)
+    assert (work == ops.prefill_work_table([300, 1], [5000, 77], 64, 64, 8, 0, 222)).all()
+    assert ops._prefill_work_flat(step, 64, 64, 8, 0, None) is work  # built once per step

@@ -176,6 +176,50 @@ def test_prefill_attention_at_a_window_s_edge_with_nan_elsewhere(ops, dtype, nq,
     ops.raise_on_error(q.device)
 
 
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(4, 2, 128, 16, None), (8, 2, 64, 16, None), (6, 3, 128, 32, 1500),
+                                                   (2, 1, 128, 16, 700)])
+def test_prefill_attention_in_parts(ops, nq, nkv, d, page, window):
+    """Portions of prompts over long contexts: few blocks that each see dozens of key tiles, which the
+    tcgen05 kernel lists as parts and merges (the list says so). Everything a request may not read
+    holds NaN; a far key that matches one query stands out against hundreds of others; a second
+    launch finds the tickets as the first one left them."""
+    dtype = torch.bfloat16
+    q_lens, seq_lens = [70, 130, 1, 33], [2900, 1700, 300, 1203]
+    step = step_of(q_lens, seq_lens)
+    work = ops.prefill_work_table(q_lens, seq_lens, 128 // (nq // nkv), 64, nkv, window or 0, ops.prefill_places(ops.sm_count()))
+    assert ((work[:, 5] & 255) > 1).any()
+    pages, table = make_kv(seq_lens, nkv, d, page, dtype, 8 + sum(-(-n // page) for n in seq_lens), seed=41)
+    pages.fill_(float("nan"))
+    for s, (q, n) in enumerate(zip(q_lens, seq_lens)):
+        dead_below = n - q - window + 1 if window else 0
+        for first in range(0, n, page):
+            if first + page <= dead_below:
+                table[s, first // page] = -1
+                continue
+            count = min(page, n - first)
+            pages[int(table[s, first // page]), :, :, :count, :] = rand(2, nkv, count, d, dtype=dtype, scale=0.3, seed=100 * s + first)
+    q = rand(step.num_tokens, nq, d, dtype=dtype, scale=0.3, seed=51)
+    # Request 0's last token looks for the key at position 2,000 (visible whatever the window is here).
+    far = 2000 if not window or window > 900 else 2500
+    slot = int(table[0, far // page])
+    pages[slot, 0, :, far % page, :] = 0.0
+    pages[slot, 0, :, far % page, 0] = 8.0
+    q[q_lens[0] - 1] = 0.0
+    q[q_lens[0] - 1, :, 0] = 50.0
+    gate = rand(step.num_tokens, nq * d, dtype=dtype, seed=52)
+    view = KVView(pages, table, torch.zeros(step.num_tokens, dtype=torch.int64, device="cuda"), page, window)
+    scale = 1.2 * d ** -0.5
+    want = kernel_refs.paged_attention(q, view, step, scale, gate=gate)
+    for _ in range(2):
+        got = ops.paged_attention(q, view, step, scale, gate=gate)
+        assert not torch.isnan(got).any()
+        close(got, want, dtype)
+    plain = ops.paged_attention(q, view, step, scale)
+    value = pages[slot, 1, :, far % page, :].float()  # [nkv, d]: the far key's value, what the last token must return
+    close(plain[q_lens[0] - 1].view(nq, d), value.repeat_interleave(nq // nkv, dim=0), dtype, scale=3)
+    ops.raise_on_error(q.device)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,d,page,window", [(4, 2, 16, 4, None), (8, 1, 24, 8, 16), (6, 3, 128, 16, None),
                                                    (6, 3, 128, 16, 200), (5, 5, 40, 3, 130), (16, 8, 64, 16, None),
