@@ -215,12 +215,15 @@ def test_command_line_takes_text_and_the_checkpoint_s_defaults(tmp_path):
     assert f"prompt 2 tokens, completion {cut} tokens" in done.stderr
 
 
-@pytest.mark.parametrize("name,dtype,page", [("B", "float32", 8), ("C", "bfloat16", 16), ("A", "bfloat16", 4)])
-def test_captured_mixed_steps_equal_eager_ones(name, dtype, page):
+@pytest.mark.parametrize("name,dtype,page,portion,steps", [("B", "float32", 8, 48, 7), ("C", "bfloat16", 16, 48, 7),
+                                                           ("A", "bfloat16", 4, 48, 7), ("C", "bfloat16", 16, 96, 14)])
+def test_captured_mixed_steps_equal_eager_ones(name, dtype, page, portion, steps):
     """Decoding requests beside a long prompt that is read in equal portions: the step's shape comes
     again and again, so from its second coming it is replayed from a captured graph. The logits are
     those of the same steps launched kernel by kernel, the cache is the same afterwards (what is
-    decoded later agrees too), and the reader's logits match the plain implementation."""
+    decoded later agrees too), and the reader's logits match the plain implementation. In the last
+    case the prompt grows to 1,344 tokens: the tcgen05 attention kernel's blocks are then listed in
+    parts, more of them from replay to replay, in a list whose place was made before the capture."""
     from floors import Oracle
     from mlx_omnia_b200.engine.engine import Engine, EngineArgs
     from mlx_omnia_b200.engine.step import StepEntry
@@ -228,28 +231,29 @@ def test_captured_mixed_steps_equal_eager_ones(name, dtype, page):
     raw, weights = tiny_configs.config(name), tiny_configs.tensors(name)
     vocab = raw["text_config"]["vocab_size"]
     decoders = [tiny_configs.prompt(n, vocab, 400 + n) for n in (37, 90, 11)]
-    reader = tiny_configs.prompt(7 * 48, vocab, 499)
+    reader = tiny_configs.prompt(steps * portion, vocab, 499)
     results = []
     for graphs in (False, True):
-        engine = Engine.from_tensors(raw, weights, EngineArgs(dtype=dtype, page_size=page, cache_tokens=1024,
+        engine = Engine.from_tensors(raw, weights, EngineArgs(dtype=dtype, page_size=page, cache_tokens=1024 + steps * portion,
                                                               max_requests=4, cuda_graphs=graphs))
         requests = [engine.cache.open(f"d{i}") for i in range(3)]
         long_one = engine.cache.open("reader")
         engine.runner.run([StepEntry(r, p[:-8], []) for r, p in zip(requests, decoders)])
         rows = []
-        for k in range(7):  # seven mixed steps of one shape: three decoded tokens beside 48 prompt tokens
-            entries = [StepEntry(r, [p[len(p) - 8 + k]], [0]) for r, p in zip(requests, decoders)]
-            entries.append(StepEntry(long_one, reader[48 * k: 48 * (k + 1)], [0, 47]))
+        for k in range(steps):  # mixed steps of one shape: three decoded tokens beside a portion of the prompt
+            entries = [StepEntry(r, [p[len(p) - 8 + k % 7]], [0]) for r, p in zip(requests, decoders)] if k < 7 else \
+                [StepEntry(r, [1 + k], [0]) for r in requests]
+            entries.append(StepEntry(long_one, reader[portion * k: portion * (k + 1)], [0, portion - 1]))
             rows.append(engine.runner.run(entries))
         rows.append(engine.runner.run([StepEntry(r, [p[-1]], [0]) for r, p in zip(requests, decoders)]))
         if graphs:
-            assert engine.runner.mixed_graphs.replays == 5 and len(engine.runner.mixed_graphs.captured) == 1
+            assert engine.runner.mixed_graphs.replays == steps - 2 and len(engine.runner.mixed_graphs.captured) == 1
         ops_check(engine)
         results.append(torch.cat(rows))
     assert torch.equal(results[0], results[1])
     oracle = Oracle(raw, weights, {"reader": reader})
-    got = torch.stack([results[1][5 * k + 3 + j] for k in range(7) for j in range(2)])
-    want_rows = [48 * k + w for k in range(7) for w in (0, 47)]
+    got = torch.stack([results[1][5 * k + 3 + j] for k in range(steps) for j in range(2)])
+    want_rows = [portion * k + w for k in range(steps) for w in (0, portion - 1)]
     assert oracle.diff("reader", got, want_rows) < oracle.tolerance[dtype]
 
 
