@@ -338,15 +338,17 @@ def _prefill_work(step: StepContext, tokens_per_block: int, device: torch.device
 
 
 PREFILL_MAX_PARTS = 16
-PREFILL_MIN_PART_TILES = 4
+PREFILL_MIN_PART_TILES = 12
 """The tcgen05 prefill kernel's blocks may be listed in parts (runs of a block's key tiles, merged by
 the part that finishes last): at most this many parts a block, none shorter than this many tiles,
 and only in steps with at most one block per SM (portions of prompts over long contexts), whose
-tiles are then shared out over one and a half places per SM. Measured on B200, 16/8 heads of 128,
-microseconds a layer whole and in parts: 256 tokens over 4,096: 68.5 and 35.0; over 16,384: 244 and 69;
-512 over 8,192: 128 and 57; 64 over 8,192: 126 and 28; 1,024 over 8,192: 132 and 94. A whole prompt
-has blocks enough of its own: cut, its 2,048-token attention takes 47 us a layer against 44 (a part
-pays for its start, for writing its 64 KB and for the merge)."""
+tiles are then shared out over one and a half places per SM. Measured on B200 with the headline
+model (`bench.py --only portions`, `--only mixed`), whole blocks against parts: a prompt of 8,192
+tokens read in portions of 512: 68 and 53 ms, in portions of 256: 119 and 84; 32,768 tokens in
+portions of 512: 586 and 328; a step of 8 decoding requests beside a 512-token portion: 6.1 and 4.9
+ms. Parts of at least 4, 8, 12, 16, 24 tiles: 4.00, 3.92, 3.83, 4.23, 4.01 ms for such a step with a
+256-token portion. A whole prompt has blocks enough of its own: cut, its 2,048-token attention
+takes 47 us a layer against 44 (a part pays for its start, for writing its 64 KB and for the merge)."""
 
 
 def prefill_places(sms: int) -> int:
