@@ -151,6 +151,7 @@ def run(args) -> dict:
     cache_tokens = max(batches) * (args.context + 16) + max(PREFILL_TOKENS, args.prefill_tokens,
                                                               32768 + 16 if args.only == "portions" else 8192 + 16,
                                                               (max(args.steps, 8) + max(args.warmup, 3) + 2) * args.portion)
+    cache_tokens = max(cache_tokens, args.pool_tokens)
     engine = Engine.from_random(raw, SEED, EngineArgs(dtype="bfloat16", page_size=16, cache_tokens=cache_tokens,
                                                       max_requests=max(batches) + 1))
     g = torch.Generator().manual_seed(SEED)
@@ -555,6 +556,7 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=0, help="tokens each request holds at the last timed step "
                                                                "(default: the configuration's own)")
     parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
+    parser.add_argument("--pool-tokens", type=int, default=0, help="at least this many tokens of cache pool (default: what the run needs)")
     parser.add_argument("--portion", type=int, default=256,
                         help="--only mixed: tokens of a prompt that run beside --batch decoding requests")
     args = parser.parse_args()

@@ -154,8 +154,11 @@ class DecodeGraphs:
         return logits.clone() if copy else logits
 
 
-MIXED_MAX_TOKENS = 1024
-"""Steps of more tokens are bound by the GPU, not by launching them, and stay uncaptured."""
+MIXED_MAX_TOKENS = 4096
+"""Steps of more tokens stay uncaptured (a captured step keeps buffers of its own for as long as its
+graph lives). Steps of thousands of tokens are bound by the GPU, not by launching them, yet a replayed
+graph still runs them faster: a kernel that follows a library product cannot start its preamble early,
+and in a graph the gap between the two is shorter (a 2,048-token step: 7.71 -> 7.37 ms)."""
 MIXED_MAX_GRAPHS = 8
 
 
