@@ -19,14 +19,18 @@ decoded tokens, launches some 230 kernels one by one from Python and is bound by
 (16 us a launch) long before the GPU. In continuous batching such steps repeat in shape:
 the same requests decode while a long prompt is read in portions of the token budget. So
 a step whose shape (tokens per request, wanted rows per request, the bucket of the
-longest decoding request) comes a second time is captured with exactly that shape, and
-replayed whenever it comes again. Its block tables are as wide as the pool allows, so the
-width never changes; the small lists that the attention kernels read (which block of
-query tokens runs where) are given a place on the device during the capture and filled by
-the host before every replay (`ops.fill_step_lists`). The second step of a shape runs
-uncaptured on the buffers the graph will use (so every scratch buffer and list exists
-before the capture), and the capture that follows runs nothing, so a mixer's state is
-never stepped twice; from its third coming on the shape is replayed.
+longest decoding request, the width of the block tables: the next power of two above the
+longest request's pages, so a prompt doubles before it leaves its graph) comes for the
+third time is captured with exactly that shape, and replayed whenever it comes again. The
+small lists that the attention kernels read (which block of query tokens runs where) are
+given a place on the device before the capture and filled by the host before every replay
+(`ops.fill_step_lists`). The capturing step runs uncaptured on the buffers the graph will
+use (so every scratch buffer and list exists before the capture), and the capture that
+follows runs nothing, so a mixer's state is never stepped twice; from its fourth coming on
+the shape is replayed. (A capture costs about three steps' time. In a stream of 64 requests
+of many lengths most shapes come once or twice: capturing at the second coming, with tables
+as wide as the pool, made such a stream twice as slow as launching every step kernel by
+kernel.)
 
 The kernels and the model code are the same as in an uncaptured step; only the way
 they are launched differs, so logits agree bit for bit with an eager step of the same
@@ -159,7 +163,14 @@ MIXED_MAX_TOKENS = 4096
 graph lives). Steps of thousands of tokens are bound by the GPU, not by launching them, yet a replayed
 graph still runs them faster: a kernel that follows a library product cannot start its preamble early,
 and in a graph the gap between the two is shorter (a 2,048-token step: 7.71 -> 7.37 ms)."""
+MIXED_MAX_REQUESTS = 16
+"""Steps of more requests stay uncaptured: they are bound by the GPU (the decoding requests' attention
+alone outlasts the launching of the step), and in a stream of many requests their shapes change
+with every request that joins or leaves."""
 MIXED_MAX_GRAPHS = 8
+MIXED_CAPTURE_AT = 3
+"""A shape is captured at this coming: a capture costs about three steps' time, and in a stream of
+requests of many lengths most shapes come once or twice."""
 
 
 class MixedGraphs:
@@ -171,8 +182,8 @@ class MixedGraphs:
         self.captured: dict[tuple, _Captured] = {}  # in order of last use, oldest first
         self.replays = 0
         cache = runner.cache
-        # Block tables as wide as the longest request the pools can hold: the width is then no part of a shape.
-        self.widths = [cache.pages_for(g, cache.capacity_tokens()) for g in range(len(cache.groups))]
+        # No block table is wider than the longest request the pools can hold.
+        self.widest = [cache.pages_for(g, cache.capacity_tokens()) for g in range(len(cache.groups))]
 
     @staticmethod
     def supported(model) -> bool:
@@ -180,11 +191,17 @@ class MixedGraphs:
 
     def key(self, entries) -> tuple | None:
         q_lens = tuple(len(e.tokens) for e in entries)
-        if sum(q_lens) > MIXED_MAX_TOKENS or all(q == 1 for q in q_lens):
+        if sum(q_lens) > MIXED_MAX_TOKENS or len(q_lens) > MIXED_MAX_REQUESTS or all(q == 1 for q in q_lens):
             return None
         page = self.runner.cache.page_size
         longest = max((e.request.tokens + 1 for e, q in zip(entries, q_lens) if q == 1), default=0)
-        return q_lens, tuple(len(e.want) for e in entries), ops.width_bucket(-(-longest // page)) if longest else 0
+        # Block tables are as wide as the next power of two above the longest request of the step: a
+        # prompt that is read in portions doubles before it leaves its graph, and a step's tables
+        # are at most twice what its requests need (tables as wide as the pool cost a step of 64
+        # requests 2.4 MB of metadata to fill and to copy).
+        pages = max(-(-(e.request.tokens + q) // page) for e, q in zip(entries, q_lens))
+        return (q_lens, tuple(len(e.want) for e in entries), ops.width_bucket(-(-longest // page)) if longest else 0,
+                max(64, 1 << (pages - 1).bit_length()))
 
     def wants(self, entries) -> tuple | None:
         """The shape's key if this step should run from a graph: the shape has come before."""
@@ -196,7 +213,7 @@ class MixedGraphs:
         self.seen[key] = self.seen.get(key, 0) + 1
         if len(self.seen) > 4096:
             self.seen.clear()
-        return key if self.seen[key] >= 2 else None
+        return key if self.seen[key] >= MIXED_CAPTURE_AT else None
 
     def run(self, key: tuple, entries, copy: bool = True) -> torch.Tensor:
         runner = self.runner
@@ -214,7 +231,7 @@ class MixedGraphs:
             while len(self.captured) >= MIXED_MAX_GRAPHS:
                 torch.cuda.synchronize(runner.runtime.device)
                 del self.captured[next(iter(self.captured))]
-            layout = StepLayout(at, len(entries), len(rows), self.widths)
+            layout = StepLayout(at, len(entries), len(rows), [min(key[3], widest) for widest in self.widest])
             host_tensor = torch.zeros(layout.words, dtype=torch.int32).pin_memory()
             dev = torch.zeros(layout.words, dtype=torch.int32, device=runner.runtime.device)
         else:
