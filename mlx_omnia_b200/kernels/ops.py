@@ -91,6 +91,11 @@ def raise_on_error(device: torch.device) -> None:
     bits = int(word.item())
     if bits:
         word.zero_()
+        # A kernel that gave up may have left its tickets half drawn: the buffers that their users
+        # are to leave zero are zero again for the next launch.
+        for key in _zeroed:
+            if key[0] == (device.index or 0):
+                _scratch[key].zero_()
         raise KernelError("kernel index check failed: " + "; ".join(m for b, m in ERROR_BITS.items() if bits & b))
 
 
@@ -174,6 +179,7 @@ DECODE_CHUNK = 128
 """Keys per split of the decode attention kernel (chunks are aligned to absolute positions)."""
 
 _scratch: dict[tuple[int, str], torch.Tensor] = {}
+_zeroed: set[tuple[int, str]] = set()  # the scratch buffers that are zero between launches
 
 
 def scratch(device: torch.device, name: str, numel: int, dtype: torch.dtype = torch.float32,
@@ -185,6 +191,8 @@ def scratch(device: torch.device, name: str, numel: int, dtype: torch.dtype = to
     if held is None or held.numel() < numel or held.dtype != dtype:
         make = torch.zeros if zeroed else torch.empty
         held = _scratch[key] = make(max(numel, 1), dtype=dtype, device=device)
+        if zeroed:
+            _zeroed.add(key)
     return held
 
 
