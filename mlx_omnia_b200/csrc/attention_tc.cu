@@ -434,7 +434,7 @@ struct FusedQK {
   long long num_slots;
 };
 
-template <int WARPS>
+template <int WARPS, int RING>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages,
                         const int* __restrict__ block_table, const int* __restrict__ cu_seqlens,
@@ -451,7 +451,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
   const bool early = fused.proj != nullptr;
   OMNIA_TRACE_BLOCK(2);
   if (!early) pdl_wait();
-  constexpr int STAGES = WARPS == 1 ? DECODE_STAGES : 1;  // stages of each warp's own ring
+  constexpr int STAGES = RING;  // stages of each warp's own ring
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   bf16* kv = reinterpret_cast<bf16*>(smem_raw) + warp * STAGES * 2 * DECODE_BN * ROW;  // STAGES x (K [32][ROW], V [32][ROW])
@@ -502,8 +502,11 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
       cp_async16(vt + key * ROW + c * 8, kp ? kp + v_offset + c * 8 : pages, kp != nullptr);
     }
   };
-  // In flight before the loop: all stages but one of a ring, the one stage of a warp without a ring.
-  constexpr int AHEAD = STAGES > 1 ? STAGES - 1 : 1;
+  // In flight before the loop: all stages but one of a lone warp's ring (the last is asked for at the
+  // top of the loop), the one stage of a warp without a ring, every stage of a ring beside other
+  // warps' (FILLED: a stage is then asked for again once its tile has been worked on).
+  constexpr bool FILLED = WARPS > 1 && STAGES > 1;
+  constexpr int AHEAD = FILLED ? STAGES : STAGES > 1 ? STAGES - 1 : 1;
 #pragma unroll
   for (int s = 0; s < AHEAD; ++s) {
     if (s < tiles) load_tile(s, s);
@@ -637,7 +640,9 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
   const float sl2 = scale * LOG2E;
 
   for (int tile = 0; tile < tiles; ++tile) {
-    if (STAGES > 1) {
+    if (FILLED) {
+      cp_async_wait<STAGES - 1>();
+    } else if (STAGES > 1) {
       const int ahead = tile + STAGES - 1;
       if (ahead < tiles) load_tile(ahead, ahead % STAGES);
       cp_async_commit();
@@ -661,6 +666,9 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     __syncwarp();
     if (STAGES == 1) {  // the one stage is free again
       if (tile + 1 < tiles) load_tile(tile + 1, 0);
+      cp_async_commit();
+    } else if (FILLED) {
+      if (tile + STAGES < tiles) load_tile(tile + STAGES, tile % STAGES);
       cp_async_commit();
     }
   }
@@ -816,17 +824,24 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
     return (int)cudaErrorInvalidValue;
   const FusedQK fused{(const bf16*)proj, proj_stride, q_col, k_col, v_col, eps, inv_freq, slot_mapping,
                       (bf16*)const_cast<void*>(pages), (long long)num_pages * page_size};
-  // One warp: a two-stage ring. Four warps: one stage each (a warp has few tiles), and the merge area fits in it.
-  size_t smem = (size_t)((warps == 1 ? DECODE_STAGES : 4) * 2 * DECODE_BN) * ROW * sizeof(bf16);
+  // One warp: a two-stage ring. Four warps: one stage each (a warp has few tiles), and the merge area
+  // fits in it; where the grid is at most a block per SM, two stages each: a warp's tiles are then
+  // all on their way before it needs the first (a single request of 4,096 tokens: each warp has two).
   const int sms = omnia_sm_count();
+  const bool deep = warps == 4 && (long long)max_chunks * nkv * requests <= sms &&
+                    (size_t)(8 * 2 * DECODE_BN) * ROW * sizeof(bf16) <= BLOCK_MOST - BLOCK_OVERHEAD;  // (head size 256: too large)
+  size_t smem = (size_t)((warps == 1 ? DECODE_STAGES : deep ? 8 : 4) * 2 * DECODE_BN) * ROW * sizeof(bf16);
   static bool configured[64] = {};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
   if (!configured[device]) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<1, DECODE_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)(BLOCK_MOST - BLOCK_OVERHEAD));
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attention_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      e = cudaFuncSetAttribute(attention_decode_kernel<4, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)(BLOCK_MOST - BLOCK_OVERHEAD));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_decode_kernel<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                (int)(BLOCK_MOST - BLOCK_OVERHEAD));
     if (e != cudaSuccess) return (int)e;
     configured[device] = true;
@@ -842,12 +857,17 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
     if (room > smem + BLOCK_OVERHEAD) smem = (room > BLOCK_MOST ? BLOCK_MOST : room) - BLOCK_OVERHEAD;
   }
   if (warps == 1)
-    launch_pdl(attention_decode_kernel<1>, dim3(max_chunks, nkv, requests), 32, smem, stream,
+    launch_pdl(attention_decode_kernel<1, DECODE_STAGES>, dim3(max_chunks, nkv, requests), 32, smem, stream,
+        (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
+        tickets, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
+        num_pages, nq, nkv, page_size, window, scale, fused, err);
+  else if (deep)
+    launch_pdl(attention_decode_kernel<4, 2>, dim3(max_chunks, nkv, requests), 128, smem, stream,
         (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
         tickets, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
         num_pages, nq, nkv, page_size, window, scale, fused, err);
   else
-    launch_pdl(attention_decode_kernel<4>, dim3(max_chunks, nkv, requests), 128, smem, stream,
+    launch_pdl(attention_decode_kernel<4, 1>, dim3(max_chunks, nkv, requests), 128, smem, stream,
         (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
         tickets, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
         num_pages, nq, nkv, page_size, window, scale, fused, err);
@@ -922,7 +942,7 @@ extern "C" int omnia_attention_decode_tc_static(const void* q, const void* pages
       snprintf(static_error, sizeof static_error, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
       return (int)e;
     }
-    e = cudaFuncSetAttribute(attention_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(attention_decode_kernel<1, DECODE_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)(BLOCK_MOST - BLOCK_OVERHEAD));
     if (e != cudaSuccess) {
       snprintf(static_error, sizeof static_error, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
@@ -941,7 +961,7 @@ extern "C" int omnia_attention_decode_tc_static(const void* q, const void* pages
     return (int)e;
   }
   const size_t smem = (size_t)(DECODE_STAGES * 2 * DECODE_BN) * ROW * sizeof(bf16);
-  launch_pdl(attention_decode_kernel<1>, dim3(max_chunks, nkv, requests), 32, smem, stream,
+  launch_pdl(attention_decode_kernel<1, DECODE_STAGES>, dim3(max_chunks, nkv, requests), 32, smem, stream,
       (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
       ticket_area, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
       num_pages, nq, nkv, page_size, window, scale, FusedQK{}, err);
