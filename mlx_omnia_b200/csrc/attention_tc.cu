@@ -342,10 +342,15 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pa
 // everything a round needs is asked for before anything is used: the gates at once, then per
 // round of eight chunks the chunks' (max, sum) pairs, one chunk per lane, and the H x 8 partial
 // rows, every lane its own dims. Eight chunks or fewer are one round trip for all H heads.
+// The merge of a head's (H heads') chunks by one warp. The chunks' unnormalised accumulators lie one
+// after the other in part_o, so a batch of them is brought into shared memory (`stage`, room for
+// `stage_floats` floats: the block's ring, idle by now) with one round of 16-byte asynchronous
+// copies, all in flight together: one trip to L2 for up to 32 chunks, where reading them eight at
+// a time into registers took one trip per eight. Lane u holds chunk u's maximum and sum.
 template <int H>
 __device__ __forceinline__ void combine_heads(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               size_t base, int max_chunks, int c0, int c1, const bf16* gate_row,
-                                              bf16* out_row) {
+                                              bf16* out_row, float* stage, int stage_floats) {
   const int lane = threadIdx.x & 31;
   constexpr int PER_LANE = (D + 31) / 32;
   float gate_v[H][PER_LANE];
@@ -363,24 +368,21 @@ __device__ __forceinline__ void combine_heads(const float* __restrict__ part_o, 
 #pragma unroll
     for (int k = 0; k < PER_LANE; ++k) acc[h][k] = 0.f;
   }
-  for (int r0 = c0; r0 <= c1; r0 += 8) {
-    const int count = min(8, c1 - r0 + 1);
-    float mc[H], lc[H], vals[H][8][PER_LANE];
+  const int batch = min(32, stage_floats / (H * D));  // chunks a round (at least one: a stage holds far more than H rows)
+  for (int r0 = c0; r0 <= c1; r0 += batch) {
+    const int count = min(batch, c1 - r0 + 1);
+    float mc[H], lc[H];
 #pragma unroll
     for (int h = 0; h < H; ++h) {
       const size_t slot = base + (size_t)h * max_chunks + r0;
+      const float* src = part_o + slot * D;  // `count` chunks of D floats, one after the other
+      for (int i = lane; i < count * (D / 4); i += 32) cp_async16(stage + (size_t)h * batch * D + 4 * i, src + 4 * i, true);
       mc[h] = lane < count ? __ldcg(part_ml + (slot + lane) * 2) : -INFINITY;
       lc[h] = lane < count ? __ldcg(part_ml + (slot + lane) * 2 + 1) : 0.f;
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const float* src = part_o + (slot + min(u, count - 1)) * D;
-#pragma unroll
-        for (int k = 0; k < PER_LANE; ++k) {
-          const int dim = lane + 32 * k;
-          vals[h][u][k] = dim < D ? __ldcg(src + dim) : 0.f;
-        }
-      }
     }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncwarp();
 #pragma unroll
     for (int h = 0; h < H; ++h) {
       const float mx_new = fmaxf(mx[h], warp_max(mc[h]));
@@ -390,13 +392,17 @@ __device__ __forceinline__ void combine_heads(const float* __restrict__ part_o, 
       mx[h] = mx_new;
 #pragma unroll
       for (int k = 0; k < PER_LANE; ++k) acc[h][k] *= rescale;
+      const float* rows = stage + (size_t)h * batch * D;
+      for (int u = 0; u < count; ++u) {
+        const float wj = __shfl_sync(0xffffffffu, w, u);
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const float wj = __shfl_sync(0xffffffffu, w, u);  // zero beyond `count`
-#pragma unroll
-        for (int k = 0; k < PER_LANE; ++k) acc[h][k] += vals[h][u][k] * wj;
+        for (int k = 0; k < PER_LANE; ++k) {
+          const int dim = lane + 32 * k;
+          if (dim < D) acc[h][k] += rows[u * D + dim] * wj;
+        }
       }
     }
+    __syncwarp();  // the stage is read before the next round overwrites it
   }
 #pragma unroll
   for (int h = 0; h < H; ++h) {
@@ -752,16 +758,20 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
   // Two heads at a time (their loads travel together; one at a time where a head's rows would not
   // fit in registers twice), then the odd one.
   constexpr int TOGETHER = D <= 128 ? 2 : 1;
+  // The block's rings are idle by now: the least they hold, in floats, stages the chunks' accumulators.
+  constexpr int STAGE_FLOATS = WARPS * STAGES * 2 * DECODE_BN * ROW * (int)sizeof(bf16) / (int)sizeof(float);
 #pragma unroll 1
   for (int r = 0; r + TOGETHER <= GROUP; r += TOGETHER) {
     const int head = kvh * GROUP + r;
     combine_heads<TOGETHER>(part_o, part_ml, ((size_t)blockIdx.z * nq + head) * max_chunks, max_chunks, c0, c1,
-                     gate ? gate + token * gate_stride + (size_t)head * D : nullptr, out + (token * nq + head) * D);
+                     gate ? gate + token * gate_stride + (size_t)head * D : nullptr, out + (token * nq + head) * D,
+                     reinterpret_cast<float*>(smem_raw), STAGE_FLOATS);
   }
   if (GROUP % TOGETHER) {
     const int head = kvh * GROUP + GROUP - 1;
     combine_heads<1>(part_o, part_ml, ((size_t)blockIdx.z * nq + head) * max_chunks, max_chunks, c0, c1,
-                     gate ? gate + token * gate_stride + (size_t)head * D : nullptr, out + (token * nq + head) * D);
+                     gate ? gate + token * gate_stride + (size_t)head * D : nullptr, out + (token * nq + head) * D,
+                     reinterpret_cast<float*>(smem_raw), STAGE_FLOATS);
   }
   OMNIA_TRACE_BLOCK(7);
 }
