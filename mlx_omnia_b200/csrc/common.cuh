@@ -18,6 +18,7 @@
 #define OMNIA_ERR_TOKEN_ID 1   // a token id outside the embedding table
 #define OMNIA_ERR_SLOT 2       // a cache slot outside the page pool
 #define OMNIA_ERR_PAGE 4       // a block-table entry outside the page pool was needed
+#define OMNIA_ERR_WORK 16      // a work list asks a kernel for what it does not do
 
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);

@@ -20,7 +20,8 @@ decoded tokens, launches some 230 kernels one by one from Python and is bound by
 the same requests decode while a long prompt is read in portions of the token budget. So
 a step whose shape (tokens per request, wanted rows per request, the bucket of the
 longest decoding request, the width of the block tables: the next power of two above the
-longest request's pages, so a prompt doubles before it leaves its graph) comes for the
+longest request's pages, so a prompt doubles before it leaves its graph; whether its
+prompts all start at their first token, which kernels are chosen by) comes for the
 third time is captured with exactly that shape, and replayed whenever it comes again. The
 small lists that the attention kernels read (which block of query tokens runs where) are
 given a place on the device before the capture and filled by the host before every replay
@@ -200,8 +201,11 @@ class MixedGraphs:
         # are at most twice what its requests need (tables as wide as the pool cost a step of 64
         # requests 2.4 MB of metadata to fill and to copy).
         pages = max(-(-(e.request.tokens + q) // page) for e, q in zip(entries, q_lens))
+        # Whether every prompt of the step starts at its first token: kernels are chosen by it (a step's
+        # launches are the captured ones for as long as its key is the same).
+        fresh = all(e.request.tokens == 0 for e, q in zip(entries, q_lens) if q > 1)
         return (q_lens, tuple(len(e.want) for e in entries), ops.width_bucket(-(-longest // page)) if longest else 0,
-                max(64, 1 << (pages - 1).bit_length()))
+                max(64, 1 << (pages - 1).bit_length()), fresh)
 
     def wants(self, entries) -> tuple | None:
         """The shape's key if this step should run from a graph: the shape has come before."""

@@ -24,7 +24,8 @@ from mlx_omnia_b200.parts.base import KVView, StepContext
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
 ERROR_BITS = {1: "a token id outside the embedding table", 2: "a cache slot outside the page pool",
-              4: "a block-table entry outside the page pool", 8: "a bounded wait inside a kernel ran out"}
+              4: "a block-table entry outside the page pool", 8: "a bounded wait inside a kernel ran out",
+              16: "a work list asked a kernel for what it does not do"}
 
 
 class KernelError(RuntimeError):
@@ -433,13 +434,38 @@ def prefill_work_table(q_lens, seq_lens, tokens_per_block: int, tile: int, nkv: 
     return out
 
 
+WIDE_MIN_TOKENS = 512
+WIDE_MIN_WINDOW = 1024
+
+
+def wide_prefill_pays(q_lens, seq_lens, tokens_per_block: int, nkv: int, window: int, sms: int) -> bool:
+    """Which of the two tcgen05 prefill kernels a step's prompts take: True for the one that gives a
+    block an SM of its own (attention_tcgen05_wide.cu), False for the one that runs two blocks to an
+    SM and cuts long blocks into parts (attention_tcgen05.cu).
+
+    Measured on a B200 (16 query and 8 key/value heads of 128, with the gate; us, wide against two to
+    an SM): whole prompts of 1,024 / 2,048 / 3,000 tokens 23 / 38 / 69 against 29 / 46 / 86 (few blocks,
+    each a long chain of tiles, which a block alone on its SM walks at 1.16 us for 128 keys against
+    1.06 us for 64), 4 prompts of 512: 24 against 23; a whole prompt of 4,096 / 8,192 tokens 104 / 327
+    against 89 / 296 (many blocks: a block's 7 us of start and epilogue overlap nothing when it has its
+    SM alone); 8 portions of 256 over 1,024: 38 against 32; 512 over 8,192 cut into parts: 75 against
+    57. So: prompts from their first token, each of at least WIDE_MIN_TOKENS tokens, more blocks than
+    the other kernel would cut (two thirds of the SMs) and at most 2.6 to an SM, and no window shorter
+    than WIDE_MIN_WINDOW. The answer depends on the step's lengths and on whether its prompts start
+    at zero, both of which a captured step's key holds."""
+    prompts = [(n, held) for n, held in zip(q_lens, seq_lens or ()) if n > 1]
+    if not prompts or any(held != n or n < WIDE_MIN_TOKENS for n, held in prompts):
+        return False
+    blocks = sum(-(-n // tokens_per_block) for n, _ in prompts) * nkv
+    return 2 * sms < 3 * blocks and 5 * blocks <= 13 * sms and (not window or window >= WIDE_MIN_WINDOW)
+
+
 def _prefill_work_flat(step: StepContext, tokens_per_block: int, tile: int, nkv: int, window: int,
-                       device: torch.device) -> torch.Tensor:
+                       device: torch.device, places: int) -> torch.Tensor:
     """The list of `prefill_work_table` for this step, made once and shared by the layers of equal window."""
-    places = prefill_places(sm_count(device))
     capacity = prefill_blocks(step, tokens_per_block, nkv) + places if (step.workspace or {}).get("private") else None
     build = lambda st: prefill_work_table(st.q_lens, st.seq_lens_host, tokens_per_block, tile, nkv, window, places, capacity)
-    return _step_list(step, ("prefill_work_flat", tokens_per_block, tile, nkv, window), build, device)
+    return _step_list(step, ("prefill_work_flat", tokens_per_block, tile, nkv, window, places), build, device)
 
 
 def single_token_longest(step: StepContext) -> int:
@@ -489,7 +515,7 @@ def decode_fusable(proj: torch.Tensor, nq: int, nkv: int, d: int, inv_freq: torc
 
 def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale: float,
                     gate: torch.Tensor | None = None, gate_col: int = 0,
-                    projection: Projection | None = None) -> torch.Tensor:
+                    projection: Projection | None = None, wide: bool | None = None) -> torch.Tensor:
     """Causal (windowed) attention of this step's queries over the paged cache, the
     output multiplied by sigmoid(gate) when `gate` (the projected rows; the gate's
     columns start at `gate_col`) is given.  -> [tokens, nq * d]
@@ -550,13 +576,26 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
             return out
     if tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):
         per_block = 128 // (nq // nkv)
-        work = _prefill_work_flat(step, per_block, 64, nkv, kv.window or 0, q.device)
+        sms = sm_count(q.device)
+        if wide is None:
+            wide = wide_prefill_pays(step.q_lens, step.seq_lens_host, per_block, nkv, kv.window or 0, sms)
+        if wide:
+            # Every block whole (no places to share tiles over), an SM to a block.
+            work = _prefill_work_flat(step, per_block, 64, nkv, kv.window or 0, q.device, 0)
+            fn = _function("attention_tcgen05_wide", "omnia_attention_prefill_tcgen05_wide",
+                           [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p], defines)
+            _check(fn(_ptr(q), tokens, _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.seq_lens),
+                      _ptr(work), work.shape[0], gate_ptr, gate_stride, _ptr(out), max_pages, num_pages, nq, nkv,
+                      kv.page_size, kv.window or 0, scale, err, _stream()), "attention_prefill_tcgen05_wide")
+            return out
+        work = _prefill_work_flat(step, per_block, 64, nkv, kv.window or 0, q.device, prefill_places(sms))
         # Room for the parts of blocks that are cut (at most one more item per block the device runs at
         # a time) and a ticket per block; the sizes do not depend on the contexts' lengths.
         part_floats = _function("attention_tcgen05", "omnia_attention_tcgen05_part_floats", [], defines)()
         base = prefill_blocks(step, per_block, nkv)
         partial, tickets = _step_buffers(step, q.device, {
-            "prefill_parts": ((base + prefill_places(sm_count(q.device))) * part_floats, torch.float32, False),
+            "prefill_parts": ((base + prefill_places(sms)) * part_floats, torch.float32, False),
             "prefill_tickets": (base, torch.int32, True)})
         fn = _function("attention_tcgen05", "omnia_attention_prefill_tcgen05",
                        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,

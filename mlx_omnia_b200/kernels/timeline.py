@@ -24,7 +24,7 @@ def by_layer(kernels: list[tuple[str, int, float]], anchor: str) -> list[str]:
     """The spans of a model step as text: kernels of the repeating part (found by the distance
     between launches of library `anchor`, one per layer) by their place in a layer, with the
     median over layers; the kernels before and after the layers one by one."""
-    at = [i for i, (lib, _, _) in enumerate(kernels) if lib == anchor]
+    at = [i for i, (lib, _, _) in enumerate(kernels) if lib == anchor or lib == anchor + "_wide"]
     if len(at) < 2:
         return [f"{lib}:{line} {us:8.2f} us" for lib, line, us in kernels]
     period = at[1] - at[0]

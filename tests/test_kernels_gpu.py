@@ -124,6 +124,12 @@ def test_qk_norm_rope_store(ops, dtype, nq, nkv, d, page, rot):
     ops.raise_on_error(proj.device)
 
 
+def prefill_kernels(ops, dtype, nq, nkv, d, page):
+    """The choices of prefill kernel to run a case with: the dispatcher's own, and, where the tcgen05
+    kernels take the case, each of the two by name (False: two blocks to an SM; True: one)."""
+    return (None, False, True) if ops.tcgen05_attention_supported(dtype, nq, nkv, d, page) else (None,)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,d,page,window", [(4, 2, 16, 4, None), (8, 1, 24, 8, 16), (6, 3, 128, 16, None),
                                                    (5, 5, 40, 3, 7), (2, 1, 256, 16, 33), (16, 8, 64, 16, None)])
@@ -139,9 +145,10 @@ def test_paged_attention(ops, dtype, nq, nkv, d, page, window):
     gate = rand(step.num_tokens, nq * d + 24, dtype=dtype, seed=12)
     view = KVView(pages, table, torch.zeros(step.num_tokens, dtype=torch.int64, device="cuda"), page, window)
     scale = 1.3 * d ** -0.5
-    close(ops.paged_attention(q, view, step, scale), kernel_refs.paged_attention(q, view, step, scale), dtype)
-    close(ops.paged_attention(q, view, step, scale, gate=gate, gate_col=24),
-          kernel_refs.paged_attention(q, view, step, scale, gate=gate, gate_col=24), dtype)
+    for wide in prefill_kernels(ops, dtype, nq, nkv, d, page):
+        close(ops.paged_attention(q, view, step, scale, wide=wide), kernel_refs.paged_attention(q, view, step, scale), dtype)
+        close(ops.paged_attention(q, view, step, scale, gate=gate, gate_col=24, wide=wide),
+              kernel_refs.paged_attention(q, view, step, scale, gate=gate, gate_col=24), dtype)
     ops.raise_on_error(q.device)
 
 
@@ -170,9 +177,11 @@ def test_prefill_attention_at_a_window_s_edge_with_nan_elsewhere(ops, dtype, nq,
     gate = rand(step.num_tokens, nq * d, dtype=dtype, seed=32)
     view = KVView(pages, table, torch.zeros(step.num_tokens, dtype=torch.int64, device="cuda"), page, window)
     scale = 1.1 * d ** -0.5
-    got = ops.paged_attention(q, view, step, scale, gate=gate)
-    assert not torch.isnan(got).any()
-    close(got, kernel_refs.paged_attention(q, view, step, scale, gate=gate), dtype)
+    want = kernel_refs.paged_attention(q, view, step, scale, gate=gate)
+    for wide in prefill_kernels(ops, dtype, nq, nkv, d, page):
+        got = ops.paged_attention(q, view, step, scale, gate=gate, wide=wide)
+        assert not torch.isnan(got).any()
+        close(got, want, dtype)
     ops.raise_on_error(q.device)
 
 
@@ -214,9 +223,15 @@ def test_prefill_attention_in_parts(ops, nq, nkv, d, page, window):
         got = ops.paged_attention(q, view, step, scale, gate=gate)
         assert not torch.isnan(got).any()
         close(got, want, dtype)
-    plain = ops.paged_attention(q, view, step, scale)
     value = pages[slot, 1, :, far % page, :].float()  # [nkv, d]: the far key's value, what the last token must return
-    close(plain[q_lens[0] - 1].view(nq, d), value.repeat_interleave(nq // nkv, dim=0), dtype, scale=3)
+    for wide in (None, True):
+        plain = ops.paged_attention(q, view, step, scale, wide=wide)
+        close(plain[q_lens[0] - 1].view(nq, d), value.repeat_interleave(nq // nkv, dim=0), dtype, scale=3)
+    # The kernel that gives a block its SM walks the same long runs of keys whole, two teams taking
+    # turns with the tiles, the score buffers coming round many times.
+    got = ops.paged_attention(q, view, step, scale, gate=gate, wide=True)
+    assert not torch.isnan(got).any()
+    close(got, want, dtype)
     ops.raise_on_error(q.device)
 
 
