@@ -46,6 +46,8 @@ CUDA graphs are this engine's counterpart.
 
 from __future__ import annotations
 
+import contextlib
+import gc
 from dataclasses import dataclass
 
 import numpy as np
@@ -56,6 +58,24 @@ from mlx_omnia_b200.kernels import ops
 from mlx_omnia_b200.parts.base import StepContext
 
 MAX_GRAPHS = 24
+
+
+@contextlib.contextmanager
+def capturing(graph: torch.cuda.CUDAGraph, **options):
+    """`torch.cuda.graph` with the garbage collector out of the way. An object that owns a captured
+    graph or CUDA memory and is kept alive by reference cycles only (an engine dropped a while ago)
+    is freed whenever the collector next runs; if that is in the middle of a capture, freeing it is
+    an operation the capturing stream does not permit, and the capture is lost. So what is dead is
+    collected before the capture and nothing is collected during it."""
+    gc.collect()
+    enabled = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph, **options):
+            yield
+    finally:
+        if enabled:
+            gc.enable()
 
 
 def _bucket(n: int) -> int:
@@ -109,7 +129,7 @@ class DecodeGraphs:
         torch.cuda.synchronize(device)
         graph = torch.cuda.CUDAGraph()
         before = ops.launches
-        with torch.cuda.graph(graph):
+        with capturing(graph):
             logits = runner.model.forward(step, layers)
         return _Captured(graph, step, layout, host_tensor, dev, logits, ops.launches - before)
 
@@ -253,7 +273,7 @@ class MixedGraphs:
             torch.cuda.synchronize(runner.runtime.device)
             graph = torch.cuda.CUDAGraph()
             before = ops.launches
-            with torch.cuda.graph(graph):
+            with capturing(graph):
                 logits = runner.model.forward(step, layers)
             launches = ops.launches - before
             ops.launches = before  # the capture launched nothing

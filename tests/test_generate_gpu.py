@@ -249,9 +249,11 @@ def test_captured_mixed_steps_equal_eager_ones(name, dtype, page, portion, steps
         if graphs:
             # A shape is captured at its third coming; its tables are as wide as the next power of two
             # above the prompt's pages (64 at least), so the longer prompt outgrows its first graph.
-            widths = [max(64, 1 << (-(-portion * (k + 1) // page) - 1).bit_length()) for k in range(steps)]
+            # The step that brings the prompt's first portion has a key of its own (kernels may be chosen by
+            # whether a step's prompts start at their first token).
+            widths = [(max(64, 1 << (-(-portion * (k + 1) // page) - 1).bit_length()), k == 0) for k in range(steps)]
             comings = {w: widths.count(w) for w in set(widths)}
-            assert engine.runner.mixed_graphs.replays == sum(max(0, n - 3) for n in comings.values()) >= 2
+            assert engine.runner.mixed_graphs.replays == sum(max(0, n - 3) for n in comings.values()) >= 1
             assert len(engine.runner.mixed_graphs.captured) == sum(n >= 3 for n in comings.values())
         ops_check(engine)
         results.append(torch.cat(rows))
