@@ -401,6 +401,32 @@ extern "C" int omnia_qk_norm_rope_store(const void* proj, int row_stride, int q_
 }
 
 // ---------------------------------------------------------------------------------
+// angles[i][t] = (cos, sin)(positions[t] * inv_freq[i]): what a product's epilogue that rotates its
+// own rows reads. It has a thread per row, so the tokens run along the table's rows: a warp's 32
+// threads then read 32 neighbours. The same expression as in the kernel above, so a row rotates
+// alike wherever it is rotated.
+__global__ void rope_angles_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int half,
+                                   int tokens, float2* __restrict__ out) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (index >= (long long)tokens * half) return;
+  const int t = (int)(index / half), i = (int)(index % half);
+  float sn, cs;
+  sincosf((float)positions[t] * inv_freq[i], &sn, &cs);
+  out[(size_t)i * tokens + t] = make_float2(cs, sn);
+}
+
+extern "C" int omnia_rope_angles(const int* positions, const float* inv_freq, int half, int tokens, void* out,
+                                 cudaStream_t stream) {
+  const long long total = (long long)tokens * half;
+  if (total == 0) return 0;
+  launch_pdl(rope_angles_kernel, (int)((total + 255) / 256), 256, 0, stream, positions, inv_freq, half, tokens,
+             (float2*)out);
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------------------------
 // act[t, i] = silu(gu[t, i]) * gu[t, inner + i], in float32, rounded once.
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, long long total,

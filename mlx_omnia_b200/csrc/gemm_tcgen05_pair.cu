@@ -16,7 +16,11 @@
 // Blocks are persistent (one per SM); clusters take tiles round-robin; two accumulators in tensor
 // memory let the epilogue of one tile run while the next is multiplied. Epilogues: 0 store
 // bfloat16; 1 SwiGLU: the leader stages 128 gate rows of w, its peer the matching 128 up rows, the
-// blocks store silu(gate) * up; 2 soft cap to float32.
+// blocks store silu(gate) * up; 2 soft cap to float32; 3 the attention input projection
+// [q | gate | k | v]: a tile's 256 columns are whole heads, and the thread that owns a row gives each
+// head of q and k its weightless RMS norm and its rotation (angles from a table of the step's
+// positions), stores q to [tokens, heads, head size] and k and v straight into the cache pages at
+// the row's slot; columns of neither (the gate) are stored as epilogue 0 does.
 //
 // Every wait on a barrier is bounded: when the bound is hit the block raises OMNIA_ERR_TIMEOUT in
 // the error word and its roles leave their loops (its peer's waits then run out too); both blocks
@@ -37,7 +41,19 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;  // producer warp, MMA warp, four epilogue warps
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
 
-enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_SOFTCAP = 2 };
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_SOFTCAP = 2, EPI_QKV = 3 };
+
+// What epilogue 3 needs besides the product's own arguments.
+struct QkvParts {
+  int head_dim, q_col, k_col, v_col, nq, nkv;  // q: columns [q_col, q_col + nq * head_dim); k and v alike with nkv
+  float eps;                                    // of the norm of q and k heads; < 0: no norm
+  const float2* angles;                         // [head_dim / 2, rows] (cos, sin) at each row's position; null: no rotation
+  const long long* slots;                       // [rows] the cache slot of each row (negative: not stored); null with nkv 0
+  bf16* q_out;                                  // [rows, nq, head_dim]
+  bf16* pages;                                  // [pages, 2, nkv, page_size, head_dim]
+  int page_size;
+  long long num_slots;
+};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -151,11 +167,29 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
 
 constexpr int ACC_BUFS = 2;                                         // the tile being multiplied, the tile being stored
 
+// Which column of 256-wide tiles the `index`-th one to be worked on is. Epilogue 3 takes the tiles of
+// q and k first: theirs is the long epilogue, and the last tiles' epilogues overlap no product.
+template <int EPI>
+__device__ __forceinline__ int tile_column(int index, const QkvParts& parts) {
+  if (EPI != EPI_QKV) return index;
+  const int heads = 256 / parts.head_dim;  // of a tile
+  if (parts.q_col % 256 || parts.k_col % 256 || parts.nq % heads || parts.nkv % heads) return index;
+  const int q_tiles = parts.nq / heads, k_tiles = parts.nkv / heads, q0 = parts.q_col / 256, k0 = parts.k_col / 256;
+  if (index < q_tiles) return q0 + index;
+  if (index < q_tiles + k_tiles) return k0 + index - q_tiles;
+  // The others in their own order: count on past the two ranges, the lower one first.
+  int column = index - q_tiles - k_tiles;
+  const bool q_first = q0 < k0;
+  if (column >= (q_first ? q0 : k0)) column += q_first ? q_tiles : k_tiles;
+  if (column >= (q_first ? k0 : q0)) column += q_first ? k_tiles : q_tiles;
+  return column;
+}
+
 template <int EPI, uint32_t TILE_N>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          void* __restrict__ out, int m, int n, int k, int pair_offset, float multiplier,
-                         float cap, int m_tiles, int n_tiles, int* err) {
+                         float cap, int m_tiles, int n_tiles, const QkvParts parts, int* err) {
   constexpr int TILE_COLS = EPI == EPI_SWIGLU ? TILE_N / 2 : TILE_N;
   constexpr uint32_t HALF_N = TILE_N / 2;                           // rows of w a block stages
   constexpr uint32_t B_BYTES = HALF_N * BLOCK_K * sizeof(bf16);
@@ -210,7 +244,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       uint32_t it = 0;
       bool ok = true;
       for (int tile = cluster_id; tile < total_tiles && ok; tile += clusters) {
-        const int m0 = (tile % m_tiles) * 2 * BLOCK_M + rank * BLOCK_M, n0 = (tile / m_tiles) * TILE_COLS;
+        const int m0 = (tile % m_tiles) * 2 * BLOCK_M + rank * BLOCK_M, n0 = tile_column<EPI>(tile / m_tiles, parts) * TILE_COLS;
         const int w_row = EPI == EPI_SWIGLU ? (leader ? n0 : pair_offset + n0) : n0 + (int)rank * (int)HALF_N;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
@@ -259,7 +293,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     uint32_t local = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < total_tiles && ok; tile += clusters, ++local) {
-      const int m0 = (tile % m_tiles) * 2 * BLOCK_M + rank * BLOCK_M, n0 = (tile / m_tiles) * TILE_COLS;
+      const int m0 = (tile % m_tiles) * 2 * BLOCK_M + rank * BLOCK_M, n0 = tile_column<EPI>(tile / m_tiles, parts) * TILE_COLS;
       const int row = m0 + quarter * 32 + lane;
       const uint32_t buf = local % ACC_BUFS, round = local / ACC_BUFS;
       ok = mbar_wait(acc_full0 + 8 * buf, round & 1, abort_flag);
@@ -292,6 +326,91 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 if (col < pair_offset) dst[c + j] = __float2bfloat16_rn(v[0]);
                 if (col + 1 < pair_offset) dst[c + j + 1] = __float2bfloat16_rn(v[1]);
               }
+            }
+          }
+        }
+      } else if (EPI == EPI_QKV) {
+        const int d = parts.head_dim, half = d / 2;
+        const bool live = row < m;
+        const long long slot = live && parts.slots != nullptr ? parts.slots[row] : -1;
+        if (live && slot >= parts.num_slots && n0 == parts.k_col) atomicOr(err, OMNIA_ERR_SLOT);
+        // The accumulator's values rounded to bfloat16 first, as a separate product would store them.
+        auto rounded = [](uint32_t bits) { return __bfloat162float(__float2bfloat16_rn(__uint_as_float(bits))); };
+        auto store32 = [](bf16* to, const float* v) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+            *reinterpret_cast<uint4*>(to + j) = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
+                                                           *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+          }
+        };
+#pragma unroll 1
+        for (int seg = 0; seg < (int)TILE_N && n0 + seg < n; seg += d) {
+          const int col0 = n0 + seg;
+          // Whose head this is: 0 q, 1 k, 2 v, 3 neither. (The same for every thread of the block.)
+          int kind = 3, head = 0;
+          if (col0 >= parts.q_col && col0 < parts.q_col + parts.nq * d) kind = 0, head = (col0 - parts.q_col) / d;
+          else if (col0 >= parts.k_col && col0 < parts.k_col + parts.nkv * d) kind = 1, head = (col0 - parts.k_col) / d;
+          else if (col0 >= parts.v_col && col0 < parts.v_col + parts.nkv * d) kind = 2, head = (col0 - parts.v_col) / d;
+          bf16* dst = nullptr;
+          if (live) {
+            if (kind == 0) {
+              dst = parts.q_out + ((size_t)row * parts.nq + head) * d;
+            } else if (kind == 3) {
+              dst = reinterpret_cast<bf16*>(out) + (size_t)row * n + col0;
+            } else if (slot >= 0 && slot < parts.num_slots) {
+              const long long page = slot / parts.page_size, off = slot % parts.page_size;
+              dst = parts.pages + (((page * 2 + (kind == 2)) * parts.nkv + head) * parts.page_size + off) * d;
+            }
+          }
+          float scale = 1.f;
+          if (kind <= 1 && parts.eps >= 0.f) {
+            float ss[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+            for (int c = 0; c < d; c += 32) {
+              uint32_t acc[32];
+              tmem_load32(lane_base + seg + c, acc);
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float v = rounded(acc[j]);
+                ss[j & 3] = fmaf(v, v, ss[j & 3]);
+              }
+            }
+            scale = rsqrtf(((ss[0] + ss[1]) + (ss[2] + ss[3])) / (float)d + parts.eps);
+          }
+          if (kind <= 1 && parts.angles != nullptr) {
+            // Dims i and i + half turn together by the row's angle i.
+            const float2* angle = parts.angles + (live ? row : 0);  // this row's column of the table
+#pragma unroll 1
+            for (int c = 0; c < half; c += 32) {
+              uint32_t lo[32], hi[32];
+              tmem_load32(lane_base + seg + c, lo);
+              tmem_load32(lane_base + seg + half + c, hi);
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+              float out_lo[32], out_hi[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float2 turn = __ldg(angle + (size_t)(c + j) * m);  // (cos, sin)
+                const float a0 = rounded(lo[j]) * scale, b0 = rounded(hi[j]) * scale;
+                out_lo[j] = a0 * turn.x - b0 * turn.y, out_hi[j] = a0 * turn.y + b0 * turn.x;
+              }
+              if (dst != nullptr) {
+                store32(dst + c, out_lo);
+                store32(dst + half + c, out_hi);
+              }
+            }
+          } else {
+#pragma unroll 1
+            for (int c = 0; c < d; c += 32) {
+              uint32_t acc[32];
+              tmem_load32(lane_base + seg + c, acc);
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+              float v[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = rounded(acc[j]) * scale;
+              if (dst != nullptr) store32(dst + c, v);
             }
           }
         }
@@ -399,7 +518,7 @@ long long tile_count(int m, int n, int pair_offset, int tile_n, int* m_tiles, in
 
 template <int EPI, uint32_t TILE_N>
 int launch_width(const void* a, const void* w, void* out, int m, int n, int k, int pair_offset, float multiplier,
-                 float cap, int* err, cudaStream_t stream) {
+                 float cap, const QkvParts& parts, int* err, cudaStream_t stream) {
   constexpr uint32_t STAGE_BYTES = A_BYTES + (TILE_N / 2) * BLOCK_K * sizeof(bf16);
   CUtensorMap map_a, map_b;
   if (!make_map(&map_a, a, m, k, BLOCK_M) || !make_map(&map_b, w, n, k, (int)(TILE_N / 2)))
@@ -417,7 +536,7 @@ int launch_width(const void* a, const void* w, void* out, int m, int n, int k, i
   const int pairs = sm_count() / 2;
   const int clusters = (int)(total < pairs ? total : pairs);  // one persistent block per SM
   launch_pdl(gemm_tcgen05_pair_kernel<EPI, TILE_N>, 2 * clusters, THREADS, smem, stream,
-             map_a, map_b, out, m, n, k, pair_offset, multiplier, cap, m_tiles, n_tiles, err);
+             map_a, map_b, out, m, n, k, pair_offset, multiplier, cap, m_tiles, n_tiles, parts, err);
   return OMNIA_LAUNCH_RESULT();
 }
 
@@ -425,12 +544,13 @@ int launch_width(const void* a, const void* w, void* out, int m, int n, int k, i
 template <int EPI>
 int launch(const void* a, const void* w, void* out, int m, int n, int k, int pair_offset, float multiplier,
            float cap, int* err, cudaStream_t stream) {
+  const QkvParts parts = {};
   const int pairs = sm_count() / 2;
   int mt, nt;
   const long long wide = (tile_count<EPI>(m, n, pair_offset, 256, &mt, &nt) + pairs - 1) / pairs * 256;
   const long long narrow = (tile_count<EPI>(m, n, pair_offset, 192, &mt, &nt) + pairs - 1) / pairs * 192;
-  if (narrow < wide) return launch_width<EPI, 192>(a, w, out, m, n, k, pair_offset, multiplier, cap, err, stream);
-  return launch_width<EPI, 256>(a, w, out, m, n, k, pair_offset, multiplier, cap, err, stream);
+  if (narrow < wide) return launch_width<EPI, 192>(a, w, out, m, n, k, pair_offset, multiplier, cap, parts, err, stream);
+  return launch_width<EPI, 256>(a, w, out, m, n, k, pair_offset, multiplier, cap, parts, err, stream);
 }
 
 }  // namespace
@@ -449,4 +569,25 @@ extern "C" int omnia_gemm_tcgen05_pair(const void* a, const void* w, void* out, 
   if (epilogue == EPI_SOFTCAP) return launch<EPI_SOFTCAP>(a, w, out, m, n, k, 0, multiplier, cap, err, stream);
   if (epilogue != EPI_STORE) return (int)cudaErrorInvalidValue;
   return launch<EPI_STORE>(a, w, out, m, n, k, 0, 1.f, 0.f, err, stream);
+}
+
+// The attention input projection with epilogue 3: out [m, n] receives the columns that are neither
+// q, k nor v (the gate's); q_out [m, nq, head_dim]; k and v go to pages [.., 2, nkv, page_size,
+// head_dim] at slots[row] (nkv 0: nothing is stored). head_dim 64 or 128; q_col, k_col, v_col and n
+// multiples of head_dim, so that every head_dim columns of a tile are one head of one kind; angles
+// [head_dim / 2, m] (cos, sin) or null; eps < 0: no norm.
+extern "C" int omnia_gemm_tcgen05_pair_qkv(const void* a, const void* w, void* out, int m, int n, int k, int head_dim,
+                                           int q_col, int k_col, int v_col, int nq, int nkv, float eps,
+                                           const void* angles, const long long* slots, void* q_out, void* pages,
+                                           int page_size, long long num_slots, int* err, cudaStream_t stream) {
+  if (m == 0 || n == 0) return 0;
+  if (k <= 0 || k % 8 != 0 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) ||
+      ((uintptr_t)q_out & 15) || ((uintptr_t)pages & 15) || ((uintptr_t)angles & 15))
+    return (int)cudaErrorInvalidValue;
+  if ((head_dim != 64 && head_dim != 128) || n % head_dim || q_col % head_dim || k_col % head_dim || v_col % head_dim ||
+      nq < 0 || nkv < 0 || (nkv > 0 && (slots == nullptr || pages == nullptr || page_size < 1)))
+    return (int)cudaErrorInvalidValue;
+  const QkvParts parts = {head_dim, q_col, k_col, v_col, nq, nkv, eps, (const float2*)angles, slots, (bf16*)q_out,
+                          (bf16*)pages, page_size, num_slots};
+  return launch_width<EPI_QKV, 256>(a, w, out, m, n, k, 0, 1.f, 0.f, parts, err, stream);
 }

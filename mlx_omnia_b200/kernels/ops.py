@@ -711,6 +711,67 @@ def _gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epil
     return out
 
 
+def begin_pass(step: StepContext) -> None:
+    """A pass over the model's layers begins: what kernels keep for the length of one pass (tables
+    made from the step's positions, shared by the layers) is made afresh. A captured step is the
+    same object from replay to replay, and its capture must hold the kernels that make them."""
+    if isinstance(step.workspace, dict):
+        step.workspace.pop("pass", None)
+
+
+def rope_angles(step: StepContext, inv_freq: torch.Tensor) -> torch.Tensor:
+    """(cos, sin)(position * inv_freq) for every token of the step, float32 [len(inv_freq), tokens, 2],
+    made once per pass and per table of frequencies (layers of one base share it)."""
+    if step.workspace is None:
+        step.workspace = {}
+    made = step.workspace.setdefault("pass", {})
+    key = ("rope_angles", inv_freq.data_ptr())
+    table = made.get(key)
+    if table is None:
+        half = inv_freq.shape[0]
+        (table,) = _step_buffers(step, inv_freq.device,
+                                 {f"rope_angles_{inv_freq.data_ptr()}": (step.num_tokens * half * 2, torch.float32, False)})
+        fn = _function("elementwise", "omnia_rope_angles", [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
+        _check(fn(_ptr(step.positions), _ptr(inv_freq), half, step.num_tokens, _ptr(table), _stream()), "rope_angles")
+        made[key] = table
+    return table
+
+
+FUSED_QKV_ROWS = 1536
+"""From how many rows on the attention input projection runs on the two-SM tcgen05 kernel with the
+head norms, the rotation and the cache write in its epilogue, instead of the library's product and
+the kernel that reads its result back (B200, 2,048 x 2,048 -> 6,144: 38.8 us against 37.3 for the
+bare products, and the separate kernel's 13.9 us go away; at 1,024 rows the library's product is
+6 us ahead, which is what that kernel costs there)."""
+
+
+def linear_qkv(x, weight: torch.Tensor, q_col: int, k_col: int, v_col: int, nq: int, nkv: int, d: int,
+               eps: float | None, inv_freq: torch.Tensor | None, step: StepContext,
+               kv: KVView | None) -> tuple[torch.Tensor, torch.Tensor] | None:
+    """x @ weight.T for weight = [q | (gate) | k | v] rows, with `qk_norm_rope_store` done in the
+    product's epilogue: -> (the projected rows, of which only the columns that are neither q, k nor
+    v are written; q as [tokens, nq, d]), k and v in the cache pages. None where this does not
+    apply (few rows, another dtype, a head size other than 64 or 128, a rotation of part of the
+    head): the caller then takes the product and `qk_norm_rope_store` one after the other."""
+    store = kv is not None and kv.writes
+    if not (isinstance(x, torch.Tensor) and _tensor_core(x, weight, FUSED_QKV_ROWS) and d in (64, 128)
+            and (inv_freq is None or 2 * inv_freq.shape[0] == d) and weight.shape[0] % d == 0
+            and q_col % d == 0 and (not store or (k_col % d == 0 and v_col % d == 0 and kv.pages.dtype == torch.bfloat16))):
+        return None
+    rows, n = x.shape[0], weight.shape[0]
+    proj = torch.empty(rows, n, dtype=x.dtype, device=x.device)
+    q = torch.empty(rows, nq, d, dtype=x.dtype, device=x.device)
+    angles = None if inv_freq is None else rope_angles(step, inv_freq)
+    fn = _function("gemm_tcgen05_pair", "omnia_gemm_tcgen05_pair_qkv",
+                   [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                    c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p])
+    _check(fn(_ptr(x), _ptr(weight), _ptr(proj), rows, n, x.shape[1], d, q_col, k_col if store else 0, v_col if store else 0,
+              nq, nkv if store else 0, -1.0 if eps is None else eps, _ptr(angles), _ptr(kv.slot_mapping) if store else None,
+              _ptr(q), _ptr(kv.pages) if store else None, kv.page_size if store else 1,
+              kv.pages.shape[0] * kv.page_size if store else 0, _ptr(error_word(x.device)), _stream()), "gemm_tcgen05_pair_qkv")
+    return proj, q
+
+
 def _library_mm(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     if a.dtype == torch.float32 and (torch.backends.cuda.matmul.allow_tf32
                                       or torch.get_float32_matmul_precision() != "highest"):

@@ -77,8 +77,18 @@ class GQAAttention(Mixer):
             raise RuntimeError("an attention mixer needs cache pages")
         if ctx.kv.writes and not self.own_kv:
             raise RuntimeError("a mixer without k/v projections cannot own a cache entry")
-        proj = ops.linear(h, self.in_proj)
         inv_freq = self.position.table()
+        # Many rows: the product's epilogue normalises, rotates and stores (only the gate's columns of
+        # the projected rows are then written).
+        made = ops.linear_qkv(h, self.in_proj, self.q_col, self.k_col, self.v_col, self.heads,
+                              self.kv_heads if self.own_kv else 0, self.head_dim, self.qk_norm_eps, inv_freq, ctx.step,
+                              ctx.kv if self.own_kv else None)
+        if made is not None:
+            proj, q = made
+            out = ops.paged_attention(q, ctx.kv, ctx.step, self.scale, gate=proj if self.gated else None,
+                                      gate_col=self.gate_col)
+            return ops.linear(out, self.o_proj)
+        proj = ops.linear(h, self.in_proj)
         gate = proj if self.gated else None
         if self.own_kv and ops.decode_fusable(proj, self.heads, self.kv_heads, self.head_dim, inv_freq, ctx.kv,
                                               ctx.step):

@@ -113,6 +113,7 @@ class DecoderModel:
     def forward(self, step: StepContext, layers: list[LayerContext]) -> torch.Tensor:
         """Run this step's tokens through the schedule. -> float32 logits [wanted, vocab]"""
         schedule = self.spec.schedule
+        ops.begin_pass(step)
         x = self.embedding.forward(step.token_ids, step.positions)
         h = self.blocks[schedule[0].layer].entry_norm.forward(x)
         for e, entry in enumerate(schedule):

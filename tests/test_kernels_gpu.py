@@ -124,6 +124,50 @@ def test_qk_norm_rope_store(ops, dtype, nq, nkv, d, page, rot):
     ops.raise_on_error(proj.device)
 
 
+@pytest.mark.parametrize("nq,nkv,d,page,rotated,gated,hidden", [(4, 2, 128, 16, True, True, 192), (6, 3, 64, 32, True, False, 136),
+                                                                 (3, 1, 128, 16, False, True, 64), (4, 0, 64, 16, True, True, 72)])
+def test_input_projection_with_norm_rotation_and_cache_write_in_its_epilogue(ops, nq, nkv, d, page, rotated, gated, hidden):
+    """From some 1,500 rows on the attention input projection does in its epilogue what a kernel of
+    its own does for fewer rows: against the plain product followed by that kernel's reference,
+    with rows in two requests at positions far from zero, a row that stores nothing, a last tile
+    of rows that is not full, and pages that hold NaN wherever nothing is to be written (nkv 0: a
+    layer that reads another layer's cache writes none)."""
+    dtype = torch.bfloat16
+    q_lens, seq_lens = [900, 750], [5000, 750]
+    step = step_of(q_lens, seq_lens)
+    store = nkv > 0
+    pages, table = make_kv(seq_lens, max(nkv, 1), d, page, dtype, 4 + sum(-(-n // page) for n in seq_lens), seed=5)
+    pages.fill_(float("nan"))
+    slots = []
+    for s, (q, n) in enumerate(zip(q_lens, seq_lens)):
+        slots += [int(table[s, pos // page]) * page + pos % page for pos in range(n - q, n)]
+    slots[1000] = -1  # a padded token stores nothing
+    q_cols, kv_cols = nq * d, nkv * d
+    q_col, gate_col = 0, q_cols
+    k_col = q_cols * (2 if gated else 1)
+    v_col = k_col + kv_cols
+    weight = rand(v_col + kv_cols, hidden, dtype=dtype, scale=hidden ** -0.5, seed=61)
+    x = rand(step.num_tokens, hidden, dtype=dtype, seed=62)
+    inv_freq = (10000.0 ** (-torch.arange(d // 2, dtype=torch.float64) * 2 / d)).float().cuda() if rotated else None
+    for eps in (1e-6, None):
+        mine = KVView(pages.clone(), table, torch.tensor(slots, device="cuda"), page, None) if store else None
+        theirs = KVView(pages.clone(), table, torch.tensor(slots, device="cuda"), page, None) if store else None
+        made = ops.linear_qkv(x, weight, q_col, k_col, v_col, nq, nkv, d, eps, inv_freq, step, mine)
+        assert made is not None
+        proj, q = made
+        plain = (x.float() @ weight.float().t()).to(dtype)
+        want = kernel_refs.qk_norm_rope_store(plain, q_col, k_col, v_col, nq, nkv, d, eps, inv_freq, step.positions, theirs)
+        close(q, want, dtype)
+        if gated:
+            close(proj[:, gate_col: gate_col + q_cols], plain[:, gate_col: gate_col + q_cols], dtype)
+        if store:
+            written = ~torch.isnan(theirs.pages)
+            assert torch.equal(written, ~torch.isnan(mine.pages))  # the same places, no other
+            close(torch.nan_to_num(mine.pages), torch.nan_to_num(theirs.pages), dtype)
+    assert ops.linear_qkv(x[:1000], weight, q_col, k_col, v_col, nq, nkv, d, 1e-6, inv_freq, step, None) is None  # few rows
+    ops.raise_on_error(x.device)
+
+
 def prefill_kernels(ops, dtype, nq, nkv, d, page):
     """The choices of prefill kernel to run a case with: the dispatcher's own, and, where the tcgen05
     kernels take the case, each of the two by name (False: two blocks to an SM; True: one)."""

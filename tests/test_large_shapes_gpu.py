@@ -32,7 +32,7 @@ CONFIG = {
         "eos_token_id": [], "tie_word_embeddings": True,
     },
 }
-LENGTH = 1500
+LENGTH = 1600  # whole, its attention input projection has the norms, the rotation and the cache write in its epilogue
 
 
 @pytest.fixture(scope="module")
@@ -78,7 +78,7 @@ def exact_and_tolerances(config, tensors, ids):
 
 
 CUTS = {"whole": [LENGTH], "chunks": [512, 2, 301, 128, 7, LENGTH - 950 - 32] + [1] * 32,
-        "tail": [1000, 500 - 32] + [1] * 32}
+        "tail": [1000, LENGTH - 1000 - 32] + [1] * 32}
 
 
 def test_every_cut_at_the_benchmark_sizes(model):
