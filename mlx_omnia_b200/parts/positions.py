@@ -16,6 +16,9 @@ import torch
 from mlx_omnia_b200.parts.base import Position, register_position
 
 
+_TABLES: dict[tuple[int, float, str], torch.Tensor] = {}
+
+
 @register_position("rotary")
 class Rotary(Position):
     """Half-split rotary embedding over the first `dims` dims of each head.
@@ -34,9 +37,14 @@ class Rotary(Position):
 
     def load(self, tensors, runtime) -> None:
         super().load(tensors, runtime)
-        exponent = torch.arange(self.dims // 2, dtype=torch.float64) * (2.0 / self.dims)
-        inv = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -exponent)
-        self._table = inv.to(torch.float32).to(runtime.device)
+        # Layers of one base share one tensor: what kernels make from a table once per pass over the
+        # layers (the angles of a step's positions) is then made once, not once per layer.
+        key = (self.dims, self.theta, str(runtime.device))
+        if key not in _TABLES:
+            exponent = torch.arange(self.dims // 2, dtype=torch.float64) * (2.0 / self.dims)
+            inv = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -exponent)
+            _TABLES[key] = inv.to(torch.float32).to(runtime.device)
+        self._table = _TABLES[key]
 
     def table(self) -> torch.Tensor | None:
         return self._table
