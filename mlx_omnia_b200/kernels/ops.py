@@ -737,12 +737,14 @@ def rope_angles(step: StepContext, inv_freq: torch.Tensor) -> torch.Tensor:
     return table
 
 
-FUSED_QKV_ROWS = 1536
+FUSED_QKV_ROWS = 1280
 """From how many rows on the attention input projection runs on the two-SM tcgen05 kernel with the
 head norms, the rotation and the cache write in its epilogue, instead of the library's product and
-the kernel that reads its result back (B200, 2,048 x 2,048 -> 6,144: 38.8 us against 37.3 for the
-bare products, and the separate kernel's 13.9 us go away; at 1,024 rows the library's product is
-6 us ahead, which is what that kernel costs there)."""
+the kernel that reads its result back. B200, rows x 2,048 -> 6,144, us for the two against the one
+(without the 3 us of the angles' table, which a pass makes once for all its layers): 768 rows 22.7
+against 23.2, 1,024: 29.4 against 29.7, 1,280: 34.8 against 31.2, 1,536: 37.2 against 31.7, 2,048:
+50.7 against 42.9, 4,096: 94.0 against 80.8, 8,192: 182.7 against 154.8 (the bare products at
+2,048 rows: 38.8 us for this kernel, 37.3 for the library's)."""
 
 
 def linear_qkv(x, weight: torch.Tensor, q_col: int, k_col: int, v_col: int, nq: int, nkv: int, d: int,

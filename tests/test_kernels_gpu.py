@@ -127,7 +127,7 @@ def test_qk_norm_rope_store(ops, dtype, nq, nkv, d, page, rot):
 @pytest.mark.parametrize("nq,nkv,d,page,rotated,gated,hidden", [(4, 2, 128, 16, True, True, 192), (6, 3, 64, 32, True, False, 136),
                                                                  (3, 1, 128, 16, False, True, 64), (4, 0, 64, 16, True, True, 72)])
 def test_input_projection_with_norm_rotation_and_cache_write_in_its_epilogue(ops, nq, nkv, d, page, rotated, gated, hidden):
-    """From some 1,500 rows on the attention input projection does in its epilogue what a kernel of
+    """From some 1,300 rows on the attention input projection does in its epilogue what a kernel of
     its own does for fewer rows: against the plain product followed by that kernel's reference,
     with rows in two requests at positions far from zero, a row that stores nothing, a last tile
     of rows that is not full, and pages that hold NaN wherever nothing is to be written (nkv 0: a
