@@ -477,17 +477,22 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       }
     }
     if (ok && whole) {
-      // Eight dims a turn, the next turn's accumulator columns already on their way.
+      // 64 dims of the row's accumulator in one go (two loads side by side; eight dims a turn with the
+      // next turn's columns on their way took longer: every turn waited for a load), then eight dims
+      // at a time: normalise, gate, 16 bytes stored.
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = out + (token * nq + head) * D;
       const uint32_t o_addr = tmem_base + lane_field + O_COL;
-      uint32_t cur[8], next[8];
-      tmem_load8(o_addr, cur);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll 1
-      for (int c = 0; c < D; c += 8) {
-        if (c + 8 < D) tmem_load8(o_addr + c + 8, next);
-        if (live) {
+      for (int c0 = 0; c0 < D; c0 += 64) {
+        uint32_t acc[64];
+        tmem_load32(o_addr + c0, acc);
+        tmem_load32(o_addr + c0 + 32, acc + 32);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (!live) continue;
+#pragma unroll
+        for (int i = 0; i < 64; i += 8) {
+          const int c = c0 + i;
           uint4 g = make_uint4(0u, 0u, 0u, 0u);
           if (gate_tma) {
             // Row `row` of the 64-dim half c / 64, 128 bytes a row, its 16-byte pieces swizzled by the row.
@@ -504,7 +509,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            float a = __uint_as_float(cur[2 * e]) * inv, b2 = __uint_as_float(cur[2 * e + 1]) * inv;
+            float a = __uint_as_float(acc[i + 2 * e]) * inv, b2 = __uint_as_float(acc[i + 2 * e + 1]) * inv;
             if (gp) {
               const float2 gate2 = sigmoid_pair(g2[e]);
               a *= gate2.x;
@@ -514,9 +519,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
           }
           *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
         }
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int i = 0; i < 8; ++i) cur[i] = next[i];
       }
     } else if (whole && gate_issued) {
       // Giving up: the gate's copy must land before the block's shared memory goes away.

@@ -28,8 +28,8 @@
 // once a tile whatever has gone wrong, and `ok` is kept the same within a warp.
 //
 // Measured on a B200 (16/8 heads of 128, with the gate), against the two-blocks-to-an-SM kernel: a
-// whole prompt of 1,024 / 2,048 / 3,000 tokens 23 / 38 / 69 us against 29 / 46 / 86; of 4,096 / 8,192
-// tokens 104 / 327 against 89 / 296 (a block's 7 us of start and epilogue overlap nothing here, and in
+// whole prompt of 1,024 / 2,048 / 3,000 tokens 19 / 37 / 66 us against 24 / 44 / 85; of 4,096 / 8,192
+// tokens 101 / 323 against 88 / 290 (a block's 7 us of start and epilogue overlap nothing here, and in
 // the steady state both kernels take 1.35 us for 128 keys); portions cut into parts 75 against 57
 // (512 tokens over 8,192).
 #ifndef HEAD_DIM

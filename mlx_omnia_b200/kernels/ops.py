@@ -444,11 +444,11 @@ def wide_prefill_pays(q_lens, seq_lens, tokens_per_block: int, nkv: int, window:
     SM and cuts long blocks into parts (attention_tcgen05.cu).
 
     Measured on a B200 (16 query and 8 key/value heads of 128, with the gate; us, wide against two to
-    an SM): whole prompts of 1,024 / 2,048 / 3,000 tokens 23 / 38 / 69 against 29 / 46 / 86 (few blocks,
+    an SM): whole prompts of 1,024 / 2,048 / 3,000 tokens 19 / 37 / 66 against 24 / 44 / 85 (few blocks,
     each a long chain of tiles, which a block alone on its SM walks at 1.16 us for 128 keys against
-    1.06 us for 64), 4 prompts of 512: 24 against 23; a whole prompt of 4,096 / 8,192 tokens 104 / 327
-    against 89 / 296 (many blocks: a block's 7 us of start and epilogue overlap nothing when it has its
-    SM alone); 8 portions of 256 over 1,024: 38 against 32; 512 over 8,192 cut into parts: 75 against
+    1.06 us for 64), 4 prompts of 512: 23 against 23; a whole prompt of 4,096 / 8,192 tokens 101 / 323
+    against 88 / 290 (many blocks: a block's 7 us of start and epilogue overlap nothing when it has its
+    SM alone); 8 portions of 256 over 1,024: 36 against 31; 512 over 8,192 cut into parts: 75 against
     57. So: prompts from their first token, each of at least WIDE_MIN_TOKENS tokens, more blocks than
     the other kernel would cut (two thirds of the SMs) and at most 2.6 to an SM, and no window shorter
     than WIDE_MIN_WINDOW. The answer depends on the step's lengths and on whether its prompts start
