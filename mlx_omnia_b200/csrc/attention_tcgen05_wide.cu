@@ -309,9 +309,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const bool live = row < rows;
-    const int pos = pos0 + row / GROUP;
-    const int row_hi = live ? pos : -1;
-    const int row_lo = live ? (window > 0 ? max(0, pos - window + 1) : 0) : 0;
+    // A row past the block's last token (a prompt's last block need not be full) sees what the last
+    // token sees: it is never stored, and with a range of its own (none) its warp would take the
+    // masked path through every tile, which set the pace of a prompt's longest block (3,000 tokens:
+    // 85 us a layer against 63 for 3,008).
+    const int pos = min(pos0 + row / GROUP, last);
+    const int row_hi = pos;
+    const int row_lo = window > 0 ? max(0, pos - window + 1) : 0;
     const uint32_t lane_field = (uint32_t)(quarter * 32) << 16;
     const float sl2 = scale * LOG2E;
     float m = -INFINITY, l = 0.f;  // the offset this team last used (in units of scores), its sum against it

@@ -444,20 +444,21 @@ def wide_prefill_pays(q_lens, seq_lens, tokens_per_block: int, nkv: int, window:
     SM and cuts long blocks into parts (attention_tcgen05.cu).
 
     Measured on a B200 (16 query and 8 key/value heads of 128, with the gate; us, wide against two to
-    an SM): whole prompts of 1,024 / 2,048 / 3,000 tokens 19 / 37 / 66 against 24 / 44 / 85 (few blocks,
-    each a long chain of tiles, which a block alone on its SM walks at 1.16 us for 128 keys against
-    1.06 us for 64), 4 prompts of 512: 23 against 23; a whole prompt of 4,096 / 8,192 tokens 101 / 323
-    against 88 / 290 (many blocks: a block's 7 us of start and epilogue overlap nothing when it has its
-    SM alone); 8 portions of 256 over 1,024: 36 against 31; 512 over 8,192 cut into parts: 75 against
-    57. So: prompts from their first token, each of at least WIDE_MIN_TOKENS tokens, more blocks than
-    the other kernel would cut (two thirds of the SMs) and at most 2.6 to an SM, and no window shorter
-    than WIDE_MIN_WINDOW. The answer depends on the step's lengths and on whether its prompts start
-    at zero, both of which a captured step's key holds."""
+    an SM; a prompt of n tokens makes n / 64 blocks per key/value head): one whole prompt of 512 / 1,024
+    / 2,048 / 2,304 tokens 17 / 19 / 37 / 42 against 22 / 24 / 44 / 52 (few blocks, each a long chain of
+    tiles, which a block alone on its SM walks at 1.16 us for 128 keys against 1.06 us for 64), of
+    2,560 / 2,816 / 3,072: 53 / 61 / 68 against 57 / 60 / 65, of 4,096 / 8,192: 101 / 323 against 88 / 290
+    (a block's 7 us of start and epilogue overlap nothing when it has its SM alone); 2 prompts of 768
+    or of 1,024, 4 of 512: even; 2 of 1,536, 3 of 1,024 (384 blocks): 48 / 40 against 39 / 31; 8
+    portions of 256 over 1,024: 36 against 31; 512 over 8,192 cut into parts: 75 against 57. So:
+    prompts from their first token, each of at least WIDE_MIN_TOKENS tokens, at most two blocks to an
+    SM, and no window shorter than WIDE_MIN_WINDOW. The answer depends on the step's lengths and on
+    whether its prompts start at zero, both of which a captured step's key holds."""
     prompts = [(n, held) for n, held in zip(q_lens, seq_lens or ()) if n > 1]
     if not prompts or any(held != n or n < WIDE_MIN_TOKENS for n, held in prompts):
         return False
     blocks = sum(-(-n // tokens_per_block) for n, _ in prompts) * nkv
-    return 2 * sms < 3 * blocks and 5 * blocks <= 13 * sms and (not window or window >= WIDE_MIN_WINDOW)
+    return blocks <= 2 * sms and (not window or window >= WIDE_MIN_WINDOW)
 
 
 def _prefill_work_flat(step: StepContext, tokens_per_block: int, tile: int, nkv: int, window: int,

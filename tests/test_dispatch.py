@@ -152,15 +152,15 @@ def test_prefill_blocks_are_listed_longest_first_and_cut_into_parts(monkeypatch)
 
 
 def test_which_prefill_kernel_a_step_takes():
-    """One block to an SM pays for prompts from their first token with blocks enough not to be cut and
-    few enough for at most 2.6 to an SM; every other step takes the kernel with two blocks to an SM."""
+    """One block to an SM pays for prompts from their first token, each at least 512 tokens long, that
+    make at most two blocks to an SM; every other step takes the kernel with two blocks to an SM."""
     pays = lambda q, held, window=0: ops.wide_prefill_pays(q, held, 64, 8, window, 148)
-    assert pays([2048], [2048]) and pays([1024], [1024]) and pays([3000], [3000]) and pays([512] * 4, [512] * 4)
+    assert pays([512], [512]) and pays([1024], [1024]) and pays([2048], [2048]) and pays([2304], [2304])
+    assert pays([512] * 4, [512] * 4) and pays([1024, 1024], [1024, 1024])
     assert pays([1, 2048, 1], [300, 2048, 77])                # requests that decode beside the prompt do not matter
-    assert not pays([4096], [4096]) and not pays([2048, 2048], [2048, 2048])   # too many blocks
-    assert not pays([640], [640])                              # so few that the other kernel would cut them
+    assert not pays([2432], [2432]) and not pays([4096], [4096]) and not pays([1536, 1536], [1536, 1536])  # too many blocks
     assert not pays([1024], [4096]) and not pays([512], [8192])  # portions of prompts under way
-    assert not pays([256] * 8, [256] * 8)                      # short prompts: short chains of tiles
+    assert not pays([256] * 8, [256] * 8) and not pays([2048, 300], [2048, 300])  # short prompts: short chains of tiles
     assert not pays([2048], [2048], window=600) and pays([2048], [2048], window=1024)
     assert not pays([1, 1], [50, 60]) and not pays([2048], None)
     assert ops.wide_prefill_pays([2048], [2048], 32, 8, 0, 148) is False  # groups of four: 512 blocks
