@@ -647,14 +647,15 @@ def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
 SKINNY_ROWS = 16
 """Up to this many activation rows, bfloat16 products run on the weight-streaming kernel."""
 
-FUSED_GATE_ROWS = 640
+FUSED_GATE_ROWS = 320
 FUSED_CAP_ROWS = 129
 """From these many rows on, the products that have an epilogue fused into them (gate‖up with SwiGLU;
 the head with its soft cap) run on this package's tcgen05 kernels. Measured on B200 inside replayed
 graphs (weights of 8 to 50 MB, fresh for every launch): gate‖up with SwiGLU takes 46.7 us at 1,024
 rows, 87.5 at 2,048 and 305 at 8,192, against 58.7, 112 and 408 for the vendor library's product
-followed by the SwiGLU kernel; below some 600 rows the library's pair is the faster one (23 against
-24 us at 264 rows).
+followed by the SwiGLU kernel; at 384 / 512 / 640 / 768 / 896 rows 24.3 / 31.0 / 34.6 / 35.0 / 46.3
+against 26.7 / 33.8 / 41.5 / 43.0 / 55.5 (the kernel with one SM or two to a tile, whichever runs fewer
+waves: `_pair_pays`); at 264 rows the library's pair is the faster one (23.3 against 24.1 us).
 
 A product with nothing fused into it is the vendor library's above the streaming kernel's rows, as the
 reference's is MLX's. The tcgen05 kernels take the same products (`_gemm_tcgen05`, tested), but the
@@ -693,8 +694,16 @@ def _pair_pays(rows: int, n: int, k: int, epilogue: int, sms: int) -> bool:
     the work is less (2,048 x 2,048 x 2,048; 512 rows)."""
     if rows < 256:
         return False
-    tile_cols = 128 if epilogue == 1 else 256
-    tiles = -(-rows // 256) * -(-(n // 2 if epilogue == 1 else n) // tile_cols)
+    if epilogue == 1:
+        # gate|up with SwiGLU: tiles of 128 output columns, 128 rows to an SM or 256 to a pair. What
+        # decides is how many waves of tiles each kernel runs (measured, 12,288 weight rows of 2,048:
+        # some 10 us and 14 a wave for one SM, 8 and 13 a wave for a pair; 264 / 512 / 768 / 896 rows:
+        # 24 / 38 / 38 / 51 us against 30 / 31 / 35 / 46).
+        tiles = -(-(n // 2) // 128)
+        one = -(-(-(-rows // 128) * tiles) // sms)
+        two = -(-(-(-rows // 256) * tiles) // (sms // 2))
+        return 8 + 13 * two < 10 + 14 * one
+    tiles = -(-rows // 256) * -(-n // 256)
     return tiles * -(-k // 64) >= 64 * (sms // 2)
 
 
