@@ -164,3 +164,15 @@ def test_which_prefill_kernel_a_step_takes():
     assert not pays([2048], [2048], window=600) and pays([2048], [2048], window=1024)
     assert not pays([1, 1], [50, 60]) and not pays([2048], None)
     assert ops.wide_prefill_pays([2048], [2048], 32, 8, 0, 148) is False  # groups of four: 512 blocks
+
+
+def test_which_tcgen05_kernel_takes_gate_up_with_swiglu():
+    """One SM to a 128-row tile or two SMs to a 256-row tile: the one that runs fewer waves of tiles
+    (12,288 weight rows: 48 tiles of 128 output columns per tile of rows, 148 SMs or 74 pairs)."""
+    pair = lambda rows, n=12288: ops._pair_pays(rows, n, 2048, 1, 148)
+    assert not pair(264) and not pair(384)          # 144 tiles: one wave of SMs against two of pairs
+    assert pair(385) and pair(512) and pair(768)    # two waves either way, and a pair's wave is the shorter
+    assert pair(896) and pair(2048) and pair(8192)
+    assert not pair(200)                            # under a pair's 256 rows
+    assert not pair(896, 24576)                     # twice the columns: five waves of SMs against six of pairs
+    assert ops.FUSED_GATE_ROWS <= 384
