@@ -333,7 +333,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const int d = parts.head_dim, half = d / 2;
         const bool live = row < m;
         const long long slot = live && parts.slots != nullptr ? parts.slots[row] : -1;
-        if (live && slot >= parts.num_slots && n0 == parts.k_col) atomicOr(err, OMNIA_ERR_SLOT);
         // The accumulator's values rounded to bfloat16 first, as a separate product would store them.
         auto rounded = [](uint32_t bits) { return __bfloat162float(__float2bfloat16_rn(__uint_as_float(bits))); };
         auto store32 = [](bf16* to, const float* v) {
@@ -353,6 +352,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           if (col0 >= parts.q_col && col0 < parts.q_col + parts.nq * d) kind = 0, head = (col0 - parts.q_col) / d;
           else if (col0 >= parts.k_col && col0 < parts.k_col + parts.nkv * d) kind = 1, head = (col0 - parts.k_col) / d;
           else if (col0 >= parts.v_col && col0 < parts.v_col + parts.nkv * d) kind = 2, head = (col0 - parts.v_col) / d;
+          // A slot past the pool is reported (once a row: by whoever has the first head of k) and not stored to.
+          if (live && kind == 1 && head == 0 && slot >= parts.num_slots) atomicOr(err, OMNIA_ERR_SLOT);
           bf16* dst = nullptr;
           if (live) {
             if (kind == 0) {

@@ -166,6 +166,15 @@ def test_input_projection_with_norm_rotation_and_cache_write_in_its_epilogue(ops
             close(torch.nan_to_num(mine.pages), torch.nan_to_num(theirs.pages), dtype)
     assert ops.linear_qkv(x[:1000], weight, q_col, k_col, v_col, nq, nkv, d, 1e-6, inv_freq, step, None) is None  # few rows
     ops.raise_on_error(x.device)
+    if store:
+        # A slot past the pool is reported, and nothing is written for it.
+        beyond = list(slots)
+        beyond[7] = pages.shape[0] * page + 3
+        view = KVView(pages.clone(), table, torch.tensor(beyond, device="cuda"), page, None)
+        ops.linear_qkv(x, weight, q_col, k_col, v_col, nq, nkv, d, 1e-6, inv_freq, step, view)
+        with pytest.raises(ops.KernelError, match="cache slot"):
+            ops.raise_on_error(x.device)
+        assert int((~torch.isnan(view.pages)).sum()) == (len(slots) - 2) * 2 * nkv * d  # all rows but that one and the padded one
 
 
 def prefill_kernels(ops, dtype, nq, nkv, d, page):
